@@ -1,0 +1,269 @@
+// Row-wise kernels of the decoder: embedding gather, RMS norm fused with the
+// residual add, per-head q/k norm + rotation + cache write, and the SiLU gate.
+//
+// The residual stream is always float32.  `act` tensors (what matrix products read
+// and write) are float32 or bfloat16, chosen per call by `act_bf16`; weights of
+// norms and the embedding table by `w_bf16`.  All arithmetic is float32.
+//
+// Formulas restated from the reference (paths within lilong555/mini-llm-runtime):
+//   gather        src/minillm/cuda/ops.cu:60-81     out[r,:] = table[id[r],:]
+//   rms norm      src/minillm/kernels.cpp:209-216   (x * 1/sqrt(mean(x^2)+eps)) * w
+//   rotation      src/minillm/cuda/ops.cu:128-151   half-split, products rounded separately
+//   cache write   src/minillm/cuda/attention.cu:74-95
+//   gate          src/minillm/cuda/ops.cu:161       g / (1 + exp(-g)) * u
+#include "common.cuh"
+
+namespace {
+
+// ------------------------------------------------------------------ embedding
+template <typename W>
+__global__ void embed_gather_kernel(float* __restrict__ out, const W* __restrict__ table,
+                                    const int* __restrict__ ids, int width, int vocab, int* status) {
+    const int row = blockIdx.x;
+    const int id = ids[row];
+    float* dst = out + static_cast<size_t>(row) * width;
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0 && status) atomicOr(status, MLR_STATUS_BAD_INDEX);
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = 0.0f;
+        return;
+    }
+    const W* src = table + static_cast<size_t>(id) * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = mlr_load(src, i);
+}
+
+// ------------------------------------------------------------------ rms norm
+// out[r,:] = rmsnorm(h[row,:] + delta[row,:]) * w, row = rows ? rows[r] : r.
+// With write_back the sum replaces h[row,:] (the residual stream moves on).
+template <typename T, typename W>
+__global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta,
+                               const W* __restrict__ weight, T* __restrict__ out,
+                               const int* __restrict__ rows, int width, float eps, int write_back) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const size_t row = rows ? static_cast<size_t>(rows[r]) : static_cast<size_t>(r);
+    float* hr = h + row * width;
+    const float* dr = delta ? delta + row * width : nullptr;
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float x = dr ? hr[i] + dr[i] : hr[i];
+        sum = fmaf(x, x, sum);
+    }
+    sum = mlr_block_sum(sum, scratch);
+    const float scale = 1.0f / sqrtf(sum / static_cast<float>(width) + eps);
+    T* dst = out + static_cast<size_t>(r) * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float x = dr ? hr[i] + dr[i] : hr[i];
+        if (write_back && dr) hr[i] = x;
+        mlr_store(dst, i, (x * scale) * mlr_load(weight, i));
+    }
+}
+
+// h[row,:] += delta[row,:] for all rows (when no norm follows).
+__global__ void residual_add_kernel(float* __restrict__ h, const float* __restrict__ delta, size_t count) {
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < count;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x)
+        h[i] += delta[i];
+}
+
+// ------------------------------------------------------------------ q/k norm, rotation, cache write
+// One warp per (row, head).  Heads [0,Hq) are queries (normed and rotated in place),
+// [Hq,Hq+Hkv) keys (normed, rotated, written to the cache; also in place), the last Hkv
+// are values (copied to the cache).  The cache of one layer is
+// [page][K|V][kv_head][token_in_page][D]; the page of a token is
+// block_table[segment][position / page_size].
+constexpr int kMaxPairsPerLane = 4;  // D/2 <= 128
+
+template <typename T, typename W>
+__global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, int ld, int rows, int q_heads, int kv_heads,
+                                          int head_dim, const W* __restrict__ q_weight,
+                                          const W* __restrict__ k_weight, float eps,
+                                          const float* __restrict__ cos_sin, int table_positions,
+                                          const int* __restrict__ positions,
+                                          const int* __restrict__ segment_of_row,
+                                          const int* __restrict__ block_table, int table_stride,
+                                          int page_size, T* __restrict__ cache, int num_pages,
+                                          int write_cache, int* status) {
+    const int warps = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x;
+    const int head = blockIdx.y * warps + (threadIdx.x >> 5);
+    const int heads = q_heads + 2 * kv_heads;
+    if (row >= rows || head >= heads) return;
+    const int half = head_dim >> 1;
+    const int position = positions[row];
+    T* x = qkv + static_cast<size_t>(row) * ld + static_cast<size_t>(head) * head_dim;
+    const bool is_query = head < q_heads;
+    const bool is_key = !is_query && head < q_heads + kv_heads;
+    const bool is_value = !is_query && !is_key;
+    if (!is_query && !write_cache) return;
+
+    // Destination in the cache for keys and values.
+    T* dst = nullptr;
+    if (!is_query) {
+        const int kv_head = is_key ? head - q_heads : head - q_heads - kv_heads;
+        const int segment = segment_of_row[row];
+        const int page = block_table[static_cast<size_t>(segment) * table_stride + position / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (lane == 0 && status) atomicOr(status, MLR_STATUS_BAD_PAGE);
+            return;
+        }
+        const size_t page_elems = static_cast<size_t>(2) * kv_heads * page_size * head_dim;
+        dst = cache + page * page_elems +
+              (static_cast<size_t>(is_key ? 0 : 1) * kv_heads + kv_head) * page_size * head_dim +
+              static_cast<size_t>(position % page_size) * head_dim;
+    }
+    if (is_value) {
+        for (int i = lane; i < head_dim; i += 32) dst[i] = x[i];
+        return;
+    }
+    float lo[kMaxPairsPerLane], hi[kMaxPairsPerLane];
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kMaxPairsPerLane; ++k) {
+        const int j = lane + 32 * k;
+        lo[k] = hi[k] = 0.0f;
+        if (j < half) {
+            lo[k] = mlr_load(x, j);
+            hi[k] = mlr_load(x, j + half);
+            sum = fmaf(lo[k], lo[k], sum);
+            sum = fmaf(hi[k], hi[k], sum);
+        }
+    }
+    const W* weight = is_query ? q_weight : k_weight;
+    float scale = 1.0f;
+    if (weight) {
+        sum = mlr_warp_sum(sum);
+        scale = 1.0f / sqrtf(sum / static_cast<float>(head_dim) + eps);
+    }
+    const bool rotate = cos_sin != nullptr;
+    if (rotate && (position < 0 || position >= table_positions)) {
+        if (lane == 0 && status) atomicOr(status, MLR_STATUS_BAD_INDEX);
+        return;
+    }
+    const float* cs = rotate ? cos_sin + static_cast<size_t>(position) * head_dim : nullptr;
+#pragma unroll
+    for (int k = 0; k < kMaxPairsPerLane; ++k) {
+        const int j = lane + 32 * k;
+        if (j < half) {
+            float a = lo[k], b = hi[k];
+            if (weight) {
+                a = (a * scale) * mlr_load(weight, j);
+                b = (b * scale) * mlr_load(weight, j + half);
+            }
+            if (rotate) {
+                const float c = cs[j], s = cs[j + half];
+                const float ra = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+                const float rb = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
+                a = ra;
+                b = rb;
+            }
+            mlr_store(x, j, a);
+            mlr_store(x, j + half, b);
+            if (dst) {
+                mlr_store(dst, j, a);
+                mlr_store(dst, j + half, b);
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ SiLU gate
+// gate_up is [rows, 2*inter]: the gate in the first `inter` columns, up in the rest.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inter) {
+    const size_t total = static_cast<size_t>(rows) * inter;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t r = i / inter, c = i - r * inter;
+        const float g = mlr_load(gate_up, r * 2 * inter + c);
+        const float u = mlr_load(gate_up, r * 2 * inter + inter + c);
+        mlr_store(out, i, (g / (1.0f + expf(-g))) * u);
+    }
+}
+
+int row_threads(int width) {
+    int t = 32;
+    while (t < 256 && t * 4 < width) t <<= 1;
+    return t;
+}
+
+}  // namespace
+
+MLR_API int mlr_embed_gather(float* out, const void* table, int w_bf16, const int* ids, int rows, int width,
+                             int vocab, int* status, cudaStream_t stream) {
+    MLR_REQUIRE(rows >= 0 && width > 0 && vocab > 0, "embed_gather: bad sizes rows=%d width=%d vocab=%d", rows, width, vocab);
+    if (rows == 0) return 0;
+    const int threads = row_threads(width);
+    if (w_bf16)
+        embed_gather_kernel<<<rows, threads, 0, stream>>>(out, static_cast<const __nv_bfloat16*>(table), ids, width, vocab, status);
+    else
+        embed_gather_kernel<<<rows, threads, 0, stream>>>(out, static_cast<const float*>(table), ids, width, vocab, status);
+    return mlr_launched("embed_gather");
+}
+
+MLR_API int mlr_rmsnorm(float* h, const float* delta, const void* weight, int w_bf16, void* out, int act_bf16,
+                        const int* rows, int count, int width, float eps, int write_back, cudaStream_t stream) {
+    MLR_REQUIRE(count >= 0 && width > 0, "rmsnorm: bad sizes count=%d width=%d", count, width);
+    MLR_REQUIRE(eps > 0.0f, "rmsnorm: eps must be positive, got %g", static_cast<double>(eps));
+    if (count == 0) return 0;
+    const int threads = row_threads(width);
+#define MLR_LAUNCH(T, W)                                                                                   \
+    rmsnorm_kernel<T, W><<<count, threads, 0, stream>>>(h, delta, static_cast<const W*>(weight),          \
+                                                         static_cast<T*>(out), rows, width, eps, write_back)
+    if (act_bf16 && w_bf16) MLR_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else if (act_bf16) MLR_LAUNCH(__nv_bfloat16, float);
+    else if (w_bf16) MLR_LAUNCH(float, __nv_bfloat16);
+    else MLR_LAUNCH(float, float);
+#undef MLR_LAUNCH
+    return mlr_launched("rmsnorm");
+}
+
+MLR_API int mlr_residual_add(float* h, const float* delta, long long count, cudaStream_t stream) {
+    MLR_REQUIRE(count >= 0, "residual_add: negative count");
+    if (count == 0) return 0;
+    const int blocks = static_cast<int>(count / 1024 + 1 < 4096 ? count / 1024 + 1 : 4096);
+    residual_add_kernel<<<blocks, 256, 0, stream>>>(h, delta, static_cast<size_t>(count));
+    return mlr_launched("residual_add");
+}
+
+MLR_API int mlr_qk_norm_rope_cache(void* qkv, int act_bf16, int ld, int rows, int q_heads, int kv_heads,
+                                   int head_dim, const void* q_weight, const void* k_weight, int w_bf16,
+                                   float eps, const float* cos_sin, int rotary_dim, int table_positions,
+                                   const int* positions, const int* segment_of_row, const int* block_table,
+                                   int table_stride, int page_size, void* cache, int num_pages,
+                                   int write_cache, int* status, cudaStream_t stream) {
+    MLR_REQUIRE(rows >= 0 && q_heads > 0 && kv_heads > 0, "qk_norm_rope_cache: bad head counts %d/%d", q_heads, kv_heads);
+    MLR_REQUIRE(head_dim >= 2 && head_dim % 2 == 0 && head_dim <= 64 * kMaxPairsPerLane,
+                "qk_norm_rope_cache: head size %d is not an even number in [2, %d]", head_dim, 64 * kMaxPairsPerLane);
+    MLR_REQUIRE(cos_sin == nullptr || rotary_dim == head_dim,
+                "qk_norm_rope_cache: rotary size %d differs from head size %d (partial rotation is not built)", rotary_dim, head_dim);
+    MLR_REQUIRE(ld >= (q_heads + 2 * kv_heads) * head_dim, "qk_norm_rope_cache: row stride %d is smaller than the qkv width", ld);
+    MLR_REQUIRE((q_weight == nullptr) == (k_weight == nullptr), "qk_norm_rope_cache: q and k norm weights must both be given or both be absent");
+    MLR_REQUIRE(!write_cache || (cache && block_table && page_size > 0 && num_pages > 0), "qk_norm_rope_cache: cache write without a cache");
+    if (rows == 0) return 0;
+    const int warps = 4;
+    const dim3 grid(rows, (q_heads + 2 * kv_heads + warps - 1) / warps);
+#define MLR_LAUNCH(T, W)                                                                                       \
+    qk_norm_rope_cache_kernel<T, W><<<grid, warps * 32, 0, stream>>>(                                          \
+        static_cast<T*>(qkv), ld, rows, q_heads, kv_heads, head_dim, static_cast<const W*>(q_weight),         \
+        static_cast<const W*>(k_weight), eps, cos_sin, table_positions, positions, segment_of_row, block_table, \
+        table_stride, page_size, static_cast<T*>(cache), num_pages, write_cache, status)
+    if (act_bf16 && w_bf16) MLR_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else if (act_bf16) MLR_LAUNCH(__nv_bfloat16, float);
+    else if (w_bf16) MLR_LAUNCH(float, __nv_bfloat16);
+    else MLR_LAUNCH(float, float);
+#undef MLR_LAUNCH
+    return mlr_launched("qk_norm_rope_cache");
+}
+
+MLR_API int mlr_swiglu(const void* gate_up, void* out, int act_bf16, int rows, int inter, cudaStream_t stream) {
+    MLR_REQUIRE(rows >= 0 && inter > 0, "swiglu: bad sizes rows=%d inter=%d", rows, inter);
+    if (rows == 0) return 0;
+    const size_t total = static_cast<size_t>(rows) * inter;
+    const int blocks = static_cast<int>(total / 1024 + 1 < 148 * 16 ? total / 1024 + 1 : 148 * 16);
+    if (act_bf16)
+        swiglu_kernel<<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, inter);
+    else
+        swiglu_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float*>(gate_up), static_cast<float*>(out), rows, inter);
+    return mlr_launched("swiglu");
+}

@@ -1,0 +1,289 @@
+"""The generic model: parts built from a plan, a cache, and ONE step function.
+
+`Model.step(entries)` is the only way tokens reach the kernels.  Generation
+(`engine/engine.py`), the command line and trace replay (`bin/trace_run`) all call
+it; it is the counterpart of the reference's `CudaRuntime::forward`
+(src/minillm/cuda/runtime.cpp:146-254): validate the batch, take cache pages before
+any device work, upload the step's metadata in one copy, gather the embeddings, run
+the layers in the plan's order, norm and project only the rows whose logits are
+wanted, and publish lengths and page maps once the work is enqueued.
+
+A batch is a list of entries, one per request: its next tokens (a portion of its
+prompt, or one decoded token) and the places among them whose logits are wanted.
+All entries run as one batch of rows; the rows of one request are consecutive
+positions that continue what the cache holds for it.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import parts as _builtin_parts  # noqa: F401  (registers the built-in parts)
+from ..cache.manager import CacheManager, GroupSpec, OutOfPages
+from ..config.base import ModelPlan, PartSpec
+from ..config.registry import part_class
+from ..csrc import build
+from ..parts.base import Block, CacheNeed, RunContext, Segment, StateNeed, StepContext
+from ..weights.loader import WeightSpec, merge_specs
+from .runtime import Runtime
+
+
+class StepError(ValueError):
+    """A batch the step function refuses; nothing was run and nothing changed."""
+
+
+class DeviceFault(RuntimeError):
+    """A kernel reported a bad index, a bad page or a non-finite value."""
+
+
+@dataclass
+class StepEntry:
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class CacheConfig:
+    page_size: int = 16
+    num_pages: int = 0                       # pages of every group, unless `pages_per_group` says otherwise
+    max_requests: int = 4
+    max_model_len: int = 0                   # 0: the model's maximum positions
+    pages_per_group: Optional[Sequence[int]] = None
+    fill_nan: bool = True                    # start the pools as NaN so that a stale read shows
+
+
+@dataclass
+class _RunPlan:
+    block: Block
+    context: RunContext
+    need: Optional[CacheNeed]
+    state_need: Optional[StateNeed]
+
+
+def build_part(category: str, spec: PartSpec):
+    return part_class(category, spec.kind)(spec)
+
+
+class Model:
+    def __init__(self, plan: ModelPlan, rt: Runtime):
+        plan.validate()
+        self.plan, self.rt = plan, rt
+        self.positions = {name: build_part("position", spec) for name, spec in plan.positions.items()}
+        self.embedding = build_part("embedding", plan.embedding)
+        self.final_norm = build_part("norm", plan.final_norm)
+        self.lm_head = build_part("lm_head", plan.lm_head)
+        self.blocks: List[Block] = []
+        for layer in plan.layers:
+            mixer = build_part("mixer", layer.mixer)
+            if getattr(mixer, "position_name", None) is not None:
+                mixer.position = self.positions[mixer.position_name]
+            ff = build_part("feed_forward", layer.feed_forward)
+            norms = {slot: build_part("norm", spec) for slot, spec in layer.norms.items()}
+            self.blocks.append(part_class("block", layer.block)(PartSpec(layer.block), mixer, ff, norms))
+        # Cache groups: runs whose mixers keep the same span of keys share page ids.
+        self.group_windows: List[Optional[int]] = []
+        self.runs: List[_RunPlan] = []
+        for i, run in enumerate(plan.schedule):
+            block = self.blocks[run.layer]
+            need, state_need = block.mixer.cache_need(), block.mixer.state_need()
+            ctx = RunContext()
+            if run.kv_from is not None:
+                source = self.runs[run.kv_from]
+                if need is None or source.need != need:
+                    raise ValueError(f"run {i} cannot read the cache of run {run.kv_from}: {need} vs {source.need}")
+                ctx.group, ctx.write_cache = source.context.group, False
+            elif need is not None:
+                if need.window not in self.group_windows:
+                    self.group_windows.append(need.window)
+                ctx.group = self.group_windows.index(need.window)
+            self.runs.append(_RunPlan(block, ctx, need, state_need))
+        self.cache: Optional[CacheManager] = None
+        self.cache_config: Optional[CacheConfig] = None
+        self.status = None
+        self._pinned: List[Tuple[torch.Tensor, torch.cuda.Event]] = []
+        self._pinned_next = 0
+        self._bound = False
+
+    # ------------------------------------------------------------------ weights
+    def _all_parts(self):
+        yield self.embedding
+        yield from self.positions.values()
+        for block in self.blocks:
+            yield block.mixer
+            yield block.feed_forward
+            yield from block.norms.values()
+        yield self.final_norm
+        yield self.lm_head
+
+    def expected_weights(self) -> Dict[str, WeightSpec]:
+        return merge_specs(spec for part in self._all_parts() for spec in part.weight_specs())
+
+    def kernel_modules(self) -> List[str]:
+        names = ["host", "sampling"]
+        for part in self._all_parts():
+            names += part.kernel_modules(self.rt.dtype)
+        return list(dict.fromkeys(names))
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        build.ensure(self.kernel_modules())
+        for part in self._all_parts():
+            part.bind(tensors, self.rt)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.rt.device)
+        self._bound = True
+
+    # ------------------------------------------------------------------ cache
+    def allocate_cache(self, config: CacheConfig) -> None:
+        max_len = config.max_model_len or self.plan.max_positions
+        if max_len > self.plan.max_positions:
+            raise ValueError(f"max_model_len {max_len} exceeds the model's {self.plan.max_positions} positions")
+        pages = list(config.pages_per_group) if config.pages_per_group else [config.num_pages] * len(self.group_windows)
+        if len(pages) != len(self.group_windows) or any(p <= 0 for p in pages):
+            raise ValueError(f"need a positive page count for each of {len(self.group_windows)} cache groups, got {pages}")
+        self.cache_config = CacheConfig(config.page_size, config.num_pages, config.max_requests, max_len, pages, config.fill_nan)
+        self.cache = CacheManager([GroupSpec(w, p) for w, p in zip(self.group_windows, pages)],
+                                  config.page_size, config.max_requests, max_len)
+        for i, run in enumerate(self.runs):
+            ctx = run.context
+            if run.need is not None and ctx.write_cache:
+                shape = (pages[ctx.group], 2, run.need.kv_heads, config.page_size, run.need.head_dim)
+                ctx.cache = torch.empty(shape, dtype=self.rt.dtype, device=self.rt.device)
+                if config.fill_nan:
+                    ctx.cache.view(torch.uint8).fill_(0xFF)   # all-ones bytes are NaN in both precisions
+            if run.state_need is not None:
+                ctx.state = torch.zeros((config.max_requests, *run.state_need.shape), dtype=run.state_need.dtype,
+                                        device=self.rt.device)
+        for i, run in enumerate(self.runs):
+            source = self.plan.schedule[i].kv_from
+            if source is not None:
+                run.context.cache = self.runs[source].context.cache
+
+    def cache_bytes_per_token(self) -> int:
+        element = 2 if self.rt.is_bf16 else 4
+        return sum(2 * r.need.kv_heads * r.need.head_dim * element for r in self.runs
+                   if r.need is not None and r.context.write_cache)
+
+    def open_request(self) -> int:
+        slot = self.cache.open()
+        for run in self.runs:
+            if run.context.state is not None:
+                run.context.state[slot].zero_()
+        return slot
+
+    def close_request(self, slot: int) -> None:
+        self.cache.close(slot)
+
+    # ------------------------------------------------------------------ the step
+    def _pinned_buffer(self, count: int) -> torch.Tensor:
+        if len(self._pinned) < 4:
+            self._pinned.append((torch.empty(max(count, 1 << 16), dtype=torch.int32, pin_memory=True), torch.cuda.Event()))
+            index = len(self._pinned) - 1
+        else:
+            index = self._pinned_next
+            self._pinned_next = (index + 1) % len(self._pinned)
+        buffer, event = self._pinned[index]
+        event.synchronize()
+        if buffer.numel() < count:
+            buffer = torch.empty(count * 2, dtype=torch.int32, pin_memory=True)
+            self._pinned[index] = (buffer, event)
+        self._pinned_current = index
+        return buffer
+
+    def _validate(self, entries: Sequence[StepEntry]):
+        if not self._bound or self.cache is None:
+            raise StepError("the model has no weights or no cache yet")
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        segments, row = [], 0
+        seen = set()
+        max_len = self.cache_config.max_model_len
+        for e in entries:
+            count = len(e.tokens)
+            if count == 0:
+                raise StepError(f"the entry of slot {e.slot} has no tokens")
+            if e.slot in seen:
+                raise StepError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            start = self.cache.length(e.slot)
+            if start + count > max_len:
+                raise StepError(f"slot {e.slot} would hold {start + count} tokens, the limit is {max_len}")
+            for w in e.want:
+                if not 0 <= w < count:
+                    raise StepError(f"slot {e.slot} wants logits at place {w} of {count} tokens")
+            segments.append(Segment(e.slot, start, count, row))
+            row += count
+        return segments, row
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs the entries' tokens as one batch from the cache and returns the float32
+        logits [wanted, vocab] in the order of the entries and of each entry's `want`
+        (None if nothing is wanted).  Raises `OutOfPages` before any device work if
+        the cache cannot hold the step."""
+        segments, rows = self._validate(entries)
+        n = len(segments)
+        vocab = self.plan.vocab_size
+        tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+        if tokens.min() < 0 or tokens.max() >= vocab:
+            raise StepError(f"a token id is outside the vocabulary of {vocab}")
+        want_rows = [s.row + w for s, e in zip(segments, entries) for w in e.want]
+        self.cache.prepare([s.slot for s in segments], [s.count for s in segments])
+        try:
+            max_context = max(s.start + s.count for s in segments)
+            columns = (max_context + self.cache_config.page_size - 1) // self.cache_config.page_size
+            n_groups = len(self.group_windows)
+            # One packed int32 buffer: ids | positions | segment_of_row | info[n,4] | slots | want | tables
+            sizes = [rows, rows, rows, 4 * n, n, len(want_rows)] + [n * columns] * n_groups
+            offsets = np.concatenate([[0], np.cumsum(sizes)])
+            host = self._pinned_buffer(int(offsets[-1]))
+            view = host.numpy()
+            view[offsets[0]:offsets[1]] = tokens
+            for i, s in enumerate(segments):
+                view[offsets[1] + s.row: offsets[1] + s.row + s.count] = np.arange(s.start, s.start + s.count)
+                view[offsets[2] + s.row: offsets[2] + s.row + s.count] = i
+                view[offsets[3] + 4 * i: offsets[3] + 4 * i + 4] = (s.row, s.count, s.start, s.slot)
+                view[offsets[4] + i] = s.slot
+            view[offsets[5]:offsets[6]] = want_rows
+            for g in range(n_groups):
+                table = host[offsets[6 + g]:offsets[7 + g]].view(n, columns)
+                self.cache.fill_table(g, [s.slot for s in segments], table, columns)
+            total = int(offsets[-1])
+            device = torch.empty(total, dtype=torch.int32, device=self.rt.device)
+            device.copy_(host[:total], non_blocking=True)
+            self._pinned[self._pinned_current][1].record()
+            part = lambda k: device[offsets[k]:offsets[k + 1]]
+            step = StepContext(
+                rt=self.rt, num_rows=rows, segments=segments, token_ids=part(0), positions=part(1),
+                segment_of_row=part(2), segment_info=part(3).view(n, 4), slots=part(4),
+                tables={g: part(6 + g).view(n, columns) for g in range(n_groups)},
+                page_size=self.cache_config.page_size, status=self.status,
+                max_count=max(s.count for s in segments), max_context=max_context,
+                all_single=all(s.count == 1 for s in segments))
+            logits = self._forward(step, part(5) if want_rows else None)
+        except BaseException:
+            self.cache.discard()
+            raise
+        self.cache.commit()
+        return logits
+
+    def _forward(self, step: StepContext, want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        h = self.embedding.forward(step)
+        for position in self.positions.values():
+            position.add_to_embedding(h, step)
+        pending = None
+        for run in self.runs:
+            pending = run.block.forward(h, pending, step, run.context)
+        if want_rows is None:
+            return None
+        x = self.final_norm.forward(h, pending, step, rows=want_rows)
+        return self.lm_head.forward(x, step)
+
+    def check_status(self) -> None:
+        """Reads the device status word (this waits for the device) and raises if a
+        kernel flagged a fault.  After a fault the model must not be used further."""
+        value = int(self.status.item())
+        if value:
+            raise DeviceFault(f"kernels reported status {value} (1 = index outside a table, 2 = page outside the pool, "
+                              f"4 = non-finite logits); the cache can no longer be trusted")

@@ -1,0 +1,125 @@
+"""The operations the parts are made of, each one a hand-written kernel launch.
+
+Shapes use M = rows of the step, H = model width.  The residual stream `h` is
+always float32; activations are float32 or bfloat16.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .native import call, expect, is_bf16, on_gpu, ptr, stream, KernelError
+
+
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    """out[r, :] = table[ids[r], :] as float32; an id outside the table zeroes the row
+    and sets a status bit."""
+    on_gpu(table, ids, out, status)
+    expect(ids, torch.int32, "token ids")
+    expect(out, torch.float32, "the residual stream")
+    rows, width = out.shape
+    call("elementwise", "mlr_embed_gather", ptr(out), ptr(table), is_bf16(table), ptr(ids), rows, width,
+         table.shape[0], ptr(status), stream())
+
+
+def rmsnorm(h: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+            write_back: bool = True) -> None:
+    """out[r] = rmsnorm(h[row] + delta[row]) * weight with row = rows[r] (or r).  With
+    `write_back` the sum is stored to h[row], which moves the residual stream on."""
+    on_gpu(h, weight, out, delta, rows)
+    expect(h, torch.float32, "the residual stream")
+    if delta is not None:
+        expect(delta, torch.float32, "the residual delta")
+        if delta.shape != h.shape:
+            raise KernelError("residual delta and residual stream differ in shape")
+    if rows is not None:
+        expect(rows, torch.int32, "row indices")
+    count = out.shape[0]
+    call("elementwise", "mlr_rmsnorm", ptr(h), ptr(delta), ptr(weight), is_bf16(weight), ptr(out), is_bf16(out),
+         ptr(rows), count, h.shape[1], float(eps), int(write_back), stream())
+
+
+def residual_add(h: torch.Tensor, delta: torch.Tensor) -> None:
+    on_gpu(h, delta)
+    expect(h, torch.float32, "the residual stream")
+    expect(delta, torch.float32, "the residual delta")
+    call("elementwise", "mlr_residual_add", ptr(h), ptr(delta), h.numel(), stream())
+
+
+def qk_norm_rope_cache(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int,
+                       q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                       cos_sin: Optional[torch.Tensor], positions: torch.Tensor, segment_of_row: torch.Tensor,
+                       block_table: Optional[torch.Tensor], page_size: int, cache: Optional[torch.Tensor],
+                       write_cache: bool, status: torch.Tensor) -> None:
+    """In place on qkv [M, (Hq + 2 Hkv) D]: per-head RMS norm of q and k, rotation by
+    the table row of each position, and the write of k and v into the layer's cache
+    [page, 2, Hkv, page_size, D]."""
+    on_gpu(qkv, q_weight, k_weight, cos_sin, positions, segment_of_row, block_table, cache, status)
+    expect(positions, torch.int32, "positions")
+    expect(segment_of_row, torch.int32, "segment_of_row")
+    if cos_sin is not None:
+        expect(cos_sin, torch.float32, "the rotation table")
+    if write_cache:
+        expect(block_table, torch.int32, "the block table")
+        if cache.dtype is not qkv.dtype:
+            raise KernelError(f"cache dtype {cache.dtype} differs from activation dtype {qkv.dtype}")
+    w_bf16 = is_bf16(q_weight) if q_weight is not None else 0
+    call("elementwise", "mlr_qk_norm_rope_cache", ptr(qkv), is_bf16(qkv), qkv.stride(0), qkv.shape[0], q_heads,
+         kv_heads, head_dim, ptr(q_weight), ptr(k_weight), w_bf16, float(eps), ptr(cos_sin),
+         cos_sin.shape[1] if cos_sin is not None else 0, cos_sin.shape[0] if cos_sin is not None else 0,
+         ptr(positions), ptr(segment_of_row), ptr(block_table),
+         block_table.stride(0) if block_table is not None else 0, page_size, ptr(cache),
+         cache.shape[0] if cache is not None else 0, int(write_cache), ptr(status), stream())
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+    on_gpu(gate_up, out)
+    if not gate_up.is_contiguous() or not out.is_contiguous() or gate_up.dtype is not out.dtype:
+        raise KernelError("swiglu wants contiguous tensors of one dtype")
+    call("elementwise", "mlr_swiglu", ptr(gate_up), ptr(out), is_bf16(out), out.shape[0], out.shape[1], stream())
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = a[M, K] @ w[N, K]^T in true float32 on the CUDA cores."""
+    on_gpu(a, w, out)
+    for t, what in ((a, "a"), (w, "w"), (out, "out")):
+        if t.dtype is not torch.float32 or t.stride(1) != 1:
+            raise KernelError(f"gemm_f32: {what} must be float32 with unit inner stride")
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"gemm_f32: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} do not fit")
+    call("gemm_f32", "mlr_gemm_f32", ptr(a), ptr(w), ptr(out), M, N, K, a.stride(0), w.stride(0), out.stride(0), stream())
+
+
+def attention_generic(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor,
+                      segment_of_row: torch.Tensor, block_table: torch.Tensor, page_size: int, q_heads: int,
+                      kv_heads: int, head_dim: int, window: int, scale: float, status: torch.Tensor) -> None:
+    """Causal (optionally windowed) attention of every row over its request's cache.
+    q is [M, >= Hq*D] (a view into the qkv buffer is fine), out is [M, Hq*D]."""
+    on_gpu(q, out, cache, positions, segment_of_row, block_table, status)
+    if q.dtype is not out.dtype or q.dtype is not cache.dtype:
+        raise KernelError("attention: q, out and cache must share one dtype")
+    if q.stride(1) != 1 or out.stride(1) != 1 or not cache.is_contiguous():
+        raise KernelError("attention: inner strides must be 1 and the cache contiguous")
+    call("attention_generic", "mlr_attention_generic", ptr(q), q.stride(0), ptr(out), out.stride(0), is_bf16(q),
+         ptr(cache), cache.shape[0], ptr(positions), ptr(segment_of_row), ptr(block_table), block_table.stride(0),
+         page_size, q.shape[0], q_heads, kv_heads, head_dim, int(window), float(scale), ptr(status), stream())
+
+
+def sample(logits: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
+           temperature: Optional[torch.Tensor] = None, uniform: Optional[torch.Tensor] = None) -> None:
+    """out[r] = greedy choice of logits[r] (temperature 0) or an inverse-CDF draw with
+    the row's uniform number."""
+    on_gpu(logits, out, status, temperature, uniform)
+    expect(out, torch.int32, "sampled ids")
+    if logits.dtype is not torch.float32 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be float32 rows")
+    if temperature is not None:
+        expect(temperature, torch.float32, "temperatures")
+        expect(uniform, torch.float64, "uniform numbers")
+    call("sampling", "mlr_sample", ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1],
+         ptr(temperature), ptr(uniform), ptr(out), ptr(status), stream())

@@ -1,0 +1,102 @@
+"""Thin typed wrappers over the kernel modules' C ABI.
+
+Each function checks that its tensors live on the GPU, are contiguous where the
+kernel assumes it and have the dtype it names, passes raw pointers and the current
+CUDA stream, and turns a non-zero return into `KernelError` with the module's own
+message.  Nothing here computes anything and nothing falls back to another
+implementation: without a GPU or without the compiled module the call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ..csrc import build
+
+c_int, c_float, c_void_p, c_longlong = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_SIGNATURES = {
+    "elementwise": {
+        "mlr_embed_gather": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+        "mlr_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+        "mlr_residual_add": [c_void_p, c_void_p, c_longlong, c_void_p],
+        "mlr_qk_norm_rope_cache": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                                   c_float, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                   c_void_p, c_int, c_int, c_void_p, c_void_p],
+        "mlr_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    },
+    "gemm_f32": {
+        "mlr_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    },
+    "attention_generic": {
+        "mlr_attention_generic": [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+    },
+    "sampling": {
+        "mlr_sample": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    },
+}
+
+_bound = {}
+
+
+def register_signatures(module: str, functions: dict) -> None:
+    """Lets a kernel module added later declare its functions."""
+    _SIGNATURES.setdefault(module, {}).update(functions)
+    _bound.pop(module, None)
+
+
+def module(name: str):
+    lib = _bound.get(name)
+    if lib is None:
+        lib = build.load(name)
+        for fn, argtypes in _SIGNATURES.get(name, {}).items():
+            f = getattr(lib, fn)
+            f.argtypes = argtypes
+            f.restype = c_int
+        lib.mlr_last_error.restype = ctypes.c_char_p
+        _bound[name] = lib
+    return lib
+
+
+def call(module_name: str, fn: str, *args) -> None:
+    lib = module(module_name)
+    if getattr(lib, fn)(*args) != 0:
+        raise KernelError(lib.mlr_last_error().decode("utf-8", "replace"))
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def on_gpu(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("a kernel of this package was given a tensor that is not on the GPU; "
+                              "there is no CPU path")
+
+
+def is_bf16(t: torch.Tensor) -> int:
+    if t.dtype is torch.bfloat16:
+        return 1
+    if t.dtype is torch.float32:
+        return 0
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def expect(t: torch.Tensor, dtype: torch.dtype, what: str) -> None:
+    if t.dtype is not dtype:
+        raise KernelError(f"{what} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise KernelError(f"{what} must be contiguous")

@@ -1,0 +1,86 @@
+"""Grouped-query causal attention with per-head q/k RMS norm and rotation, over the
+paged cache (src/minillm/runtime.cpp:250-319; src/minillm/cuda/layer.cpp:43-63).
+
+    qkv = x [Wq; Wk; Wv]^T                       one product on the stacked matrices
+    q_h, k_h <- rmsnorm over D, then rotate      (skipped when the spec names no norm / position)
+    cache[page(pos)] <- k, v                     unless this run reads another run's cache
+    o_h = softmax(q_h K^T * scale) V             keys [lo, pos], lo = 0 or pos - window + 1
+    delta = o Wo^T                               float32, added to the stream by the next norm
+
+Parameters: hidden_size, num_heads, num_kv_heads, head_dim, scale, window (None or
+n), qk_norm_eps (None = no q/k norm), position (name of a position encoding of the
+plan, or None).  Weights: "q" [Hq D, H], "k", "v" [Hkv D, H], "o" [H, Hq D],
+"q_norm", "k_norm" [D].
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config.registry import register_part
+from ..ops import functions as F
+from ..ops import attention as A
+from ..weights.loader import WeightSpec
+from .base import CacheNeed, Mixer, RunContext, StepContext
+
+
+class AttentionMixer(Mixer):
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = spec.params
+        self.width = int(p["hidden_size"])
+        self.heads = int(p["num_heads"])
+        self.kv_heads = int(p["num_kv_heads"])
+        self.head_dim = int(p["head_dim"])
+        self.scale = float(p["scale"])
+        self.window = p.get("window")
+        self.qk_norm_eps = p.get("qk_norm_eps")
+        self.position_name = p.get("position")
+        if self.heads % self.kv_heads:
+            raise ValueError(f"{self.heads} query heads cannot share {self.kv_heads} kv heads")
+        self.position = None       # set by the model from the plan's position encodings
+        self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed(self.window, self.kv_heads, self.head_dim)
+
+    def weight_specs(self) -> List[WeightSpec]:
+        w, D = self.spec.weights, self.head_dim
+        specs = [WeightSpec(w["q"], (self.heads * D, self.width)), WeightSpec(w["k"], (self.kv_heads * D, self.width)),
+                 WeightSpec(w["v"], (self.kv_heads * D, self.width)), WeightSpec(w["o"], (self.width, self.heads * D))]
+        if self.qk_norm_eps is not None:
+            specs += [WeightSpec(w["q_norm"], (D,), "vector", ("one_plus_normal", 0.01)),
+                      WeightSpec(w["k_norm"], (D,), "vector", ("one_plus_normal", 0.01))]
+        return specs
+
+    def kernel_modules(self, dtype) -> List[str]:
+        return ["elementwise"] + A.modules_for(dtype, self.head_dim) + (["gemm_f32"] if dtype is torch.float32 else [])
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
+        w = self.spec.weights
+        self.w_qkv = torch.cat([rt.matrix(tensors[w[r]]) for r in ("q", "k", "v")], dim=0).contiguous()
+        self.w_o = rt.matrix(tensors[w["o"]])
+        if self.qk_norm_eps is not None:
+            self.q_norm = rt.vector(tensors[w["q_norm"]])
+            self.k_norm = rt.vector(tensors[w["k_norm"]])
+            if self.q_norm.dtype is not self.k_norm.dtype:
+                self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
+
+    def forward(self, x: torch.Tensor, step: StepContext, run: RunContext) -> torch.Tensor:
+        rt = step.rt
+        D = self.head_dim
+        qkv = rt.linear(x, self.w_qkv)
+        table = step.tables[run.group]
+        rotation = self.position.rotation_table() if self.position is not None else None
+        F.qk_norm_rope_cache(qkv, self.heads, self.kv_heads, D, self.q_norm, self.k_norm,
+                             self.qk_norm_eps if self.qk_norm_eps is not None else 1.0, rotation,
+                             step.positions, step.segment_of_row, table, step.page_size, run.cache,
+                             run.write_cache, step.status)
+        out = rt.empty(x.shape[0], self.heads * D)
+        A.paged_attention(qkv, out, run.cache, table, step, self.heads, self.kv_heads, D,
+                          self.window or 0, self.scale, cache_group=run.group)
+        return rt.linear(out, self.w_o, out_dtype=torch.float32)
+
+
+register_part("mixer", "attention", AttentionMixer)

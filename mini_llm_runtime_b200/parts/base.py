@@ -1,0 +1,161 @@
+"""Interfaces of the parts a layer is put together from, and what a step hands them.
+
+A part is built from a `PartSpec` alone (its sizes and constants are the spec's
+parameters), declares the checkpoint tensors it needs, is bound to them once, and
+is then called once per step for all rows of the batch.  No part knows which model
+it is in, which layer it is, or what the other layers are.
+
+    Mixer          forward(x, step, run) -> delta      tokens exchange information
+    FeedForward    forward(x, step) -> delta           per-token
+    Norm           forward(h, delta, ...) -> x         also moves the residual stream on
+    PositionEncoding   rotation_table() / add_to_embedding(h, step)
+    Block          forward(h, pending, step, run) -> pending     arranges the above
+
+`x` is [M, width] in the activation dtype; `h` is the float32 residual stream;
+`delta` is a float32 [M, width] contribution that has not been added to `h` yet.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..config.base import PartSpec
+from ..weights.loader import WeightSpec
+
+
+# --------------------------------------------------------------------------- needs
+@dataclass(frozen=True)
+class CacheNeed:
+    """A mixer that keeps keys and values per token: how far back it reads
+    (`window` None = everything) and the page geometry of one layer."""
+    window: Optional[int]
+    kv_heads: int
+    head_dim: int
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """A mixer that keeps a state of fixed size per request (`shape` without the
+    request dimension).  A new request starts from zeros."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+# --------------------------------------------------------------------------- what a step carries
+@dataclass(frozen=True)
+class Segment:
+    """The rows one request contributes to a step: `count` consecutive tokens from
+    position `start`, at rows [row, row + count) of the batch."""
+    slot: int
+    start: int
+    count: int
+    row: int
+
+
+@dataclass
+class StepContext:
+    """Everything about a step that parts may read.  Device tensors are int32."""
+    rt: "object"                      # engine.runtime.Runtime
+    num_rows: int
+    segments: List[Segment]           # host copy, in batch order
+    token_ids: torch.Tensor           # [M]
+    positions: torch.Tensor           # [M]
+    segment_of_row: torch.Tensor      # [M] index into `segments`
+    segment_info: torch.Tensor        # [n_segments, 4]: first row, count, start position, slot
+    slots: torch.Tensor               # [n_segments] state slot of each segment
+    tables: Dict[int, torch.Tensor]   # cache group -> block table rows [n_segments, columns]
+    page_size: int
+    status: torch.Tensor              # [1] device status word
+    max_count: int = 0                # longest segment of the step
+    max_context: int = 0              # largest position + 1 of the step
+    all_single: bool = False          # every segment is one token (a pure decode step)
+    scratch: Dict[str, object] = field(default_factory=dict)   # per-step memo for kernels' plans
+
+
+@dataclass
+class RunContext:
+    """What one entry of the run order gives its mixer."""
+    group: Optional[int] = None           # cache group of this run's mixer
+    cache: Optional[torch.Tensor] = None  # [pages, 2, kv_heads, page_size, head_dim]
+    write_cache: bool = True              # False: the run reads a cache another run writes
+    state: Optional[torch.Tensor] = None  # [max_requests, *StateNeed.shape]
+
+
+# --------------------------------------------------------------------------- parts
+class Part:
+    category = ""
+
+    def __init__(self, spec: PartSpec):
+        self.spec = spec
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return []
+
+    def kernel_modules(self, dtype: torch.dtype) -> List[str]:
+        """Kernel modules this part launches in the given precision (built before the
+        first step)."""
+        return []
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
+        """Takes its tensors (CPU or device, stored precision) and keeps device copies
+        in the form its kernels want."""
+
+
+class Mixer(Part):
+    category = "mixer"
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        return None
+
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    def forward(self, x: torch.Tensor, step: StepContext, run: RunContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    category = "feed_forward"
+
+    def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Norm(Part):
+    category = "norm"
+
+    def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], step: StepContext,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Adds `delta` into `h` (if given), then returns norm(h) in the activation
+        dtype.  With `rows` only those rows are normed and returned (h is then left
+        as it is)."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    category = "position"
+
+    def rotation_table(self) -> Optional[torch.Tensor]:
+        """[max_positions, rotary_dim] float32, cos in the first half of a row and sin
+        in the second, for mixers that rotate q and k; None if this encoding does not
+        rotate."""
+        return None
+
+    def add_to_embedding(self, h: torch.Tensor, step: StepContext) -> None:
+        """Hook for encodings that act on the embedded tokens; default: nothing."""
+
+
+class Block(Part):
+    category = "block"
+
+    def __init__(self, spec: PartSpec, mixer: Mixer, feed_forward: FeedForward, norms: Dict[str, Norm]):
+        super().__init__(spec)
+        self.mixer, self.feed_forward, self.norms = mixer, feed_forward, norms
+
+    def forward(self, h: torch.Tensor, pending: Optional[torch.Tensor], step: StepContext,
+                run: RunContext) -> Optional[torch.Tensor]:
+        """Runs the layer on the residual stream `h` with a not yet added contribution
+        `pending`; returns the contribution it leaves pending."""
+        raise NotImplementedError

@@ -1,0 +1,23 @@
+"""Pre-norm residual block: `h += mixer(norm(h))`, then `h += feed_forward(norm(h))`
+(src/minillm/runtime.cpp:245-337; src/minillm/cuda/layer.cpp:42-70).
+
+Each residual add is folded into the norm that follows it: a sub-layer's output is
+handed on as `pending` and added to `h` by the next norm's kernel, so the residual
+stream is read and written once per sub-layer.  Norm slots: "pre_mixer",
+"pre_feed_forward".
+"""
+from __future__ import annotations
+
+from ..config.registry import register_part
+from .base import Block
+
+
+class PreNormBlock(Block):
+    def forward(self, h, pending, step, run):
+        x = self.norms["pre_mixer"].forward(h, pending, step)
+        mixed = self.mixer.forward(x, step, run)
+        x = self.norms["pre_feed_forward"].forward(h, mixed, step)
+        return self.feed_forward.forward(x, step)
+
+
+register_part("block", "pre_norm", PreNormBlock)
