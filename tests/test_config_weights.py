@@ -1,0 +1,195 @@
+"""Configuration, registry, safetensors and loader errors (no GPU)."""
+import json
+import os
+
+import pytest
+import torch
+
+import plain_qwen3
+import tiny_models
+from mini_llm_runtime_b200 import models as _models  # noqa: F401
+from mini_llm_runtime_b200.config.base import ConfigError, Run
+from mini_llm_runtime_b200.config.registry import config_from_dict, config_from_dir, known_architectures, plan_for
+from mini_llm_runtime_b200.engine.structure import expected_weights
+from mini_llm_runtime_b200.weights.loader import WeightMismatch, load_checkpoint
+from mini_llm_runtime_b200.weights.random_init import write_random_model
+from mini_llm_runtime_b200.weights.safetensors_io import SafetensorsFile, WeightFileError, write_safetensors
+
+
+@pytest.mark.parametrize("name", list(tiny_models.ALL))
+def test_config_reads_every_size(name):
+    raw = tiny_models.get(name)
+    cfg = config_from_dict(raw)
+    assert cfg.hidden_size == raw["hidden_size"] and cfg.num_hidden_layers == raw["num_hidden_layers"]
+    assert cfg.num_attention_heads == raw["num_attention_heads"] and cfg.num_key_value_heads == raw["num_key_value_heads"]
+    assert cfg.head_dim == raw["head_dim"] and cfg.intermediate_size == raw["intermediate_size"]
+    assert cfg.vocab_size == raw["vocab_size"] and cfg.rms_norm_eps == raw["rms_norm_eps"]
+    assert cfg.rope_theta == raw["rope_theta"] and cfg.tie_word_embeddings == raw["tie_word_embeddings"]
+    assert list(cfg.layer_windows) == plain_qwen3.layer_windows(raw)
+    assert config_from_dict(cfg.to_dict()) == cfg
+
+
+def test_head_dim_defaults_to_width_over_heads():
+    raw = tiny_models.get("tiny_a")
+    del raw["head_dim"]
+    assert config_from_dict(raw).head_dim == 16
+    raw["hidden_size"] = 66
+    with pytest.raises(ConfigError, match="not divisible"):
+        config_from_dict(raw)
+
+
+def test_layer_types_list_wins():
+    raw = tiny_models.get("tiny_c")
+    raw["layer_types"] = ["sliding_attention", "full_attention", "full_attention", "sliding_attention"]
+    assert config_from_dict(raw).layer_windows == (40, None, None, 40)
+
+
+@pytest.mark.parametrize("change, match", [
+    ({"architectures": ["LlamaForCausalLM"]}, "unknown architecture"),
+    ({"architectures": []}, "architectures"),
+    ({"hidden_size": None}, "lacks required key 'hidden_size'"),
+    ({"rms_norm_eps": None}, "rms_norm_eps"),
+    ({"rope_theta": None}, "rope_theta"),
+    ({"num_hidden_layers": 0}, "outside"),
+    ({"vocab_size": 2_000_000}, "outside"),
+    ({"num_key_value_heads": 3}, "not a multiple"),
+    ({"head_dim": 15}, "even"),
+    ({"rms_norm_eps": 0.0}, "finite and positive"),
+    ({"rope_theta": float("inf")}, "finite and positive"),
+    ({"rope_scaling": {"rope_type": "yarn", "factor": 4.0}}, "rope scaling"),
+    ({"attention_bias": True}, "attention_bias"),
+    ({"hidden_act": "gelu"}, "hidden_act"),
+    ({"eos_token_id": 999}, "outside the vocabulary"),
+])
+def test_config_errors(change, match):
+    raw = tiny_models.get("tiny_a")
+    for k, v in change.items():
+        if v is None:
+            raw.pop(k)
+        else:
+            raw[k] = v
+    with pytest.raises(ConfigError, match=match):
+        config_from_dict(raw)
+
+
+def test_registry_lists_known_names():
+    assert "Qwen3ForCausalLM" in known_architectures()
+    with pytest.raises(ConfigError, match="Qwen3ForCausalLM"):
+        config_from_dict({"architectures": ["Nope"]})
+
+
+def test_plan_is_data():
+    cfg = config_from_dict(tiny_models.get("tiny_c"))
+    plan = plan_for(cfg)
+    assert [r.layer for r in plan.schedule] == [0, 1, 2, 3] and all(r.kv_from is None for r in plan.schedule)
+    assert [l.mixer.params["window"] for l in plan.layers] == [None, 40, 40, 40]
+    assert plan.layers[0].mixer.params["head_dim"] == 48 and plan.layers[0].feed_forward.params["intermediate_size"] == 176
+    import dataclasses
+    bad = dataclasses.replace(plan, schedule=(Run(0), Run(1, kv_from=3)))
+    with pytest.raises(ConfigError, match="not an earlier run"):
+        bad.validate()
+
+
+def test_expected_weights_match_the_architecture():
+    for name in tiny_models.ALL:
+        raw = tiny_models.get(name)
+        specs = expected_weights(plan_for(config_from_dict(raw)))
+        assert {k: tuple(v.shape) for k, v in specs.items()} == plain_qwen3.tensor_names(raw)
+        assert ("lm_head.weight" in specs) == (not raw["tie_word_embeddings"])
+
+
+def test_safetensors_round_trip(tmp_path):
+    tensors = {"a": torch.randn(3, 5).to(torch.bfloat16), "b": torch.randn(7), "c": torch.arange(6, dtype=torch.int64).view(2, 3),
+               "d": torch.randn(2, 2).to(torch.float16)}
+    path = str(tmp_path / "x.safetensors")
+    write_safetensors(path, tensors, {"k": "v"})
+    f = SafetensorsFile(path)
+    assert sorted(f.names()) == ["a", "b", "c", "d"] and f.metadata == {"k": "v"}
+    for n, t in tensors.items():
+        assert f.dtype(n) == t.dtype and torch.equal(f.tensor(n), t)
+    # The same bytes are what the widely used container format defines.
+    from safetensors import safe_open
+    with safe_open(path, "pt") as g:
+        for n, t in tensors.items():
+            assert torch.equal(g.get_tensor(n), t)
+
+
+def test_safetensors_damage(tmp_path):
+    path = str(tmp_path / "x.safetensors")
+    write_safetensors(path, {"a": torch.zeros(4, 4)})
+    blob = open(path, "rb").read()
+    open(path, "wb").write(blob[:-8])
+    with pytest.raises(WeightFileError, match="does not fit"):
+        SafetensorsFile(path)
+    open(path, "wb").write(b"\x05")
+    with pytest.raises(WeightFileError, match="shorter"):
+        SafetensorsFile(path)
+    with pytest.raises(WeightFileError, match="neither"):
+        load_checkpoint(str(tmp_path / "nowhere"), {})
+
+
+def _folder(tmp_path, raw, weights):
+    os.makedirs(tmp_path, exist_ok=True)
+    json.dump(raw, open(os.path.join(tmp_path, "config.json"), "w"))
+    write_safetensors(os.path.join(tmp_path, "model.safetensors"), weights)
+    return str(tmp_path)
+
+
+def test_loader_lists_every_disagreement_at_once(tmp_path):
+    raw = tiny_models.get("tiny_b")
+    weights = plain_qwen3.random_weights(raw, 0)
+    del weights["model.layers.1.mlp.up_proj.weight"]
+    del weights["lm_head.weight"]
+    weights["model.layers.9.extra.weight"] = torch.zeros(2)
+    weights["model.layers.0.self_attn.q_norm.weight"] = torch.zeros(16, dtype=torch.bfloat16)
+    weights["model.layers.2.self_attn.k_proj.weight"] = torch.zeros(96, 95, dtype=torch.bfloat16)
+    folder = _folder(tmp_path, raw, weights)
+    specs = expected_weights(plan_for(config_from_dir(folder)))
+    with pytest.raises(WeightMismatch) as e:
+        load_checkpoint(folder, specs)
+    err = e.value
+    assert err.missing == ["lm_head.weight", "model.layers.1.mlp.up_proj.weight"]
+    assert err.unexpected == ["model.layers.9.extra.weight"]
+    assert [w[0] for w in err.wrong] == ["model.layers.0.self_attn.q_norm.weight", "model.layers.2.self_attn.k_proj.weight"]
+    text = str(err)
+    for needle in ("missing (2)", "unexpected (1)", "wrong shape (2)", "is [16], expected [32]"):
+        assert needle in text
+
+
+def test_loader_keeps_stored_precision(tmp_path):
+    raw = tiny_models.get("tiny_a")
+    weights = plain_qwen3.random_weights(raw, 0)
+    weights["model.norm.weight"] = weights["model.norm.weight"].float()
+    folder = _folder(tmp_path, raw, weights)
+    specs = expected_weights(plan_for(config_from_dir(folder)))
+    loaded = load_checkpoint(folder, specs)
+    assert loaded["model.norm.weight"].dtype is torch.float32
+    assert loaded["model.embed_tokens.weight"].dtype is torch.bfloat16
+    assert torch.equal(loaded["model.layers.1.mlp.down_proj.weight"], weights["model.layers.1.mlp.down_proj.weight"])
+
+
+def test_tied_head_with_extra_lm_head_is_unexpected(tmp_path):
+    raw = tiny_models.get("tiny_a")
+    weights = plain_qwen3.random_weights(raw, 0)
+    weights["lm_head.weight"] = weights["model.embed_tokens.weight"].clone()
+    folder = _folder(tmp_path, raw, weights)
+    with pytest.raises(WeightMismatch, match="unexpected .1.: lm_head.weight"):
+        load_checkpoint(folder, expected_weights(plan_for(config_from_dir(folder))))
+
+
+def test_random_weights_mode_writes_a_loadable_folder(tmp_path):
+    raw = tiny_models.get("tiny_c")
+    write_random_model(str(tmp_path / "m"), raw, seed=5)
+    write_random_model(str(tmp_path / "n"), raw, seed=5)
+    write_random_model(str(tmp_path / "o"), raw, seed=6)
+    cfg = config_from_dir(str(tmp_path / "m"))
+    specs = expected_weights(plan_for(cfg))
+    a, b, c = (load_checkpoint(str(tmp_path / d), specs) for d in "mno")
+    assert all(torch.equal(a[k], b[k]) for k in a) and not torch.equal(a["lm_head.weight"], c["lm_head.weight"])
+    assert a["lm_head.weight"].dtype is torch.bfloat16
+    assert abs(a["lm_head.weight"].float().std() - 0.02) < 2e-3
+    norm = a["model.layers.0.input_layernorm.weight"].float()
+    assert abs(norm.mean() - 1.0) < 0.01 and 0.003 < norm.std() < 0.03
+    # The plain implementation runs on what was written.
+    logits = plain_qwen3.forward(raw, a, [1, 2, 3])
+    assert logits.shape == (3, raw["vocab_size"]) and torch.isfinite(logits).all()
