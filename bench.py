@@ -1,0 +1,302 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200, one JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+The default run is the Qwen3-8B layer sizes (36 layers, width 4096, 32/8 heads of
+128, feed-forward 12288, vocabulary 151936, untied head) with seeded random weights
+in bfloat16, pages of 16 tokens, 8 requests each holding 8192 tokens of context.
+A step is one decode step of the whole batch.
+
+  value      decoded tokens per second, timed on the device with CUDA events around K
+             steps whose sampled tokens stay on the device
+  e2e        the same through the public entry point (Engine.submit / Engine.step):
+             token ids go host -> device from pinned memory and sampled ids come
+             device -> host every step
+  prefill    one request of 2048 tokens in one step: tokens/s, ms, and flops / time /
+             bf16 peak
+  roofline   bytes a decode step must read (every weight once plus the cache of the
+             live requests) / step time, against the HBM peak
+  points     decode tokens/s at batch 1 and 64 (same context), and at batch 1/8/64
+             with 2048 tokens of context
+
+Peaks come from MEASURED_PEAKS.json beside this file when it exists, else from the
+fallback figures of an earlier measurement on the same pool (6.65 TB/s, 1.59 PFLOP/s).
+Prompts are seeded uniform-random token ids; weights are random; no dataset is used.
+The timed steps read 15 GB of weights each, far more than the 126 MB L2, so no
+explicit L2 flush is needed between them.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_size": 4096, "num_hidden_layers": 36,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288,
+    "vocab_size": 151936, "max_position_embeddings": 40960, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+    "tie_word_embeddings": False, "use_sliding_window": False, "hidden_act": "silu", "attention_bias": False,
+    "torch_dtype": "bfloat16",
+}
+QUICK = dict(QWEN3_8B, hidden_size=512, num_hidden_layers=4, num_attention_heads=8, num_key_value_heads=2,
+             head_dim=64, intermediate_size=1024, vocab_size=4099, max_position_embeddings=4096)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    if os.path.exists(path):
+        try:
+            with open(path) as f:
+                data = json.load(f)
+            out["hbm_gbs"] = float(data.get("hbm_gbs", out["hbm_gbs"]))
+            out["bf16_tflops"] = float(data.get("bf16_tflops", out["bf16_tflops"]))
+            out["source"] = "measured"
+        except (OSError, ValueError):
+            pass
+    return out
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self, device_index: int = 0):
+        self.lines, self.proc, self.device_index = [], None, device_index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.device_index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        clocks, maxes, reasons = [], [], set()
+        for line in self.lines:
+            cells = [c.strip() for c in line.split(",")]
+            if len(cells) < 6:
+                continue
+            try:
+                clocks.append(int(cells[0]))
+                maxes.append(int(cells[1]))
+            except ValueError:
+                continue
+            for name, cell in zip(self.NAMES, cells[2:6]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        if not clocks:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        return {"sm_mhz": int(statistics.median(clocks)), "sm_max_mhz": max(maxes), "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+def reference_arm():
+    """The reference is a CMake C++ project that reads GGUF files through llama.cpp
+    sources it expects under third_party/ (absent from its tree) and has no Python
+    packaging; `pip install` of it fails at once, so there is nothing to run."""
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "lilong555/mini-llm-runtime has no Python package (pip: neither setup.py nor "
+                                     "pyproject.toml) and its CUDA runtime needs llama.cpp sources and a GGUF "
+                                     "checkpoint that are not in the offline tree"}))
+    return 0
+
+
+def matmul_params(cfg, layers):
+    H, D = cfg["hidden_size"], cfg["head_dim"]
+    per_layer = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * D * H + cfg["num_attention_heads"] * D * H \
+        + 3 * cfg["intermediate_size"] * H
+    return per_layer * layers, cfg["vocab_size"] * H
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
+    ap.add_argument("--quick", action="store_true", help="a small model, for checking this script")
+    ap.add_argument("--no-points", action="store_true")
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.impl == "reference":
+        return reference_arm()
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    from mini_llm_runtime_b200.engine.engine import Engine
+    from mini_llm_runtime_b200.engine.loading import random_model
+    from mini_llm_runtime_b200.engine.model import CacheConfig, StepEntry
+    from mini_llm_runtime_b200.ops import native
+    from mini_llm_runtime_b200.sampling.sampler import Sampler, SamplingParams
+
+    cfg = dict(QUICK if args.quick else QWEN3_8B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    layers = cfg["num_hidden_layers"]
+    context, page = args.context, 16
+    horizon = args.steps + args.warmup + 8
+    batches = [args.batch] if args.no_points else sorted({1, args.batch, 64})
+    max_batch = max(batches)
+    pages = max_batch * ((context + horizon + page - 1) // page + 1)
+    pk = peaks()
+
+    torch.manual_seed(0)
+    model = random_model(cfg, seed=2, dtype="bfloat16",
+                         cache=CacheConfig(page_size=page, num_pages=pages, max_requests=max_batch,
+                                           max_model_len=context + horizon + page, fill_nan=False))
+    gen = torch.Generator().manual_seed(1234)
+    prompt_of = lambda n: torch.randint(0, cfg["vocab_size"], (n,), generator=gen).tolist()
+    layer_params, head_params = matmul_params(cfg, layers)
+    weight_bytes = 2 * (layer_params + head_params)
+    kv_bytes_per_token = model.cache_bytes_per_token()
+
+    def timed(fn, reps):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(reps):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / reps
+
+    # ---------------------------------------------------------------- prefill of 2048 tokens
+    T = 2048 if not args.quick else 512
+    prompt = prompt_of(T)
+
+    def prefill_once():
+        slot = model.open_request()
+        model.step([StepEntry(slot, prompt, [T - 1])])
+        model.close_request(slot)
+
+    for _ in range(3):
+        prefill_once()
+    prefill_ms = timed(prefill_once, 5)
+    attn_flops = 4 * cfg["num_attention_heads"] * cfg["head_dim"] * (T * (T + 1) // 2) * layers
+    prefill_flops = 2 * T * layer_params + 2 * head_params + attn_flops
+    prefill = {"value": T / prefill_ms * 1e3, "tokens": T, "ms": prefill_ms,
+               "frac": prefill_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)}
+
+    # ---------------------------------------------------------------- decode, device-timed
+    sampler = Sampler(model.rt.device, model.status)
+
+    def fill(batch, ctx):
+        """Opens `batch` requests and prefills ctx-1 tokens each; returns slots and the
+        device tensor of their next tokens."""
+        slots = [model.open_request() for _ in range(batch)]
+        chunk = 2048
+        last = None
+        for slot in slots:
+            tokens = prompt_of(ctx - 1)
+            for pos in range(0, len(tokens), chunk):
+                part = tokens[pos:pos + chunk]
+                final = pos + chunk >= len(tokens)
+                last = model.step([StepEntry(slot, part, [len(part) - 1] if final else [])])
+        return slots
+
+    def decode_rate(batch, ctx, steps, warmup, with_clocks=False):
+        slots = fill(batch, ctx)
+        ids = torch.randint(0, cfg["vocab_size"], (batch,), generator=gen).tolist()
+
+        def one_step():
+            nonlocal ids
+            logits = model.step([StepEntry(s, [t], [0]) for s, t in zip(slots, ids)])
+            ids = sampler.sample(logits).tolist()
+
+        for _ in range(warmup):
+            one_step()
+        native.launch_count = 0
+        if with_clocks:
+            with ClockSampler() as clocks:
+                ms = timed(one_step, steps)
+            clock_summary = clocks.summary()
+        else:
+            ms, clock_summary = timed(one_step, steps), None
+        launches = native.launch_count
+        for s in slots:
+            model.close_request(s)
+        return batch / ms * 1e3, ms, launches, clock_summary
+
+    value, ms_per_step, launches, clocks = decode_rate(args.batch, context, args.steps, args.warmup, with_clocks=True)
+    step_bytes = weight_bytes + args.batch * (context + args.warmup + args.steps // 2) * kv_bytes_per_token
+    achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / pk["hbm_gbs"], "peaks": pk["source"]}
+
+    points = {}
+    if not args.no_points:
+        short = max(4, args.steps // 4)
+        for b in (1, 64):
+            if b != args.batch:
+                points[f"decode_b{b}"] = decode_rate(b, context, short, 3)[0]
+        for b in (1, 8, 64):
+            points[f"decode_b{b}_ctx2048"] = decode_rate(b, min(2048, context), short, 3)[0]
+
+    # ---------------------------------------------------------------- end to end through the engine
+    engine = Engine(model, max_batch_tokens=max(2048, args.batch), prefill_chunk=2048)
+    for _ in range(args.batch):
+        engine.submit(prompt_of(context - 1), SamplingParams(max_tokens=horizon, ignore_eos=True))
+    while any(r.prefill_remaining for r in engine.scheduler.active) or engine.scheduler.waiting:
+        engine.step()
+    for _ in range(args.warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        engine.step()
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    e2e = {"value": args.batch / e2e_ms * 1e3, "unit": "tokens/s", "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": model.last_h2d_bytes, "d2h_bytes_per_step": 4 * (args.batch + 1)}
+
+    config = {"model": "Qwen3-8B sizes, random weights (seed 2)" if not args.quick else "quick check model",
+              "layers": layers, "layers_of_model": full_layers, "hidden": cfg["hidden_size"],
+              "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+              "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": args.batch,
+              "seq_len": context, "context_len": context, "page_size": page, "prefill_tokens": T,
+              "parallelism": "single_gpu", "l2": "inputs>L2 (15 GB of weights per step), no flush",
+              "weight_gb": round(weight_bytes / 1e9, 2), "kv_kb_per_token": kv_bytes_per_token / 1024}
+    print(json.dumps({
+        "metric": "decode tok/s (Qwen3-8B sizes, batch 8, context 8192, bf16)", "value": value, "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": config, "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "prefill": prefill,
+        "roofline": roofline, "points": points}))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -107,6 +107,7 @@ class Model:
         self._pinned: List[Tuple[torch.Tensor, torch.cuda.Event]] = []
         self._pinned_next = 0
         self._bound = False
+        self.last_h2d_bytes = 0
 
     # ------------------------------------------------------------------ weights
     def _all_parts(self):
@@ -252,6 +253,7 @@ class Model:
             total = int(offsets[-1])
             device = torch.empty(total, dtype=torch.int32, device=self.rt.device)
             device.copy_(host[:total], non_blocking=True)
+            self.last_h2d_bytes = 4 * total
             self._pinned[self._pinned_current][1].record()
             part = lambda k: device[offsets[k]:offsets[k + 1]]
             step = StepContext(

@@ -45,6 +45,7 @@ _SIGNATURES = {
 }
 
 _bound = {}
+launch_count = 0   # kernel launches of this package since it was last reset (a measurement aid)
 
 
 def register_signatures(module: str, functions: dict) -> None:
@@ -67,6 +68,8 @@ def module(name: str):
 
 
 def call(module_name: str, fn: str, *args) -> None:
+    global launch_count
+    launch_count += 1
     lib = module(module_name)
     if getattr(lib, fn)(*args) != 0:
         raise KernelError(lib.mlr_last_error().decode("utf-8", "replace"))

@@ -113,7 +113,7 @@ def run_trace(model_dir: str, dtype: str, trace: List[dict], out_dir: str, vocab
     logits: Dict[Tuple[str, int], torch.Tensor] = {}
     position: Dict[str, int] = {}
     for step in trace:
-        wanted = [(e["id"], position.get(e["id"], 0) + w) for e in step["entries"] for w in e["want"]]
+        wanted = [(e["id"], position.get(e["id"], 0) + w) for e in step["entries"] for w in e.get("want", [])]
         for e in step["entries"]:
             position[e["id"]] = position.get(e["id"], 0) + len(e["tokens"])
         path = os.path.join(out_dir, f"{step['step']}.f32")
