@@ -1,0 +1,633 @@
+// bfloat16 attention over the paged cache on the tensor cores, for head sizes that are
+// multiples of 16 up to 256.  Two kernels share one set of building blocks:
+//
+//   decode_splitkv   for requests that bring few rows (tokens x query heads per kv head
+//                    <= 16: a decoded token, or a portion of two or three tokens).  One
+//                    block per (request, kv head, split of the keys); its four warps walk
+//                    disjoint keys of each 64-key tile with their own running softmax and
+//                    are merged at the end; splits are merged by `combine`.  The bytes of
+//                    the cache are what it is bound by.
+//   prefill          for prompt portions.  One block per (64 query rows, query head); its
+//                    four warps own 16 rows each and walk the keys up to the diagonal
+//                    (flash attention: running maximum and sum, no score matrix).
+//
+// Both read K and V tiles of 64 keys through the block table with 16-byte cp.async into
+// XOR-swizzled shared memory (three stages in flight), take fragments with ldmatrix, and
+// multiply with mma.sync m16n8k16 (bf16 in, float32 accumulate).  Scores, maxima, sums and
+// the output accumulators are float32.  Keys outside a row's [lo, position] are filled
+// with zeros in shared memory and masked in the scores, so unused or stale cache memory
+// cannot reach a result.
+//
+// Semantics are those of src/minillm/runtime.cpp:283-310 (scores scaled by `scale`,
+// softmax over t in [lo, position], weighted sum of V), with lo = 0 or
+// position - window + 1.  The reference computes them with three SIMT kernels and a
+// materialised score matrix (src/minillm/cuda/attention.cu:97-218).
+#include "common.cuh"
+
+namespace {
+
+constexpr int kTileKeys = 64;
+constexpr int kThreads = 128;
+constexpr int kStages = 3;
+constexpr float kLog2e = 1.4426950408889634f;
+
+// ---------------------------------------------------------------- PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// ---------------------------------------------------------------- shared-memory tiles
+// A tile is [64 keys][DMAX] bf16 with a row pitch of DMAX*2 bytes; the 16-byte chunk c of
+// row r lives at chunk position c ^ (r & 7), which spreads the 8 rows of an ldmatrix over
+// all banks.
+template <int DMAX>
+struct Tile {
+    static constexpr int kPitch = DMAX * 2;
+    static constexpr int kBytes = kTileKeys * kPitch;
+    __device__ static __forceinline__ uint32_t offset(int row, int chunk) {
+        return row * kPitch + ((chunk ^ (row & 7)) << 4);
+    }
+};
+
+struct CacheView {
+    const __nv_bfloat16* base;   // [page][2][kv_heads][page_size][head_dim]
+    const int* table;            // this request's block table row
+    int num_pages, page_size, kv_heads, head_dim, kv_head;
+};
+
+// Loads keys [tile_start, tile_start + 64) of K and V into one stage.  Keys outside
+// [first_key, last_key] are zero-filled.  Called by all threads of the block.
+template <int DMAX>
+__device__ __forceinline__ void load_tile(const CacheView& c, int tile_start, int first_key, int last_key,
+                                          uint32_t k_smem, uint32_t v_smem, int* bad_page) {
+    const int chunks = c.head_dim >> 3;
+    const size_t head_elems = static_cast<size_t>(c.page_size) * c.head_dim;
+    const size_t page_elems = head_elems * 2 * c.kv_heads;
+    const size_t value_shift = head_elems * c.kv_heads;
+    for (int idx = threadIdx.x; idx < kTileKeys * chunks; idx += kThreads) {
+        const int row = idx / chunks, chunk = idx - row * chunks;
+        const int key = tile_start + row;
+        const __nv_bfloat16* src = c.base;
+        int bytes = 0;
+        if (key >= first_key && key <= last_key) {
+            const int page = c.table[key / c.page_size];
+            if (page >= 0 && page < c.num_pages) {
+                src = c.base + page * page_elems + c.kv_head * head_elems +
+                      static_cast<size_t>(key % c.page_size) * c.head_dim + chunk * 8;
+                bytes = 16;
+            } else {
+                *bad_page = 1;
+            }
+        }
+        const uint32_t off = Tile<DMAX>::offset(row, chunk);
+        cp_async_16(k_smem + off, src, bytes);
+        cp_async_16(v_smem + off, bytes ? src + value_shift : src, bytes);
+    }
+}
+
+// One warp: S[16 rows x 16 keys] += Q[16 x D] K^T for keys [key0, key0+16) of a tile.
+template <int DMAX>
+__device__ __forceinline__ void qk_16keys(float (&s)[2][4], const uint32_t (&q)[DMAX / 16][4], uint32_t k_smem,
+                                          int key0, int dim_steps) {
+    const int lane = threadIdx.x & 31;
+    const int row = key0 + ((lane >> 4) << 3) + (lane & 7);
+    const int chunk_in_step = (lane >> 3) & 1;
+#pragma unroll
+    for (int kd = 0; kd < DMAX / 16; ++kd) {
+        if (kd < dim_steps) {
+            uint32_t b[4];
+            ldmatrix_x4(b, k_smem + Tile<DMAX>::offset(row, kd * 2 + chunk_in_step));
+            mma_bf16(s[0], q[kd], b[0], b[1]);
+            mma_bf16(s[1], q[kd], b[2], b[3]);
+        }
+    }
+}
+
+// One warp: O[16 rows x D] += P[16 x 16 keys] V for keys [key0, key0+16) of a tile.
+template <int DMAX>
+__device__ __forceinline__ void pv_16keys(float (&o)[DMAX / 8][4], const uint32_t (&p)[4], uint32_t v_smem,
+                                          int key0, int dim_steps) {
+    const int lane = threadIdx.x & 31;
+    const int row = key0 + (((lane >> 3) & 1) << 3) + (lane & 7);
+    const int chunk_in_pair = lane >> 4;
+#pragma unroll
+    for (int dn = 0; dn < DMAX / 16; ++dn) {
+        if (dn < dim_steps) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, v_smem + Tile<DMAX>::offset(row, dn * 2 + chunk_in_pair));
+            mma_bf16(o[dn * 2], p, b[0], b[1]);
+            mma_bf16(o[dn * 2 + 1], p, b[2], b[3]);
+        }
+    }
+}
+
+// Q fragments of 16 rows from global memory.  row_ptr0 / row_ptr1 point at the head's D
+// values of the thread's two rows (lane/4 and lane/4 + 8), or are null for absent rows.
+template <int DMAX>
+__device__ __forceinline__ void load_q(uint32_t (&q)[DMAX / 16][4], const __nv_bfloat16* row_ptr0,
+                                       const __nv_bfloat16* row_ptr1, int dim_steps) {
+    const int t = threadIdx.x & 3;
+#pragma unroll
+    for (int kd = 0; kd < DMAX / 16; ++kd) {
+        q[kd][0] = q[kd][1] = q[kd][2] = q[kd][3] = 0u;
+        if (kd < dim_steps) {
+            const int col = kd * 16 + 2 * t;
+            if (row_ptr0) {
+                q[kd][0] = *reinterpret_cast<const uint32_t*>(row_ptr0 + col);
+                q[kd][2] = *reinterpret_cast<const uint32_t*>(row_ptr0 + col + 8);
+            }
+            if (row_ptr1) {
+                q[kd][1] = *reinterpret_cast<const uint32_t*>(row_ptr1 + col);
+                q[kd][3] = *reinterpret_cast<const uint32_t*>(row_ptr1 + col + 8);
+            }
+        }
+    }
+}
+
+// Running softmax state of the two rows a thread owns.
+struct RowState {
+    float m[2] = {-INFINITY, -INFINITY};
+    float l[2] = {0.0f, 0.0f};
+};
+
+// Scales and masks the scores of `NT` n8-tiles (keys key_base + 8*nt + 2*t + {0,1}),
+// updates the running maxima, turns scores into probabilities, rescales O, and packs P
+// into A fragments (one per 16 keys).
+template <int DMAX, int NT>
+__device__ __forceinline__ void softmax_step(float (&s)[NT][4], RowState& st, float (&o)[DMAX / 8][4],
+                                             uint32_t (&p)[NT / 2][4], int key_base, const int (&lo)[2],
+                                             const int (&hi)[2], float scale_log2, bool need_mask) {
+    const int t = threadIdx.x & 3;
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int r = j >> 1;
+            float v = s[nt][j] * scale_log2;
+            if (need_mask) {
+                const int key = key_base + nt * 8 + 2 * t + (j & 1);
+                if (key < lo[r] || key > hi[r]) v = -INFINITY;
+            }
+            s[nt][j] = v;
+            tile_max[r] = fmaxf(tile_max[r], v);
+        }
+    }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+        const float m_new = fmaxf(st.m[r], tile_max[r]);
+        m_use[r] = m_new == -INFINITY ? 0.0f : m_new;
+        alpha[r] = exp2f(st.m[r] - m_use[r]);
+        st.m[r] = m_new;
+        st.l[r] *= alpha[r];
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int r = j >> 1;
+            const float e = exp2f(s[nt][j] - m_use[r]);
+            s[nt][j] = e;
+            st.l[r] += e;
+        }
+    }
+#pragma unroll
+    for (int dn = 0; dn < DMAX / 8; ++dn) {
+        o[dn][0] *= alpha[0];
+        o[dn][1] *= alpha[0];
+        o[dn][2] *= alpha[1];
+        o[dn][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int kk = 0; kk < NT / 2; ++kk) {
+        p[kk][0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        p[kk][1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        p[kk][2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        p[kk][3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+    }
+}
+
+// How the keys of a decode item are cut: splits of `chunk` keys from `base` (a multiple of 64).
+struct SplitPlan {
+    int base, first_key, last_key, splits;
+};
+__device__ __forceinline__ SplitPlan plan_splits(int start, int count, int window, int chunk) {
+    SplitPlan p;
+    p.last_key = start + count - 1;
+    p.first_key = window > 0 ? max(0, start - window + 1) : 0;
+    p.base = (p.first_key / kTileKeys) * kTileKeys;
+    p.splits = (p.last_key + 1 - p.base + chunk - 1) / chunk;
+    return p;
+}
+
+// ---------------------------------------------------------------- decode: split-KV
+// grid = (max_splits, kv_heads, items).  Row r of the block's 16 rows is token r / group,
+// query head kv_head * group + r % group.  Partial results go to `partial`
+// [item][kv_head][split][16 rows][head_dim + 2] (the last two floats: maximum in log2
+// units and sum); an item whose keys fit one split is written to `out` directly.
+template <int DMAX>
+__global__ void __launch_bounds__(kThreads) decode_splitkv_kernel(
+    const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat16* __restrict__ out, int ldo,
+    const __nv_bfloat16* __restrict__ cache, int num_pages, const int* __restrict__ items,
+    const int* __restrict__ segment_info, const int* __restrict__ block_table, int table_stride,
+    int page_size, int q_heads, int kv_heads, int head_dim, int window, float scale, int chunk,
+    int max_splits, float* __restrict__ partial, int* status) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ int bad_page;
+    const int item = blockIdx.z, kv_head = blockIdx.y, split = blockIdx.x;
+    const int segment = items ? items[item] : item;
+    const int first_row = segment_info[segment * 4 + 0], count = segment_info[segment * 4 + 1];
+    const int start = segment_info[segment * 4 + 2];
+    const SplitPlan plan = plan_splits(start, count, window, chunk);
+    if (split >= plan.splits) return;
+    const int group = q_heads / kv_heads;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int dim_steps = head_dim >> 4;
+    if (threadIdx.x == 0) bad_page = 0;
+
+    const int key_begin = plan.base + split * chunk;
+    const int key_end = min(key_begin + chunk, plan.last_key + 1);      // exclusive
+    const int tiles = (key_end - key_begin + kTileKeys - 1) / kTileKeys;
+
+    CacheView view{cache, block_table + static_cast<size_t>(segment) * table_stride, num_pages, page_size,
+                   kv_heads, head_dim, kv_head};
+    const uint32_t smem_base = smem_u32(smem);
+    auto k_stage = [&](int s) { return smem_base + s * 2 * Tile<DMAX>::kBytes; };
+    auto v_stage = [&](int s) { return smem_base + s * 2 * Tile<DMAX>::kBytes + Tile<DMAX>::kBytes; };
+
+    // Rows of this thread: g and g + 8.
+    int lo[2], hi[2];
+    const __nv_bfloat16* qptr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = g + 8 * r;
+        const int token = row / group, head = kv_head * group + row % group;
+        const bool valid = token < count;
+        hi[r] = valid ? start + token : -1;
+        lo[r] = valid ? (window > 0 ? max(0, start + token - window + 1) : 0) : 0;
+        qptr[r] = valid ? q + static_cast<size_t>(first_row + token) * ldq + static_cast<size_t>(head) * head_dim : nullptr;
+    }
+    uint32_t qf[DMAX / 16][4];
+    load_q<DMAX>(qf, qptr[0], qptr[1], dim_steps);
+
+    float o[DMAX / 8][4];
+#pragma unroll
+    for (int dn = 0; dn < DMAX / 8; ++dn) o[dn][0] = o[dn][1] = o[dn][2] = o[dn][3] = 0.0f;
+    RowState st;
+    const float scale_log2 = scale * kLog2e;
+    __syncthreads();
+
+#pragma unroll
+    for (int s = 0; s < kStages - 1; ++s) {
+        if (s < tiles) load_tile<DMAX>(view, key_begin + s * kTileKeys, plan.first_key, key_end - 1, k_stage(s), v_stage(s), &bad_page);
+        cp_async_commit();
+    }
+    for (int it = 0; it < tiles; ++it) {
+        cp_async_wait<kStages - 2>();
+        __syncthreads();
+        const int next = it + kStages - 1;
+        if (next < tiles)
+            load_tile<DMAX>(view, key_begin + next * kTileKeys, plan.first_key, key_end - 1, k_stage(next % kStages),
+                            v_stage(next % kStages), &bad_page);
+        cp_async_commit();
+        const int stage = it % kStages;
+        const int key_base = key_begin + it * kTileKeys + warp * 16;
+        if (key_base < key_end) {
+            float s[2][4] = {};
+            qk_16keys<DMAX>(s, qf, k_stage(stage), warp * 16, dim_steps);
+            uint32_t p[1][4];
+            softmax_step<DMAX, 2>(s, st, o, p, key_base, lo, hi, scale_log2, true);
+            pv_16keys<DMAX>(o, p[0], v_stage(stage), warp * 16, dim_steps);
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // Merge the four warps through shared memory (the tile stages are free now).
+    float* merge_o = reinterpret_cast<float*>(smem);                       // [4][16][DMAX]
+    float* merge_ml = merge_o + 4 * 16 * DMAX;                             // [4][16][2]
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+    }
+#pragma unroll
+    for (int dn = 0; dn < DMAX / 8; ++dn) {
+        if (dn * 8 < head_dim) {
+            float* row0 = merge_o + (warp * 16 + g) * DMAX + dn * 8 + 2 * t;
+            float* row1 = merge_o + (warp * 16 + g + 8) * DMAX + dn * 8 + 2 * t;
+            row0[0] = o[dn][0];
+            row0[1] = o[dn][1];
+            row1[0] = o[dn][2];
+            row1[1] = o[dn][3];
+        }
+    }
+    if (t == 0) {
+        merge_ml[(warp * 16 + g) * 2 + 0] = st.m[0];
+        merge_ml[(warp * 16 + g) * 2 + 1] = st.l[0];
+        merge_ml[(warp * 16 + g + 8) * 2 + 0] = st.m[1];
+        merge_ml[(warp * 16 + g + 8) * 2 + 1] = st.l[1];
+    }
+    __syncthreads();
+    if (bad_page && threadIdx.x == 0 && status) atomicOr(status, MLR_STATUS_BAD_PAGE);
+    const int rows = count * group;
+    const bool direct = plan.splits == 1;
+    float* part = partial + ((static_cast<size_t>(item) * kv_heads + kv_head) * max_splits + split) * 16 * (head_dim + 2);
+    for (int idx = threadIdx.x; idx < rows * head_dim; idx += kThreads) {
+        const int row = idx / head_dim, d = idx - row * head_dim;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, merge_ml[(w * 16 + row) * 2]);
+        float l = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = merge_ml[(w * 16 + row) * 2];
+            const float f = mw == -INFINITY ? 0.0f : exp2f(mw - m);
+            l += merge_ml[(w * 16 + row) * 2 + 1] * f;
+            acc += merge_o[(w * 16 + row) * DMAX + d] * f;
+        }
+        if (direct) {
+            const int token = row / group, head = kv_head * group + row % group;
+            out[static_cast<size_t>(first_row + token) * ldo + static_cast<size_t>(head) * head_dim + d] =
+                __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+        } else {
+            part[row * (head_dim + 2) + d] = acc;
+            if (d == 0) {
+                part[row * (head_dim + 2) + head_dim] = m;
+                part[row * (head_dim + 2) + head_dim + 1] = l;
+            }
+        }
+    }
+}
+
+// grid = (items, kv_heads).  Adds up the splits of an item in split order.
+__global__ void __launch_bounds__(kThreads) combine_kernel(
+    __nv_bfloat16* __restrict__ out, int ldo, const int* __restrict__ items, const int* __restrict__ segment_info,
+    int q_heads, int kv_heads, int head_dim, int window, int chunk, int max_splits, const float* __restrict__ partial) {
+    const int item = blockIdx.x, kv_head = blockIdx.y;
+    const int segment = items ? items[item] : item;
+    const int first_row = segment_info[segment * 4 + 0], count = segment_info[segment * 4 + 1];
+    const int start = segment_info[segment * 4 + 2];
+    const SplitPlan plan = plan_splits(start, count, window, chunk);
+    if (plan.splits <= 1) return;
+    const int group = q_heads / kv_heads;
+    const int stride = head_dim + 2;
+    const float* base = partial + (static_cast<size_t>(item) * kv_heads + kv_head) * max_splits * 16 * stride;
+    for (int idx = threadIdx.x; idx < count * group * head_dim; idx += kThreads) {
+        const int row = idx / head_dim, d = idx - row * head_dim;
+        float m = -INFINITY;
+        for (int s = 0; s < plan.splits; ++s) m = fmaxf(m, base[(s * 16 + row) * stride + head_dim]);
+        float l = 0.0f, acc = 0.0f;
+        for (int s = 0; s < plan.splits; ++s) {
+            const float* p = base + (s * 16 + row) * stride;
+            const float f = p[head_dim] == -INFINITY ? 0.0f : exp2f(p[head_dim] - m);
+            l += p[head_dim + 1] * f;
+            acc += p[d] * f;
+        }
+        const int token = row / group, head = kv_head * group + row % group;
+        out[static_cast<size_t>(first_row + token) * ldo + static_cast<size_t>(head) * head_dim + d] =
+            __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+    }
+}
+
+// ---------------------------------------------------------------- prefill: flash attention
+// grid = (tiles, q_heads).  tiles[i] = {segment, first token of the 64-row tile within the
+// segment}.  Warp w owns rows 16w .. 16w+15 of the tile.
+template <int DMAX>
+__global__ void __launch_bounds__(kThreads) prefill_kernel(
+    const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat16* __restrict__ out, int ldo,
+    const __nv_bfloat16* __restrict__ cache, int num_pages, const int* __restrict__ tiles,
+    const int* __restrict__ segment_info, const int* __restrict__ block_table, int table_stride,
+    int page_size, int q_heads, int kv_heads, int head_dim, int window, float scale, int* status) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ int bad_page;
+    const int head = blockIdx.y;
+    const int segment = tiles[blockIdx.x * 2], tile_token = tiles[blockIdx.x * 2 + 1];
+    const int first_row = segment_info[segment * 4 + 0], count = segment_info[segment * 4 + 1];
+    const int start = segment_info[segment * 4 + 2];
+    const int kv_head = head / (q_heads / kv_heads);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int dim_steps = head_dim >> 4;
+    if (threadIdx.x == 0) bad_page = 0;
+
+    const int tile_rows = min(kTileKeys, count - tile_token);
+    const int first_pos = start + tile_token, last_pos = first_pos + tile_rows - 1;
+    const int first_key = window > 0 ? max(0, first_pos - window + 1) : 0;
+    const int key_begin = (first_key / kTileKeys) * kTileKeys;
+    const int n_tiles = (last_pos + 1 - key_begin + kTileKeys - 1) / kTileKeys;
+
+    CacheView view{cache, block_table + static_cast<size_t>(segment) * table_stride, num_pages, page_size,
+                   kv_heads, head_dim, kv_head};
+    const uint32_t smem_base = smem_u32(smem);
+    auto k_stage = [&](int s) { return smem_base + s * 2 * Tile<DMAX>::kBytes; };
+    auto v_stage = [&](int s) { return smem_base + s * 2 * Tile<DMAX>::kBytes + Tile<DMAX>::kBytes; };
+
+    int lo[2], hi[2];
+    const __nv_bfloat16* qptr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = warp * 16 + g + 8 * r;
+        const bool valid = row < tile_rows;
+        hi[r] = valid ? first_pos + row : -1;
+        lo[r] = valid ? (window > 0 ? max(0, first_pos + row - window + 1) : 0) : 0;
+        qptr[r] = valid ? q + static_cast<size_t>(first_row + tile_token + row) * ldq + static_cast<size_t>(head) * head_dim
+                        : nullptr;
+    }
+    uint32_t qf[DMAX / 16][4];
+    load_q<DMAX>(qf, qptr[0], qptr[1], dim_steps);
+    float o[DMAX / 8][4];
+#pragma unroll
+    for (int dn = 0; dn < DMAX / 8; ++dn) o[dn][0] = o[dn][1] = o[dn][2] = o[dn][3] = 0.0f;
+    RowState st;
+    const float scale_log2 = scale * kLog2e;
+    // Rows of this warp: their lowest lower bound and highest position decide which key
+    // tiles the warp can skip and which need no mask at all.
+    const int warp_first = first_pos + warp * 16, warp_last = min(last_pos, warp_first + 15);
+    const int warp_lo_min = window > 0 ? max(0, warp_first - window + 1) : 0;
+    const int warp_lo_max = window > 0 ? max(0, warp_last - window + 1) : 0;
+    const bool warp_active = warp * 16 < tile_rows;
+    __syncthreads();
+
+#pragma unroll
+    for (int s = 0; s < kStages - 1; ++s) {
+        if (s < n_tiles) load_tile<DMAX>(view, key_begin + s * kTileKeys, first_key, last_pos, k_stage(s), v_stage(s), &bad_page);
+        cp_async_commit();
+    }
+    for (int it = 0; it < n_tiles; ++it) {
+        cp_async_wait<kStages - 2>();
+        __syncthreads();
+        const int next = it + kStages - 1;
+        if (next < n_tiles)
+            load_tile<DMAX>(view, key_begin + next * kTileKeys, first_key, last_pos, k_stage(next % kStages),
+                            v_stage(next % kStages), &bad_page);
+        cp_async_commit();
+        const int stage = it % kStages;
+        const int key0 = key_begin + it * kTileKeys;
+        if (warp_active && key0 <= warp_last && key0 + kTileKeys - 1 >= warp_lo_min) {
+            float s[8][4] = {};
+#pragma unroll
+            for (int nb = 0; nb < 4; ++nb) {
+                float pair[2][4] = {};
+                qk_16keys<DMAX>(pair, qf, k_stage(stage), nb * 16, dim_steps);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    s[nb * 2][j] = pair[0][j];
+                    s[nb * 2 + 1][j] = pair[1][j];
+                }
+            }
+            const bool need_mask = key0 + kTileKeys - 1 > warp_first || key0 < warp_lo_max;
+            uint32_t p[4][4];
+            softmax_step<DMAX, 8>(s, st, o, p, key0, lo, hi, scale_log2, need_mask);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) pv_16keys<DMAX>(o, p[kk], v_stage(stage), kk * 16, dim_steps);
+        }
+    }
+    cp_async_wait<0>();
+    if (bad_page && threadIdx.x == 0 && status) atomicOr(status, MLR_STATUS_BAD_PAGE);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = warp * 16 + g + 8 * r;
+        if (row >= tile_rows) continue;
+        const float inv = st.l[r] > 0.0f ? 1.0f / st.l[r] : 0.0f;
+        __nv_bfloat16* dst = out + static_cast<size_t>(first_row + tile_token + row) * ldo + static_cast<size_t>(head) * head_dim;
+#pragma unroll
+        for (int dn = 0; dn < DMAX / 8; ++dn) {
+            if (dn * 8 < head_dim)
+                *reinterpret_cast<uint32_t*>(dst + dn * 8 + 2 * t) = pack_bf16(o[dn][2 * r] * inv, o[dn][2 * r + 1] * inv);
+        }
+    }
+}
+
+template <int DMAX>
+constexpr size_t tile_smem() {
+    return static_cast<size_t>(kStages) * 2 * Tile<DMAX>::kBytes;
+}
+
+template <typename Kernel>
+int allow_smem(Kernel kernel, size_t bytes, const char* what) {
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+    if (e != cudaSuccess) return mlr_fail("%s: cannot use %zu bytes of shared memory: %s", what, bytes, cudaGetErrorString(e));
+    return 0;
+}
+
+int check_common(const char* what, int q_heads, int kv_heads, int head_dim, int page_size, int num_pages, int window,
+                 int ldq, int ldo) {
+    MLR_REQUIRE(q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0, "%s: %d query heads cannot share %d kv heads", what, q_heads, kv_heads);
+    MLR_REQUIRE(head_dim >= 16 && head_dim <= 256 && head_dim % 16 == 0,
+                "%s: head size %d is not a multiple of 16 in [16, 256]", what, head_dim);
+    MLR_REQUIRE(page_size > 0 && num_pages > 0 && window >= 0, "%s: bad page size, page count or window", what);
+    MLR_REQUIRE(ldq >= q_heads * head_dim && ldo >= q_heads * head_dim && ldq % 2 == 0 && ldo % 2 == 0,
+                "%s: a row stride is smaller than the row or odd", what);
+    MLR_REQUIRE(kv_heads <= 65535 && q_heads <= 65535, "%s: more than 65535 heads", what);
+    return 0;
+}
+
+}  // namespace
+
+// Floats of scratch the decode kernel needs for `items` requests cut into `max_splits`.
+MLR_API long long mlr_attention_decode_scratch_floats(int items, int kv_heads, int head_dim, int max_splits) {
+    return static_cast<long long>(items) * kv_heads * max_splits * 16 * (head_dim + 2);
+}
+
+// items: segment indices (null = segments 0..n_items-1).  Every item must have
+// count * (q_heads / kv_heads) <= 16 rows.  chunk: keys per split, a multiple of 64.
+// max_splits: the most splits any item needs (the grid's x extent).  partial: scratch of
+// mlr_attention_decode_scratch_floats floats (may be null when max_splits == 1).
+MLR_API int mlr_attention_decode_bf16(const void* q, int ldq, void* out, int ldo, const void* cache, int num_pages,
+                                      const int* items, int n_items, const int* segment_info,
+                                      const int* block_table, int table_stride, int page_size, int q_heads,
+                                      int kv_heads, int head_dim, int window, float scale, int chunk,
+                                      int max_splits, float* partial, int* status, cudaStream_t stream) {
+    if (int e = check_common("attention_decode_bf16", q_heads, kv_heads, head_dim, page_size, num_pages, window, ldq, ldo)) return e;
+    MLR_REQUIRE(q_heads / kv_heads <= 16, "attention_decode_bf16: %d query heads per kv head exceed the 16 rows of a block", q_heads / kv_heads);
+    MLR_REQUIRE(chunk > 0 && chunk % kTileKeys == 0, "attention_decode_bf16: chunk %d is not a positive multiple of %d", chunk, kTileKeys);
+    MLR_REQUIRE(max_splits >= 1 && max_splits <= 65535 && (max_splits == 1 || partial), "attention_decode_bf16: bad split count or missing scratch");
+    MLR_REQUIRE(n_items >= 0 && n_items <= 65535, "attention_decode_bf16: more than 65535 requests in one launch");
+    if (n_items == 0) return 0;
+    const dim3 grid(max_splits, kv_heads, n_items);
+    const dim3 combine_grid(n_items, kv_heads);
+#define MLR_LAUNCH(DMAX)                                                                                           \
+    do {                                                                                                           \
+        const size_t merge = sizeof(float) * (4 * 16 * DMAX + 4 * 16 * 2);                                         \
+        const size_t bytes = tile_smem<DMAX>() > merge ? tile_smem<DMAX>() : merge;                                \
+        if (int e = allow_smem(decode_splitkv_kernel<DMAX>, bytes, "attention_decode_bf16")) return e;            \
+        decode_splitkv_kernel<DMAX><<<grid, kThreads, bytes, stream>>>(                                            \
+            static_cast<const __nv_bfloat16*>(q), ldq, static_cast<__nv_bfloat16*>(out), ldo,                      \
+            static_cast<const __nv_bfloat16*>(cache), num_pages, items, segment_info, block_table, table_stride,   \
+            page_size, q_heads, kv_heads, head_dim, window, scale, chunk, max_splits, partial, status);            \
+    } while (0)
+    if (head_dim <= 64) MLR_LAUNCH(64);
+    else if (head_dim <= 128) MLR_LAUNCH(128);
+    else MLR_LAUNCH(256);
+#undef MLR_LAUNCH
+    if (int e = mlr_launched("attention_decode_bf16")) return e;
+    if (max_splits > 1) {
+        combine_kernel<<<combine_grid, kThreads, 0, stream>>>(static_cast<__nv_bfloat16*>(out), ldo, items, segment_info,
+                                                             q_heads, kv_heads, head_dim, window, chunk, max_splits, partial);
+        return mlr_launched("attention_decode_bf16 combine");
+    }
+    return 0;
+}
+
+// tiles: n_tiles pairs {segment, first token of a 64-row tile of that segment}.
+MLR_API int mlr_attention_prefill_bf16(const void* q, int ldq, void* out, int ldo, const void* cache, int num_pages,
+                                       const int* tiles, int n_tiles, const int* segment_info,
+                                       const int* block_table, int table_stride, int page_size, int q_heads,
+                                       int kv_heads, int head_dim, int window, float scale, int* status,
+                                       cudaStream_t stream) {
+    if (int e = check_common("attention_prefill_bf16", q_heads, kv_heads, head_dim, page_size, num_pages, window, ldq, ldo)) return e;
+    MLR_REQUIRE(n_tiles >= 0, "attention_prefill_bf16: negative tile count");
+    if (n_tiles == 0) return 0;
+    const dim3 grid(n_tiles, q_heads);
+#define MLR_LAUNCH(DMAX)                                                                                          \
+    do {                                                                                                          \
+        if (int e = allow_smem(prefill_kernel<DMAX>, tile_smem<DMAX>(), "attention_prefill_bf16")) return e;     \
+        prefill_kernel<DMAX><<<grid, kThreads, tile_smem<DMAX>(), stream>>>(                                      \
+            static_cast<const __nv_bfloat16*>(q), ldq, static_cast<__nv_bfloat16*>(out), ldo,                     \
+            static_cast<const __nv_bfloat16*>(cache), num_pages, tiles, segment_info, block_table, table_stride,  \
+            page_size, q_heads, kv_heads, head_dim, window, scale, status);                                       \
+    } while (0)
+    if (head_dim <= 64) MLR_LAUNCH(64);
+    else if (head_dim <= 128) MLR_LAUNCH(128);
+    else MLR_LAUNCH(256);
+#undef MLR_LAUNCH
+    return mlr_launched("attention_prefill_bf16");
+}

@@ -1,23 +1,100 @@
-"""Chooses the attention kernel for a step.
+"""Chooses the attention kernels for a step and plans their launches.
 
-float32: the generic kernel (any head size up to 256).  bfloat16: the tensor-core
-kernels when they cover the head size, else the generic kernel in bfloat16.
+float32: the generic kernel (one block per row and head; any head size up to 256).
+bfloat16, head size a multiple of 16: the tensor-core kernels.  Segments that bring
+at most 16 rows per kv head (a decoded token, a portion of two or three tokens) go
+to the split-KV kernel, the rest are cut into 64-row tiles for the flash kernel; a
+mixed step launches both.  Other head sizes in bfloat16 use the generic kernel.
+
+The plan (which segments go where, how the keys are split) depends only on the
+step's segments and on the head grouping, so it is made once per step and reused by
+every layer.
 """
 from __future__ import annotations
 
-from typing import List
+from typing import List, Optional
 
 import torch
 
 from . import functions as F
 
+_TILE = 64
+_TARGET_BLOCKS = 148 * 4      # blocks that keep every SM of a B200 busy with a few blocks each
+_MIN_CHUNK = 128
+
+
+def tensor_core_ok(head_dim: int) -> bool:
+    return head_dim % 16 == 0 and 16 <= head_dim <= 256
+
 
 def modules_for(dtype: torch.dtype, head_dim: int) -> List[str]:
+    if dtype is torch.bfloat16 and tensor_core_ok(head_dim):
+        return ["attention_bf16"]
     return ["attention_generic"]
+
+
+def split_plan(spans: List[int], blocks_per_split: int):
+    """Keys per split (a multiple of 64) and the largest number of splits, for items
+    whose key spans (from a 64-aligned base to the last key) are `spans`."""
+    longest = max(spans)
+    wanted = max(1, _TARGET_BLOCKS // max(1, blocks_per_split))
+    chunk = max(_MIN_CHUNK, -(-longest // wanted))
+    chunk = -(-chunk // _TILE) * _TILE
+    return chunk, -(-longest // chunk)
+
+
+class _Plan:
+    pass
+
+
+def _plan(step, group: int, kv_heads: int, window: int) -> _Plan:
+    key = ("attention_plan", group, kv_heads, window)
+    plan = step.scratch.get(key)
+    if plan is not None:
+        return plan
+    plan = _Plan()
+    device = step.positions.device
+    small = [i for i, s in enumerate(step.segments) if group <= 16 and s.count * group <= 16]
+    large = [i for i in range(len(step.segments)) if i not in set(small)] if len(small) < len(step.segments) else []
+    plan.n_items = len(small)
+    plan.items = None
+    plan.tiles = None
+    if small:
+        if len(small) != len(step.segments):
+            plan.items = torch.tensor(small, dtype=torch.int32).to(device)
+        spans = []
+        for i in small:
+            s = step.segments[i]
+            first = max(0, s.start - window + 1) if window else 0
+            spans.append(s.start + s.count - (first // _TILE) * _TILE)
+        plan.chunk, plan.max_splits = split_plan(spans, len(small) * kv_heads)
+    if large:
+        tiles = [(i, t) for i in large for t in range(0, step.segments[i].count, _TILE)]
+        tiles.sort(key=lambda it: -(step.segments[it[0]].start + it[1]))      # longest key walks first
+        plan.tiles = torch.tensor(tiles, dtype=torch.int32).to(device)
+    step.scratch[key] = plan
+    return plan
 
 
 def paged_attention(qkv, out, cache, table, step, q_heads, kv_heads, head_dim, window, scale, cache_group=None):
     """qkv: [M, (Hq + 2 Hkv) D] after norm and rotation (queries in the first Hq D
     columns); out: [M, Hq D]."""
-    F.attention_generic(qkv, out, cache, step.positions, step.segment_of_row, table, step.page_size,
-                        q_heads, kv_heads, head_dim, window, scale, step.status)
+    if qkv.dtype is not torch.bfloat16 or not tensor_core_ok(head_dim):
+        F.attention_generic(qkv, out, cache, step.positions, step.segment_of_row, table, step.page_size,
+                            q_heads, kv_heads, head_dim, window, scale, step.status)
+        return
+    plan = _plan(step, q_heads // kv_heads, kv_heads, window)
+    if plan.n_items:
+        partial = None
+        if plan.max_splits > 1:
+            count = F.attention_decode_scratch_floats(plan.n_items, kv_heads, head_dim, plan.max_splits)
+            partial = step.scratch.get(("attention_partial", count))
+            if partial is None:
+                partial = torch.empty(count, dtype=torch.float32, device=qkv.device)
+                step.scratch[("attention_partial", count)] = partial
+        F.attention_decode_bf16(qkv, out, cache, plan.items, plan.n_items, step.segment_info, table, step.page_size,
+                                q_heads, kv_heads, head_dim, window, scale, plan.chunk, plan.max_splits, partial,
+                                step.status)
+    if plan.tiles is not None:
+        F.attention_prefill_bf16(qkv, out, cache, plan.tiles, step.segment_info, table, step.page_size, q_heads,
+                                 kv_heads, head_dim, window, scale, step.status)

@@ -123,3 +123,48 @@ def sample(logits: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
         expect(uniform, torch.float64, "uniform numbers")
     call("sampling", "mlr_sample", ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1],
          ptr(temperature), ptr(uniform), ptr(out), ptr(status), stream())
+
+
+def attention_decode_bf16(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, items: Optional[torch.Tensor],
+                          n_items: int, segment_info: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                          q_heads: int, kv_heads: int, head_dim: int, window: int, scale: float, chunk: int,
+                          max_splits: int, partial: Optional[torch.Tensor], status: torch.Tensor) -> None:
+    """Split-KV attention for requests that bring at most 16 rows per kv head (tokens
+    times query heads per kv head).  `items` lists the segments to run (None: all of
+    them, in order); `partial` is float32 scratch of `attention_decode_scratch_floats`
+    elements (needed when max_splits > 1)."""
+    on_gpu(q, out, cache, items, segment_info, block_table, partial, status)
+    for t in (q, out, cache):
+        if t.dtype is not torch.bfloat16:
+            raise KernelError("attention_decode_bf16 takes bfloat16 tensors")
+    if q.stride(1) != 1 or out.stride(1) != 1 or not cache.is_contiguous():
+        raise KernelError("attention: inner strides must be 1 and the cache contiguous")
+    if partial is not None:
+        expect(partial, torch.float32, "the split scratch")
+        if partial.numel() < attention_decode_scratch_floats(n_items, kv_heads, head_dim, max_splits):
+            raise KernelError("attention_decode_bf16: the split scratch is too small")
+    call("attention_bf16", "mlr_attention_decode_bf16", ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(cache),
+         cache.shape[0], ptr(items), n_items, ptr(segment_info), ptr(block_table), block_table.stride(0), page_size,
+         q_heads, kv_heads, head_dim, int(window), float(scale), int(chunk), int(max_splits), ptr(partial),
+         ptr(status), stream())
+
+
+def attention_decode_scratch_floats(n_items: int, kv_heads: int, head_dim: int, max_splits: int) -> int:
+    return n_items * kv_heads * max_splits * 16 * (head_dim + 2)
+
+
+def attention_prefill_bf16(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, tiles: torch.Tensor,
+                           segment_info: torch.Tensor, block_table: torch.Tensor, page_size: int, q_heads: int,
+                           kv_heads: int, head_dim: int, window: int, scale: float, status: torch.Tensor) -> None:
+    """Flash attention for prompt portions.  `tiles` is int32 [n, 2]: segment index and
+    first token of each 64-row tile."""
+    on_gpu(q, out, cache, tiles, segment_info, block_table, status)
+    for t in (q, out, cache):
+        if t.dtype is not torch.bfloat16:
+            raise KernelError("attention_prefill_bf16 takes bfloat16 tensors")
+    if q.stride(1) != 1 or out.stride(1) != 1 or not cache.is_contiguous():
+        raise KernelError("attention: inner strides must be 1 and the cache contiguous")
+    expect(tiles, torch.int32, "the tile list")
+    call("attention_bf16", "mlr_attention_prefill_bf16", ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(cache),
+         cache.shape[0], ptr(tiles), tiles.shape[0], ptr(segment_info), ptr(block_table), block_table.stride(0),
+         page_size, q_heads, kv_heads, head_dim, int(window), float(scale), ptr(status), stream())

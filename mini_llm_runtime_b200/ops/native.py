@@ -39,6 +39,13 @@ _SIGNATURES = {
         "mlr_attention_generic": [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                   c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     },
+    "attention_bf16": {
+        "mlr_attention_decode_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                      c_void_p, c_void_p, c_void_p],
+        "mlr_attention_prefill_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                                       c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+    },
     "sampling": {
         "mlr_sample": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     },

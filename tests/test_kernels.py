@@ -1,0 +1,415 @@
+"""Each kernel alone against a plain float32/float64 reference of the same operation,
+at sizes other than the tiny models': real widths, sizes that are no power of two,
+page edges, window edges, shuffled pages, and inputs made so that one far key decides
+the result."""
+import math
+
+import pytest
+import torch
+
+import plain_qwen3 as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def F():
+    from mini_llm_runtime_b200.ops import functions
+    return functions
+
+
+def status():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+def gen(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+# ------------------------------------------------------------------ row-wise kernels
+@pytest.mark.parametrize("rows,width,vocab", [(7, 100, 33), (64, 4096, 151936), (3, 5120 + 6, 1000)])
+@pytest.mark.parametrize("wdtype", [torch.float32, torch.bfloat16])
+def test_embed_gather(rows, width, vocab, wdtype):
+    table = torch.randn(vocab, width, generator=gen(0)).to(wdtype).to(DEV)
+    ids = torch.randint(0, vocab, (rows,), generator=gen(1), dtype=torch.int32).to(DEV)
+    out, st = torch.full((rows, width), 7.0, device=DEV), status()
+    F().embed_gather(table, ids, out, st)
+    assert torch.equal(out, table[ids.long()].float()) and st.item() == 0
+    ids[rows // 2] = vocab
+    F().embed_gather(table, ids, out, st)
+    assert st.item() == 1 and out[rows // 2].abs().sum() == 0
+
+
+@pytest.mark.parametrize("rows,width", [(5, 64), (33, 4096), (4, 5120), (2, 1000), (3, 33)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("w_dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_with_residual_add(rows, width, out_dtype, w_dtype):
+    h = torch.randn(rows, width, generator=gen(0)) * 3
+    delta = torch.randn(rows, width, generator=gen(1))
+    w = (1 + 0.1 * torch.randn(width, generator=gen(2))).to(w_dtype)
+    eps = 1e-5
+    want_h = h + delta
+    want = P.rms_norm(want_h.double(), w.double(), eps)
+    hd, out = h.clone().to(DEV), torch.empty(rows, width, dtype=out_dtype, device=DEV)
+    F().rmsnorm(hd, w.to(DEV), eps, out, delta=delta.to(DEV))
+    assert torch.equal(hd.cpu(), want_h)                       # the stream moved on
+    tol = 1e-5 if out_dtype is torch.float32 else 1e-2
+    assert torch.allclose(out.double().cpu(), want, rtol=tol, atol=tol)
+    # Selected rows, stream untouched.
+    idx = torch.tensor([rows - 1, 0], dtype=torch.int32, device=DEV)
+    hd2, out2 = h.clone().to(DEV), torch.empty(2, width, dtype=out_dtype, device=DEV)
+    F().rmsnorm(hd2, w.to(DEV), eps, out2, delta=delta.to(DEV), rows=idx, write_back=False)
+    assert torch.equal(hd2.cpu(), h)
+    assert torch.allclose(out2.double().cpu(), want[[rows - 1, 0]], rtol=tol, atol=tol)
+    # Without a delta.
+    F().rmsnorm(hd2, w.to(DEV), eps, out2[:1], rows=idx[:1])
+    assert torch.allclose(out2[:1].double().cpu(), P.rms_norm(h[rows - 1:].double(), w.double(), eps), rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("rows,inter", [(3, 176), (17, 12288), (1, 7)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu(rows, inter, dtype):
+    gu = (torch.randn(rows, 2 * inter, generator=gen(0)) * 3).to(dtype)
+    out = torch.empty(rows, inter, dtype=dtype, device=DEV)
+    F().swiglu(gu.to(DEV), out)
+    g, u = gu[:, :inter].double(), gu[:, inter:].double()
+    want = g / (1 + torch.exp(-g)) * u
+    tol = 1e-6 if dtype is torch.float32 else 1e-2
+    assert torch.allclose(out.double().cpu(), want, rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (5, 100, 37), (64, 64, 16), (65, 130, 129), (3, 515, 80), (130, 300, 4096)])
+def test_gemm_f32_is_true_float32_and_independent_of_batching(M, N, K):
+    a = torch.randn(M, K, generator=gen(0))
+    w = torch.randn(N, K, generator=gen(1))
+    out = torch.empty(M, N, device=DEV)
+    F().gemm_f32(a.to(DEV), w.to(DEV), out)
+    want = a.double() @ w.double().T
+    # float32 products and sums: error ~ sqrt(K) * 2^-24 relative to the magnitudes summed.
+    bound = 2e-7 * math.sqrt(K) * (a.abs().double() @ w.abs().double().T) + 1e-6
+    assert ((out.double().cpu() - want).abs() <= bound).all()
+    # The same row alone gives the same bits.
+    alone = torch.empty(1, N, device=DEV)
+    F().gemm_f32(a[M - 1:].to(DEV), w.to(DEV), alone)
+    assert torch.equal(alone[0], out[M - 1])
+    # A strided view of a wider buffer works.
+    wide = torch.zeros(M, K + 8, device=DEV)
+    wide[:, :K] = a.to(DEV)
+    out2 = torch.empty(M, N, device=DEV)
+    F().gemm_f32(wide[:, :K], w.to(DEV), out2)
+    assert torch.equal(out2, out)
+
+
+# ------------------------------------------------------------------ paged cache helpers
+def make_cache(kvs, page_size, dtype, seed=0, extra_pages=3):
+    """kvs: list of (k, v) [T, Hkv, D] per request.  Returns cache [pages, 2, Hkv, ps, D]
+    filled with NaN except the given tokens, on shuffled pages, and the block table."""
+    Hkv, D = kvs[0][0].shape[1:]
+    blocks = [-(-k.shape[0] // page_size) for k, _ in kvs]
+    num_pages = sum(blocks) + extra_pages
+    order = torch.randperm(num_pages, generator=gen(seed)).tolist()
+    cache = torch.full((num_pages, 2, Hkv, page_size, D), float("nan"), dtype=dtype)
+    table = torch.full((len(kvs), max(blocks)), -1, dtype=torch.int32)
+    for i, (k, v) in enumerate(kvs):
+        for b in range(blocks[i]):
+            page = order.pop()
+            n = min(page_size, k.shape[0] - b * page_size)
+            cache[page, 0, :, :n] = k[b * page_size:b * page_size + n].transpose(0, 1).to(dtype)
+            cache[page, 1, :, :n] = v[b * page_size:b * page_size + n].transpose(0, 1).to(dtype)
+            table[i, b] = page
+    return cache.to(DEV), table.to(DEV)
+
+
+def segments_meta(segments):
+    """segments: list of (start, count).  Returns positions, segment_of_row, segment_info."""
+    pos, seg, info, row = [], [], [], 0
+    for i, (start, count) in enumerate(segments):
+        pos += list(range(start, start + count))
+        seg += [i] * count
+        info.append([row, count, start, i])
+        row += count
+    t = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    return t(pos), t(seg), t(info)
+
+
+def plain_attention_rows(q, k, v, start, window, scale):
+    """q: [count, Hq, D] at positions start..; k, v: [start+count, Hkv, D]."""
+    T = k.shape[0]
+    full_q = torch.zeros(T, q.shape[1], q.shape[2], dtype=q.dtype)
+    full_q[start:] = q
+    return P.causal_attention(full_q[start:].new_tensor(full_q), k, v, window, scale)[start:]
+
+
+def fast_plain_attention(q, k, v, start, window, scale):
+    """Dense float64 version of the same definition (the loop version is slow for
+    thousands of keys): q [count, Hq, D], k, v [T, Hkv, D]."""
+    count, Hq, D = q.shape
+    T, Hkv = k.shape[0], k.shape[1]
+    g = Hq // Hkv
+    qd, kd, vd = q.double(), k.double().repeat_interleave(g, 1), v.double().repeat_interleave(g, 1)
+    s = torch.einsum("qhd,thd->hqt", qd, kd) * scale
+    pos = torch.arange(start, start + count)[:, None]
+    t = torch.arange(T)[None, :]
+    mask = (t > pos) | ((t < pos - window + 1) if window else torch.zeros_like(t, dtype=torch.bool))
+    s = s.masked_fill(mask[None], float("-inf"))
+    return torch.einsum("hqt,thd->qhd", torch.softmax(s, -1), vd)
+
+
+def test_dense_reference_equals_the_plain_loop():
+    q, k, v = (torch.randn(40, h, 16, generator=gen(i)) for i, h in ((0, 6), (1, 2), (2, 2)))
+    for window in (None, 7):
+        a = P.causal_attention(q, k, v, window)
+        b = fast_plain_attention(q, k, v, 0, window or 0, 1 / 4.0)
+        assert torch.allclose(a.double(), b, atol=1e-5)
+
+
+ATTENTION_CASES = [
+    # Hq, Hkv, D, page, [(context before, new tokens)], window
+    (4, 2, 16, 4, [(0, 33)], 0),
+    (6, 3, 32, 8, [(0, 1), (16, 1), (17, 2), (40, 77)], 0),
+    (5, 1, 48, 16, [(100, 3), (0, 70), (39, 1), (40, 1), (41, 1)], 40),
+    (32, 8, 128, 16, [(127, 1), (128, 1), (129, 1), (15, 1), (16, 1), (2047, 1)], 0),
+    (32, 8, 128, 16, [(0, 129), (1536, 64), (63, 2)], 0),
+    (16, 8, 128, 64, [(300, 200), (5, 1)], 128),
+    (8, 8, 64, 1, [(10, 20), (70, 1)], 0),
+    (16, 1, 256, 32, [(90, 40), (200, 1)], 100),
+    (14, 2, 80, 16, [(64, 64), (500, 2), (1000, 1)], 0),
+]
+
+
+def run_attention_case(dtype, kernel, case, seed):
+    Hq, Hkv, D, page, segs, window = case
+    scale = 1 / math.sqrt(D)
+    kvs, qs, wants = [], [], []
+    for i, (before, count) in enumerate(segs):
+        T = before + count
+        k = torch.randn(T, Hkv, D, generator=gen(seed + 3 * i)).to(dtype).float()
+        v = torch.randn(T, Hkv, D, generator=gen(seed + 3 * i + 1)).to(dtype).float()
+        q = torch.randn(count, Hq, D, generator=gen(seed + 3 * i + 2)).to(dtype).float()
+        kvs.append((k, v))
+        qs.append(q)
+        wants.append(fast_plain_attention(q, k, v, before, window, scale))
+    cache, table = make_cache(kvs, page, dtype, seed)
+    positions, seg_of_row, info = segments_meta(segs)
+    rows = sum(c for _, c in segs)
+    # Queries sit in the first columns of a wider qkv buffer, as in the engine.
+    qkv = torch.zeros(rows, (Hq + 2 * Hkv) * D, dtype=dtype, device=DEV)
+    qkv[:, :Hq * D] = torch.cat(qs).reshape(rows, Hq * D).to(dtype).to(DEV)
+    out = torch.full((rows, Hq * D), float("nan"), dtype=dtype, device=DEV)
+    st = status()
+    kernel(qkv, out, cache, table, positions, seg_of_row, info, segs, page, Hq, Hkv, D, window, scale, st)
+    assert st.item() == 0
+    got = out.float().cpu().reshape(rows, Hq, D).double()
+    want = torch.cat(wants)
+    tol = 2e-5 if dtype is torch.float32 else 2e-2
+    assert torch.isfinite(got).all()
+    assert torch.allclose(got, want, atol=tol, rtol=tol), f"max diff {(got - want).abs().max():.3e}"
+
+
+def generic_kernel(qkv, out, cache, table, positions, seg_of_row, info, segs, page, Hq, Hkv, D, window, scale, st):
+    F().attention_generic(qkv, out, cache, positions, seg_of_row, table, page, Hq, Hkv, D, window, scale, st)
+
+
+@pytest.mark.parametrize("case", ATTENTION_CASES, ids=[f"case{i}" for i in range(len(ATTENTION_CASES))])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_generic(case, dtype):
+    run_attention_case(dtype, generic_kernel, case, seed=10)
+
+
+def tensor_core_kernels(chunk=None):
+    def kernel(qkv, out, cache, table, positions, seg_of_row, info, segs, page, Hq, Hkv, D, window, scale, st):
+        group = Hq // Hkv
+        small = [i for i, (_, c) in enumerate(segs) if group <= 16 and c * group <= 16]
+        large = [i for i in range(len(segs)) if i not in small]
+        if small:
+            spans = []
+            for i in small:
+                start, count = segs[i]
+                first = max(0, start - window + 1) if window else 0
+                spans.append(start + count - first // 64 * 64)
+            ck = chunk or 128
+            splits = max(-(-s // ck) for s in spans)
+            items = torch.tensor(small, dtype=torch.int32, device=DEV)
+            partial = torch.full((F().attention_decode_scratch_floats(len(small), Hkv, D, splits),), float("nan"),
+                                 device=DEV)
+            F().attention_decode_bf16(qkv, out, cache, items, len(small), info, table, page, Hq, Hkv, D, window, scale,
+                                      ck, splits, partial, st)
+        if large:
+            tiles = torch.tensor([(i, t) for i in large for t in range(0, segs[i][1], 64)], dtype=torch.int32, device=DEV)
+            F().attention_prefill_bf16(qkv, out, cache, tiles, info, table, page, Hq, Hkv, D, window, scale, st)
+    return kernel
+
+
+@pytest.mark.parametrize("case", ATTENTION_CASES, ids=[f"case{i}" for i in range(len(ATTENTION_CASES))])
+@pytest.mark.parametrize("chunk", [64, 128, 4096])
+def test_attention_tensor_core_kernels(case, chunk):
+    if case[2] % 16:
+        pytest.skip("head size is no multiple of 16")
+    run_attention_case(torch.bfloat16, tensor_core_kernels(chunk), case, seed=20)
+
+
+def test_tensor_core_kernels_refuse_what_they_cannot_do():
+    from mini_llm_runtime_b200.ops.native import KernelError
+    q = torch.zeros(1, 24 * 3, dtype=torch.bfloat16, device=DEV)
+    cache = torch.zeros(2, 2, 1, 16, 24, dtype=torch.bfloat16, device=DEV)
+    pos, seg, info = segments_meta([(0, 1)])
+    table = torch.zeros(1, 1, dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError, match="head size 24 is not a multiple of 16"):
+        F().attention_decode_bf16(q, q[:, :24].clone(), cache, None, 1, info, table, 16, 1, 1, 24, 0, 1.0, 64, 1, None, status())
+    with pytest.raises(KernelError, match="head size 24"):
+        F().attention_prefill_bf16(q, q[:, :24].clone(), cache, torch.zeros(1, 2, dtype=torch.int32, device=DEV), info,
+                                   table, 16, 1, 1, 24, 0, 1.0, status())
+    with pytest.raises(KernelError, match="outside"):
+        big = torch.zeros(1, 3 * 272, dtype=torch.float32, device=DEV)
+        F().attention_generic(big, big[:, :272].clone(), torch.zeros(2, 2, 1, 16, 272, device=DEV), pos, seg, table,
+                              16, 1, 1, 272, 0, 1.0, status())
+
+
+@pytest.mark.parametrize("dtype,kernel", [(torch.float32, generic_kernel), (torch.bfloat16, generic_kernel),
+                                          (torch.bfloat16, tensor_core_kernels(128))],
+                         ids=["generic-f32", "generic-bf16", "tensor-core"])
+def test_one_far_key_among_thousands_decides(dtype, kernel):
+    """Random keys give near-uniform attention, which hides a kernel that skips or
+    repeats a key.  Here one far key (and one at a page edge) matches the query so
+    strongly that the output must be that key's value."""
+    Hq, Hkv, D, page = 8, 2, 64, 16
+    for before, target in [(3000, 7), (3000, 2048 + 15), (1023, 1008), (4096, 4096)]:
+        T = before + 1
+        k = torch.randn(T, Hkv, D, generator=gen(0)) * 0.1
+        v = torch.randn(T, Hkv, D, generator=gen(1))
+        q = torch.randn(1, Hq, D, generator=gen(2)) * 0.1
+        direction = torch.randn(D, generator=gen(3))
+        direction /= direction.norm()
+        k[target, :, :] = direction * 40
+        q[0, :, :] = direction * 40
+        want = v[target].repeat_interleave(Hq // Hkv, 0)
+        cache, table = make_cache([(k, v)], page, dtype, seed=before)
+        positions, seg_of_row, info = segments_meta([(before, 1)])
+        qkv = torch.zeros(1, (Hq + 2 * Hkv) * D, dtype=dtype, device=DEV)
+        qkv[:, :Hq * D] = q.reshape(1, -1).to(dtype).to(DEV)
+        out = torch.zeros(1, Hq * D, dtype=dtype, device=DEV)
+        kernel(qkv, out, cache, table, positions, seg_of_row, info, [(before, 1)], page, Hq, Hkv, D, 0, 1.0, status())
+        got = out.float().cpu().reshape(Hq, D)
+        assert torch.allclose(got, want.to(dtype).float(), atol=2e-2), f"context {before}, key {target}"
+
+
+@pytest.mark.parametrize("dtype,kernel", [(torch.float32, generic_kernel), (torch.bfloat16, tensor_core_kernels(64))],
+                         ids=["generic", "tensor-core"])
+def test_window_edge_is_exact(dtype, kernel):
+    """The key just outside the window would dominate if it were read."""
+    Hq, Hkv, D, page, window = 4, 1, 32, 8, 24
+    for before in (23, 24, 25, 100, 127, 128):
+        T = before + 1
+        k = torch.randn(T, Hkv, D, generator=gen(0)) * 0.1
+        v = torch.randn(T, Hkv, D, generator=gen(1))
+        q = torch.randn(1, Hq, D, generator=gen(2))
+        outside = before - window
+        if outside >= 0:
+            k[outside] = q[0, 0] * 50          # must not be seen
+            v[outside] = 1000.0
+        want = fast_plain_attention(q, k, v, before, window, 1.0)
+        assert want.abs().max() < 100
+        cache, table = make_cache([(k, v)], page, dtype)
+        positions, seg_of_row, info = segments_meta([(before, 1)])
+        qkv = torch.zeros(1, (Hq + 2) * D, dtype=dtype, device=DEV)
+        qkv[:, :Hq * D] = q.reshape(1, -1).to(dtype).to(DEV)
+        out = torch.zeros(1, Hq * D, dtype=dtype, device=DEV)
+        kernel(qkv, out, cache, table, positions, seg_of_row, info, [(before, 1)], page, Hq, Hkv, D, window, 1.0, status())
+        tol = 1e-4 if dtype is torch.float32 else 3e-2
+        assert torch.allclose(out.float().cpu().reshape(1, Hq, D).double(), want, atol=tol, rtol=tol), before
+
+
+# ------------------------------------------------------------------ q/k norm, rotation, cache write
+@pytest.mark.parametrize("Hq,Hkv,D,page", [(4, 2, 16, 4), (5, 1, 48, 16), (32, 8, 128, 16), (3, 3, 256, 8), (2, 1, 6, 2)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_qk_norm_rope_cache(Hq, Hkv, D, page, dtype):
+    from mini_llm_runtime_b200.parts.rotary import rotation_table
+    segs = [(5, 9), (0, 3), (30, 1)]
+    rows = sum(c for _, c in segs)
+    theta, eps = 50000.0, 1e-5
+    qkv = torch.randn(rows, (Hq + 2 * Hkv) * D, generator=gen(0)).to(dtype)
+    wq = (1 + 0.1 * torch.randn(D, generator=gen(1))).to(dtype)
+    wk = (1 + 0.1 * torch.randn(D, generator=gen(2))).to(dtype)
+    positions, seg_of_row, info = segments_meta(segs)
+    table_cs = rotation_table(theta, D, 64)
+    cos, sin = P.rope_table(positions.tolist(), D, theta, torch.float32)
+    assert torch.allclose(table_cs[positions.long().cpu(), :D // 2], cos, atol=1e-6)
+    x = qkv.float()
+    q = P.qk_norm_rope(x[:, :Hq * D].reshape(rows, Hq, D), wq.float(), eps, cos, sin)
+    k = P.qk_norm_rope(x[:, Hq * D:(Hq + Hkv) * D].reshape(rows, Hkv, D), wk.float(), eps, cos, sin)
+    v = x[:, (Hq + Hkv) * D:].reshape(rows, Hkv, D)
+    # An empty cache with room for every request.
+    kvs = [(torch.zeros(s + c, Hkv, D), torch.zeros(s + c, Hkv, D)) for s, c in segs]
+    cache, table = make_cache(kvs, page, dtype, seed=4)
+    cache.fill_(float("nan"))
+    dev = qkv.to(DEV)
+    st = status()
+    F().qk_norm_rope_cache(dev, Hq, Hkv, D, wq.to(DEV), wk.to(DEV), eps, table_cs.to(DEV), positions, seg_of_row, table,
+                           page, cache, True, st)
+    assert st.item() == 0
+    tol = 1e-5 if dtype is torch.float32 else 2e-2
+    got = dev.float().cpu()
+    assert torch.allclose(got[:, :Hq * D].reshape(rows, Hq, D), q, atol=tol, rtol=tol)
+    assert torch.allclose(got[:, Hq * D:(Hq + Hkv) * D].reshape(rows, Hkv, D), k, atol=tol, rtol=tol)
+    assert torch.equal(got[:, (Hq + Hkv) * D:], x[:, (Hq + Hkv) * D:])
+    host_cache, host_table = cache.float().cpu(), table.cpu()
+    written = torch.zeros(host_cache.shape[0], page, dtype=torch.bool)
+    row = 0
+    for i, (start, count) in enumerate(segs):
+        for p in range(start, start + count):
+            page_id, slot = host_table[i, p // page].item(), p % page
+            assert torch.allclose(host_cache[page_id, 0, :, slot], k[row], atol=tol, rtol=tol)
+            assert torch.equal(host_cache[page_id, 1, :, slot], v[row].to(dtype).float())
+            written[page_id, slot] = True
+            row += 1
+    # Nothing else was touched.
+    assert torch.isnan(host_cache[~written[:, None, None, :, None].expand_as(host_cache)]).all()
+    # A run that reads another run's cache writes nothing and leaves k alone.
+    cache.fill_(float("nan"))
+    dev2 = qkv.to(DEV)
+    F().qk_norm_rope_cache(dev2, Hq, Hkv, D, wq.to(DEV), wk.to(DEV), eps, table_cs.to(DEV), positions, seg_of_row, table,
+                           page, cache, False, st)
+    assert torch.isnan(cache).all() and torch.equal(dev2[:, :Hq * D], dev[:, :Hq * D])
+    assert torch.equal(dev2[:, Hq * D:].cpu(), qkv[:, Hq * D:])
+
+
+def test_qk_kernel_reports_a_page_outside_the_pool():
+    pos, seg, info = segments_meta([(0, 2)])
+    qkv = torch.zeros(2, 3 * 16, device=DEV)
+    cache = torch.zeros(2, 2, 1, 4, 16, device=DEV)
+    table = torch.tensor([[5]], dtype=torch.int32, device=DEV)
+    st = status()
+    F().qk_norm_rope_cache(qkv, 1, 1, 16, None, None, 1.0, None, pos, seg, table, 4, cache, True, st)
+    assert st.item() == 2 and cache.abs().sum() == 0
+
+
+# ------------------------------------------------------------------ sampling
+@pytest.mark.parametrize("rows,vocab", [(1, 5), (7, 515), (3, 151936), (64, 4099)])
+def test_greedy_and_temperature_sampling(rows, vocab):
+    from mini_llm_runtime_b200.sampling.sampler import Sampler
+    logits = torch.randn(rows, vocab, generator=gen(0)) * 2
+    logits[0, min(3, vocab - 1)] = logits[0, 1] = logits[0].max() + 1          # a tie: the lowest id wins
+    st = status()
+    sampler = Sampler(torch.device(DEV), st)
+    greedy = sampler.sample(logits.to(DEV)).tolist()
+    assert greedy == [P.greedy(r) for r in logits] and greedy[0] == 1
+    temps = [0.0 if i % 3 == 0 else 0.5 + 0.3 * i for i in range(rows)]
+    for seed in range(3):
+        us = [P.uniform_for(seed, i, 9) for i in range(rows)]
+        got = sampler.sample(logits.to(DEV), temps, us).tolist()
+        for i in range(rows):
+            if temps[i] == 0:
+                assert got[i] == greedy[i]
+                continue
+            cdf = P.temperature_cdf(logits[i], temps[i])
+            lo = cdf[got[i] - 1].item() if got[i] else 0.0
+            # The drawn id's interval of the cumulative distribution holds u (up to rounding of the sums).
+            assert lo - 1e-6 <= us[i] <= cdf[got[i]].item() + 1e-6, (i, got[i], us[i])
+    assert st.item() == 0
+    # Edges of the distribution and a non-finite row.
+    peaked = torch.full((2, vocab), -50.0)
+    peaked[0, vocab - 1] = 50.0
+    peaked[1, 0] = 50.0
+    assert sampler.sample(peaked.to(DEV), [1.0, 1.0], [0.999999, 0.0]).tolist() == [vocab - 1, 0]
+    logits[rows - 1, vocab // 2] = float("nan")
+    assert sampler.sample(logits.to(DEV)).tolist()[rows - 1] == -1 and st.item() == 4
