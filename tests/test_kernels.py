@@ -132,14 +132,6 @@ def segments_meta(segments):
     return t(pos), t(seg), t(info)
 
 
-def plain_attention_rows(q, k, v, start, window, scale):
-    """q: [count, Hq, D] at positions start..; k, v: [start+count, Hkv, D]."""
-    T = k.shape[0]
-    full_q = torch.zeros(T, q.shape[1], q.shape[2], dtype=q.dtype)
-    full_q[start:] = q
-    return P.causal_attention(full_q[start:].new_tensor(full_q), k, v, window, scale)[start:]
-
-
 def fast_plain_attention(q, k, v, start, window, scale):
     """Dense float64 version of the same definition (the loop version is slow for
     thousands of keys): q [count, Hq, D], k, v [T, Hkv, D]."""
