@@ -229,12 +229,14 @@ def main() -> int:
 
     def decode_rate(batch, ctx, steps, warmup, with_clocks=False):
         slots = fill(batch, ctx)
-        ids = torch.randint(0, cfg["vocab_size"], (batch,), generator=gen).tolist()
+        ids = torch.randint(0, cfg["vocab_size"], (batch,), generator=gen).to(torch.int32).to(model.rt.device)
+        entries = [StepEntry(s, [0], [0]) for s in slots]
 
         def one_step():
+            # The sampled ids stay on the device and feed the next step.
             nonlocal ids
-            logits = model.step([StepEntry(s, [t], [0]) for s, t in zip(slots, ids)])
-            ids = sampler.sample(logits).tolist()
+            logits = model.step(entries, device_tokens=ids)
+            ids = sampler.sample(logits)
 
         for _ in range(warmup):
             one_step()

@@ -12,7 +12,7 @@
 //                    (flash attention: running maximum and sum, no score matrix).
 //
 // Both read K and V tiles of 64 keys through the block table with 16-byte cp.async into
-// XOR-swizzled shared memory (three stages in flight), take fragments with ldmatrix, and
+// XOR-swizzled shared memory (two or three stages), take fragments with ldmatrix, and
 // multiply with mma.sync m16n8k16 (bf16 in, float32 accumulate).  Scores, maxima, sums and
 // the output accumulators are float32.  Keys outside a row's [lo, position] are filled
 // with zeros in shared memory and masked in the scores, so unused or stale cache memory
@@ -28,7 +28,8 @@ namespace {
 
 constexpr int kTileKeys = 64;
 constexpr int kThreads = 128;
-constexpr int kStages = 3;
+constexpr int kDecodeStages = 3;   // 3 x 32 KB at head size 128: two blocks per SM
+constexpr int kPrefillStages = 2;  // two stages leave room for three blocks per SM
 constexpr float kLog2e = 1.4426950408889634f;
 
 // ---------------------------------------------------------------- PTX helpers
@@ -80,53 +81,70 @@ struct Tile {
 struct CacheView {
     const __nv_bfloat16* base;   // [page][2][kv_heads][page_size][head_dim]
     const int* table;            // this request's block table row
-    int num_pages, page_size, kv_heads, head_dim, kv_head;
+    int num_pages, page_size, page_shift, kv_heads, head_dim, kv_head;   // page_shift: log2(page_size) or -1
 };
 
+__host__ __device__ inline int log2_or_minus1(int v) {
+    int s = 0;
+    while ((1 << s) < v) ++s;
+    return (1 << s) == v ? s : -1;
+}
+
 // Loads keys [tile_start, tile_start + 64) of K and V into one stage.  Keys outside
-// [first_key, last_key] are zero-filled.  Called by all threads of the block.
+// [first_key, last_key] are zero-filled.  Called by all 128 threads of the block: two
+// threads per key, each copying half of the key's K row and half of its V row, so a
+// thread looks its page up once per tile.
 template <int DMAX>
 __device__ __forceinline__ void load_tile(const CacheView& c, int tile_start, int first_key, int last_key,
                                           uint32_t k_smem, uint32_t v_smem, int* bad_page) {
-    const int chunks = c.head_dim >> 3;
+    const int row = threadIdx.x >> 1, half = threadIdx.x & 1;
+    const int half_chunks = c.head_dim >> 4;            // 16-byte chunks in half a row
+    const int key = tile_start + row;
     const size_t head_elems = static_cast<size_t>(c.page_size) * c.head_dim;
-    const size_t page_elems = head_elems * 2 * c.kv_heads;
-    const size_t value_shift = head_elems * c.kv_heads;
-    for (int idx = threadIdx.x; idx < kTileKeys * chunks; idx += kThreads) {
-        const int row = idx / chunks, chunk = idx - row * chunks;
-        const int key = tile_start + row;
-        const __nv_bfloat16* src = c.base;
-        int bytes = 0;
-        if (key >= first_key && key <= last_key) {
-            const int page = c.table[key / c.page_size];
-            if (page >= 0 && page < c.num_pages) {
-                src = c.base + page * page_elems + c.kv_head * head_elems +
-                      static_cast<size_t>(key % c.page_size) * c.head_dim + chunk * 8;
-                bytes = 16;
-            } else {
-                *bad_page = 1;
-            }
+    const __nv_bfloat16* src = c.base;
+    int bytes = 0;
+    if (key >= first_key && key <= last_key) {
+        const int block = c.page_shift >= 0 ? key >> c.page_shift : key / c.page_size;
+        const int in_page = c.page_shift >= 0 ? key & (c.page_size - 1) : key - block * c.page_size;
+        const int page = __ldg(c.table + block);
+        if (page >= 0 && page < c.num_pages) {
+            src = c.base + (static_cast<size_t>(page) * 2 * c.kv_heads + c.kv_head) * head_elems +
+                  static_cast<size_t>(in_page) * c.head_dim + half * half_chunks * 8;
+            bytes = 16;
+        } else {
+            *bad_page = 1;
         }
-        const uint32_t off = Tile<DMAX>::offset(row, chunk);
-        cp_async_16(k_smem + off, src, bytes);
-        cp_async_16(v_smem + off, bytes ? src + value_shift : src, bytes);
+    }
+    const __nv_bfloat16* vsrc = bytes ? src + head_elems * c.kv_heads : src;
+#pragma unroll
+    for (int j = 0; j < DMAX / 16; ++j) {
+        if (j < half_chunks) {
+            const uint32_t off = Tile<DMAX>::offset(row, half * half_chunks + j);
+            cp_async_16(k_smem + off, bytes ? src + j * 8 : src, bytes);
+            cp_async_16(v_smem + off, bytes ? vsrc + j * 8 : vsrc, bytes);
+        }
     }
 }
 
-// One warp: S[16 rows x 16 keys] += Q[16 x D] K^T for keys [key0, key0+16) of a tile.
-template <int DMAX>
-__device__ __forceinline__ void qk_16keys(float (&s)[2][4], const uint32_t (&q)[DMAX / 16][4], uint32_t k_smem,
-                                          int key0, int dim_steps) {
+// One warp: S[16 rows x 16*NB keys] += Q[16 x D] K^T for keys [key0, key0 + 16*NB) of a tile.
+// The 2*NB accumulators are independent chains; walking the head dimension in the outer
+// loop keeps them all in flight.
+template <int DMAX, int NB>
+__device__ __forceinline__ void qk_keys(float (&s)[2 * NB][4], const uint32_t (&q)[DMAX / 16][4], uint32_t k_smem,
+                                        int key0, int dim_steps) {
     const int lane = threadIdx.x & 31;
     const int row = key0 + ((lane >> 4) << 3) + (lane & 7);
     const int chunk_in_step = (lane >> 3) & 1;
 #pragma unroll
     for (int kd = 0; kd < DMAX / 16; ++kd) {
         if (kd < dim_steps) {
-            uint32_t b[4];
-            ldmatrix_x4(b, k_smem + Tile<DMAX>::offset(row, kd * 2 + chunk_in_step));
-            mma_bf16(s[0], q[kd], b[0], b[1]);
-            mma_bf16(s[1], q[kd], b[2], b[3]);
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+                uint32_t b[4];
+                ldmatrix_x4(b, k_smem + Tile<DMAX>::offset(row + nb * 16, kd * 2 + chunk_in_step));
+                mma_bf16(s[2 * nb], q[kd], b[0], b[1]);
+                mma_bf16(s[2 * nb + 1], q[kd], b[2], b[3]);
+            }
         }
     }
 }
@@ -282,7 +300,7 @@ __global__ void __launch_bounds__(kThreads) decode_splitkv_kernel(
     const int tiles = (key_end - key_begin + kTileKeys - 1) / kTileKeys;
 
     CacheView view{cache, block_table + static_cast<size_t>(segment) * table_stride, num_pages, page_size,
-                   kv_heads, head_dim, kv_head};
+                   log2_or_minus1(page_size), kv_heads, head_dim, kv_head};
     const uint32_t smem_base = smem_u32(smem);
     auto k_stage = [&](int s) { return smem_base + s * 2 * Tile<DMAX>::kBytes; };
     auto v_stage = [&](int s) { return smem_base + s * 2 * Tile<DMAX>::kBytes + Tile<DMAX>::kBytes; };
@@ -310,23 +328,23 @@ __global__ void __launch_bounds__(kThreads) decode_splitkv_kernel(
     __syncthreads();
 
 #pragma unroll
-    for (int s = 0; s < kStages - 1; ++s) {
+    for (int s = 0; s < kDecodeStages - 1; ++s) {
         if (s < tiles) load_tile<DMAX>(view, key_begin + s * kTileKeys, plan.first_key, key_end - 1, k_stage(s), v_stage(s), &bad_page);
         cp_async_commit();
     }
     for (int it = 0; it < tiles; ++it) {
-        cp_async_wait<kStages - 2>();
+        cp_async_wait<kDecodeStages - 2>();
         __syncthreads();
-        const int next = it + kStages - 1;
+        const int next = it + kDecodeStages - 1;
         if (next < tiles)
-            load_tile<DMAX>(view, key_begin + next * kTileKeys, plan.first_key, key_end - 1, k_stage(next % kStages),
-                            v_stage(next % kStages), &bad_page);
+            load_tile<DMAX>(view, key_begin + next * kTileKeys, plan.first_key, key_end - 1, k_stage(next % kDecodeStages),
+                            v_stage(next % kDecodeStages), &bad_page);
         cp_async_commit();
-        const int stage = it % kStages;
+        const int stage = it % kDecodeStages;
         const int key_base = key_begin + it * kTileKeys + warp * 16;
         if (key_base < key_end) {
             float s[2][4] = {};
-            qk_16keys<DMAX>(s, qf, k_stage(stage), warp * 16, dim_steps);
+            qk_keys<DMAX, 1>(s, qf, k_stage(stage), warp * 16, dim_steps);
             uint32_t p[1][4];
             softmax_step<DMAX, 2>(s, st, o, p, key_base, lo, hi, scale_log2, true);
             pv_16keys<DMAX>(o, p[0], v_stage(stage), warp * 16, dim_steps);
@@ -392,10 +410,13 @@ __global__ void __launch_bounds__(kThreads) decode_splitkv_kernel(
     }
 }
 
-// grid = (items, kv_heads).  Adds up the splits of an item in split order.
+// grid = (items, kv_heads).  Adds up the splits of an item in split order.  The weights
+// exp2(m_split - m) / l are worked out once per (split, row) in shared memory; the sums
+// over splits then have no dependent loads.
 __global__ void __launch_bounds__(kThreads) combine_kernel(
     __nv_bfloat16* __restrict__ out, int ldo, const int* __restrict__ items, const int* __restrict__ segment_info,
     int q_heads, int kv_heads, int head_dim, int window, int chunk, int max_splits, const float* __restrict__ partial) {
+    extern __shared__ float factor[];   // [splits][16]
     const int item = blockIdx.x, kv_head = blockIdx.y;
     const int segment = items ? items[item] : item;
     const int first_row = segment_info[segment * 4 + 0], count = segment_info[segment * 4 + 1];
@@ -403,22 +424,36 @@ __global__ void __launch_bounds__(kThreads) combine_kernel(
     const SplitPlan plan = plan_splits(start, count, window, chunk);
     if (plan.splits <= 1) return;
     const int group = q_heads / kv_heads;
+    const int rows = count * group;
     const int stride = head_dim + 2;
     const float* base = partial + (static_cast<size_t>(item) * kv_heads + kv_head) * max_splits * 16 * stride;
-    for (int idx = threadIdx.x; idx < count * group * head_dim; idx += kThreads) {
-        const int row = idx / head_dim, d = idx - row * head_dim;
+    for (int i = threadIdx.x; i < plan.splits * 16; i += kThreads) {
+        const int row = i & 15;
+        factor[i] = row < rows ? base[i * stride + head_dim] : -INFINITY;   // the split's maximum, for now
+    }
+    __syncthreads();
+    if (threadIdx.x < rows) {
+        const int row = threadIdx.x;
         float m = -INFINITY;
-        for (int s = 0; s < plan.splits; ++s) m = fmaxf(m, base[(s * 16 + row) * stride + head_dim]);
-        float l = 0.0f, acc = 0.0f;
+        for (int s = 0; s < plan.splits; ++s) m = fmaxf(m, factor[s * 16 + row]);
+        float l = 0.0f;
         for (int s = 0; s < plan.splits; ++s) {
-            const float* p = base + (s * 16 + row) * stride;
-            const float f = p[head_dim] == -INFINITY ? 0.0f : exp2f(p[head_dim] - m);
-            l += p[head_dim + 1] * f;
-            acc += p[d] * f;
+            const float ms = factor[s * 16 + row];
+            const float f = ms == -INFINITY ? 0.0f : exp2f(ms - m);
+            l += base[(s * 16 + row) * stride + head_dim + 1] * f;
+            factor[s * 16 + row] = f;
         }
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        for (int s = 0; s < plan.splits; ++s) factor[s * 16 + row] *= inv;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < rows * head_dim; idx += kThreads) {
+        const int row = idx / head_dim, d = idx - row * head_dim;
+        float acc = 0.0f;
+#pragma unroll 4
+        for (int s = 0; s < plan.splits; ++s) acc = fmaf(base[(s * 16 + row) * stride + d], factor[s * 16 + row], acc);
         const int token = row / group, head = kv_head * group + row % group;
-        out[static_cast<size_t>(first_row + token) * ldo + static_cast<size_t>(head) * head_dim + d] =
-            __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+        out[static_cast<size_t>(first_row + token) * ldo + static_cast<size_t>(head) * head_dim + d] = __float2bfloat16_rn(acc);
     }
 }
 
@@ -450,7 +485,7 @@ __global__ void __launch_bounds__(kThreads) prefill_kernel(
     const int n_tiles = (last_pos + 1 - key_begin + kTileKeys - 1) / kTileKeys;
 
     CacheView view{cache, block_table + static_cast<size_t>(segment) * table_stride, num_pages, page_size,
-                   kv_heads, head_dim, kv_head};
+                   log2_or_minus1(page_size), kv_heads, head_dim, kv_head};
     const uint32_t smem_base = smem_u32(smem);
     auto k_stage = [&](int s) { return smem_base + s * 2 * Tile<DMAX>::kBytes; };
     auto v_stage = [&](int s) { return smem_base + s * 2 * Tile<DMAX>::kBytes + Tile<DMAX>::kBytes; };
@@ -482,32 +517,23 @@ __global__ void __launch_bounds__(kThreads) prefill_kernel(
     __syncthreads();
 
 #pragma unroll
-    for (int s = 0; s < kStages - 1; ++s) {
+    for (int s = 0; s < kPrefillStages - 1; ++s) {
         if (s < n_tiles) load_tile<DMAX>(view, key_begin + s * kTileKeys, first_key, last_pos, k_stage(s), v_stage(s), &bad_page);
         cp_async_commit();
     }
     for (int it = 0; it < n_tiles; ++it) {
-        cp_async_wait<kStages - 2>();
+        cp_async_wait<kPrefillStages - 2>();
         __syncthreads();
-        const int next = it + kStages - 1;
+        const int next = it + kPrefillStages - 1;
         if (next < n_tiles)
-            load_tile<DMAX>(view, key_begin + next * kTileKeys, first_key, last_pos, k_stage(next % kStages),
-                            v_stage(next % kStages), &bad_page);
+            load_tile<DMAX>(view, key_begin + next * kTileKeys, first_key, last_pos, k_stage(next % kPrefillStages),
+                            v_stage(next % kPrefillStages), &bad_page);
         cp_async_commit();
-        const int stage = it % kStages;
+        const int stage = it % kPrefillStages;
         const int key0 = key_begin + it * kTileKeys;
         if (warp_active && key0 <= warp_last && key0 + kTileKeys - 1 >= warp_lo_min) {
             float s[8][4] = {};
-#pragma unroll
-            for (int nb = 0; nb < 4; ++nb) {
-                float pair[2][4] = {};
-                qk_16keys<DMAX>(pair, qf, k_stage(stage), nb * 16, dim_steps);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    s[nb * 2][j] = pair[0][j];
-                    s[nb * 2 + 1][j] = pair[1][j];
-                }
-            }
+            qk_keys<DMAX, 4>(s, qf, k_stage(stage), 0, dim_steps);
             const bool need_mask = key0 + kTileKeys - 1 > warp_first || key0 < warp_lo_max;
             uint32_t p[4][4];
             softmax_step<DMAX, 8>(s, st, o, p, key0, lo, hi, scale_log2, need_mask);
@@ -537,8 +563,8 @@ __global__ void __launch_bounds__(kThreads) prefill_kernel(
 }
 
 template <int DMAX>
-constexpr size_t tile_smem() {
-    return static_cast<size_t>(kStages) * 2 * Tile<DMAX>::kBytes;
+constexpr size_t tile_smem(int stages) {
+    return static_cast<size_t>(stages) * 2 * Tile<DMAX>::kBytes;
 }
 
 template <typename Kernel>
@@ -579,7 +605,7 @@ MLR_API int mlr_attention_decode_bf16(const void* q, int ldq, void* out, int ldo
     if (int e = check_common("attention_decode_bf16", q_heads, kv_heads, head_dim, page_size, num_pages, window, ldq, ldo)) return e;
     MLR_REQUIRE(q_heads / kv_heads <= 16, "attention_decode_bf16: %d query heads per kv head exceed the 16 rows of a block", q_heads / kv_heads);
     MLR_REQUIRE(chunk > 0 && chunk % kTileKeys == 0, "attention_decode_bf16: chunk %d is not a positive multiple of %d", chunk, kTileKeys);
-    MLR_REQUIRE(max_splits >= 1 && max_splits <= 65535 && (max_splits == 1 || partial), "attention_decode_bf16: bad split count or missing scratch");
+    MLR_REQUIRE(max_splits >= 1 && max_splits <= 512 && (max_splits == 1 || partial), "attention_decode_bf16: the split count must be in [1, 512], with scratch when above 1");
     MLR_REQUIRE(n_items >= 0 && n_items <= 65535, "attention_decode_bf16: more than 65535 requests in one launch");
     if (n_items == 0) return 0;
     const dim3 grid(max_splits, kv_heads, n_items);
@@ -587,7 +613,7 @@ MLR_API int mlr_attention_decode_bf16(const void* q, int ldq, void* out, int ldo
 #define MLR_LAUNCH(DMAX)                                                                                           \
     do {                                                                                                           \
         const size_t merge = sizeof(float) * (4 * 16 * DMAX + 4 * 16 * 2);                                         \
-        const size_t bytes = tile_smem<DMAX>() > merge ? tile_smem<DMAX>() : merge;                                \
+        const size_t bytes = tile_smem<DMAX>(kDecodeStages) > merge ? tile_smem<DMAX>(kDecodeStages) : merge;                                \
         if (int e = allow_smem(decode_splitkv_kernel<DMAX>, bytes, "attention_decode_bf16")) return e;            \
         decode_splitkv_kernel<DMAX><<<grid, kThreads, bytes, stream>>>(                                            \
             static_cast<const __nv_bfloat16*>(q), ldq, static_cast<__nv_bfloat16*>(out), ldo,                      \
@@ -600,7 +626,7 @@ MLR_API int mlr_attention_decode_bf16(const void* q, int ldq, void* out, int ldo
 #undef MLR_LAUNCH
     if (int e = mlr_launched("attention_decode_bf16")) return e;
     if (max_splits > 1) {
-        combine_kernel<<<combine_grid, kThreads, 0, stream>>>(static_cast<__nv_bfloat16*>(out), ldo, items, segment_info,
+        combine_kernel<<<combine_grid, kThreads, sizeof(float) * 16 * max_splits, stream>>>(static_cast<__nv_bfloat16*>(out), ldo, items, segment_info,
                                                              q_heads, kv_heads, head_dim, window, chunk, max_splits, partial);
         return mlr_launched("attention_decode_bf16 combine");
     }
@@ -619,8 +645,8 @@ MLR_API int mlr_attention_prefill_bf16(const void* q, int ldq, void* out, int ld
     const dim3 grid(n_tiles, q_heads);
 #define MLR_LAUNCH(DMAX)                                                                                          \
     do {                                                                                                          \
-        if (int e = allow_smem(prefill_kernel<DMAX>, tile_smem<DMAX>(), "attention_prefill_bf16")) return e;     \
-        prefill_kernel<DMAX><<<grid, kThreads, tile_smem<DMAX>(), stream>>>(                                      \
+        if (int e = allow_smem(prefill_kernel<DMAX>, tile_smem<DMAX>(kPrefillStages), "attention_prefill_bf16")) return e; \
+        prefill_kernel<DMAX><<<grid, kThreads, tile_smem<DMAX>(kPrefillStages), stream>>>(                        \
             static_cast<const __nv_bfloat16*>(q), ldq, static_cast<__nv_bfloat16*>(out), ldo,                     \
             static_cast<const __nv_bfloat16*>(cache), num_pages, tiles, segment_info, block_table, table_stride,  \
             page_size, q_heads, kv_heads, head_dim, window, scale, status);                                       \

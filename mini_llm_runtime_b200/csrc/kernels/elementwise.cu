@@ -31,6 +31,28 @@ __global__ void embed_gather_kernel(float* __restrict__ out, const W* __restrict
     for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = mlr_load(src, i);
 }
 
+// Eight values per thread: one 16-byte load of bf16 (or two of float), two 16-byte stores.
+template <typename W>
+__global__ void embed_gather_vec8_kernel(float* __restrict__ out, const W* __restrict__ table,
+                                         const int* __restrict__ ids, int width, int vocab, int* status) {
+    const int row = blockIdx.x;
+    const int id = ids[row];
+    float4* dst = reinterpret_cast<float4*>(out + static_cast<size_t>(row) * width);
+    const bool bad = id < 0 || id >= vocab;
+    if (bad && threadIdx.x == 0 && status) atomicOr(status, MLR_STATUS_BAD_INDEX);
+    const W* src = table + static_cast<size_t>(bad ? 0 : id) * width;
+    for (int i = threadIdx.x; i < width / 8; i += blockDim.x) {
+        float v[8];
+        mlr_load8(src + i * 8, v);
+        if (bad) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = 0.0f;
+        }
+        dst[2 * i] = make_float4(v[0], v[1], v[2], v[3]);
+        dst[2 * i + 1] = make_float4(v[4], v[5], v[6], v[7]);
+    }
+}
+
 // ------------------------------------------------------------------ rms norm
 // out[r,:] = rmsnorm(h[row,:] + delta[row,:]) * w, row = rows ? rows[r] : r.
 // With write_back the sum replaces h[row,:] (the residual stream moves on).
@@ -55,6 +77,59 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ 
         const float x = dr ? hr[i] + dr[i] : hr[i];
         if (write_back && dr) hr[i] = x;
         mlr_store(dst, i, (x * scale) * mlr_load(weight, i));
+    }
+}
+
+// The same for widths that are multiples of 4 and fit 16 values per thread: each thread
+// keeps its values in registers between the two passes, so the row is read once and every
+// load of the row is in flight at the same time.  One block per row.
+template <typename T, typename W>
+__global__ void __launch_bounds__(1024) rmsnorm_cached_kernel(float* __restrict__ h, const float* __restrict__ delta,
+                                                             const W* __restrict__ weight, T* __restrict__ out,
+                                                             const int* __restrict__ rows, int width, float eps,
+                                                             int write_back) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const size_t row = rows ? static_cast<size_t>(rows[r]) : static_cast<size_t>(r);
+    float4* hr = reinterpret_cast<float4*>(h + row * width);
+    const float4* dr = delta ? reinterpret_cast<const float4*>(delta + row * width) : nullptr;
+    const int quads = width >> 2;
+    float4 x[4];
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        x[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < quads) {
+            x[k] = hr[i];
+            if (dr) {
+                const float4 d = dr[i];
+                x[k].x += d.x; x[k].y += d.y; x[k].z += d.z; x[k].w += d.w;
+            }
+        }
+    }
+    // A fixed order of summation per thread, then a fixed tree over the block: the result
+    // depends on the width alone, not on how many rows the launch has.
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        sum = fmaf(x[k].x, x[k].x, sum);
+        sum = fmaf(x[k].y, x[k].y, sum);
+        sum = fmaf(x[k].z, x[k].z, sum);
+        sum = fmaf(x[k].w, x[k].w, sum);
+    }
+    sum = mlr_block_sum(sum, scratch);
+    const float scale = 1.0f / sqrtf(sum / static_cast<float>(width) + eps);
+    T* dst = out + static_cast<size_t>(r) * width;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < quads) {
+            if (write_back && dr) hr[i] = x[k];
+            float w[4];
+            mlr_load4(weight + i * 4, w);
+            mlr_store4(dst + i * 4, (x[k].x * scale) * w[0], (x[k].y * scale) * w[1], (x[k].z * scale) * w[2],
+                       (x[k].w * scale) * w[3]);
+        }
     }
 }
 
@@ -181,6 +256,22 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
     }
 }
 
+template <typename T>
+__global__ void swiglu_vec8_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inter) {
+    const int per_row = inter >> 3;
+    const size_t total = static_cast<size_t>(rows) * per_row;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t r = i / per_row, c = (i - r * per_row) * 8;
+        float g[8], u[8];
+        mlr_load8(gate_up + r * 2 * inter + c, g);
+        mlr_load8(gate_up + r * 2 * inter + inter + c, u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) g[k] = (g[k] / (1.0f + expf(-g[k]))) * u[k];
+        mlr_store8(out + r * inter + c, g);
+    }
+}
+
 int row_threads(int width) {
     int t = 32;
     while (t < 256 && t * 4 < width) t <<= 1;
@@ -194,7 +285,12 @@ MLR_API int mlr_embed_gather(float* out, const void* table, int w_bf16, const in
     MLR_REQUIRE(rows >= 0 && width > 0 && vocab > 0, "embed_gather: bad sizes rows=%d width=%d vocab=%d", rows, width, vocab);
     if (rows == 0) return 0;
     const int threads = row_threads(width);
-    if (w_bf16)
+    const bool vec = width % 8 == 0 && reinterpret_cast<uintptr_t>(table) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+    if (vec && w_bf16)
+        embed_gather_vec8_kernel<<<rows, row_threads(width / 2), 0, stream>>>(out, static_cast<const __nv_bfloat16*>(table), ids, width, vocab, status);
+    else if (vec)
+        embed_gather_vec8_kernel<<<rows, row_threads(width / 2), 0, stream>>>(out, static_cast<const float*>(table), ids, width, vocab, status);
+    else if (w_bf16)
         embed_gather_kernel<<<rows, threads, 0, stream>>>(out, static_cast<const __nv_bfloat16*>(table), ids, width, vocab, status);
     else
         embed_gather_kernel<<<rows, threads, 0, stream>>>(out, static_cast<const float*>(table), ids, width, vocab, status);
@@ -207,9 +303,22 @@ MLR_API int mlr_rmsnorm(float* h, const float* delta, const void* weight, int w_
     MLR_REQUIRE(eps > 0.0f, "rmsnorm: eps must be positive, got %g", static_cast<double>(eps));
     if (count == 0) return 0;
     const int threads = row_threads(width);
+    // Register-cached path: width a multiple of 4, at most 16 values per thread of a block
+    // of up to 1024 threads, 16-byte aligned rows.
+    int cached_threads = 32;
+    while (cached_threads < 1024 && cached_threads * 4 < width) cached_threads <<= 1;
+    const bool cached = width % 4 == 0 && width <= cached_threads * 16 && reinterpret_cast<uintptr_t>(h) % 16 == 0 &&
+                        (!delta || reinterpret_cast<uintptr_t>(delta) % 16 == 0) &&
+                        reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(weight) % 16 == 0;
 #define MLR_LAUNCH(T, W)                                                                                   \
-    rmsnorm_kernel<T, W><<<count, threads, 0, stream>>>(h, delta, static_cast<const W*>(weight),          \
-                                                         static_cast<T*>(out), rows, width, eps, write_back)
+    do {                                                                                                   \
+        if (cached)                                                                                        \
+            rmsnorm_cached_kernel<T, W><<<count, cached_threads, 0, stream>>>(                             \
+                h, delta, static_cast<const W*>(weight), static_cast<T*>(out), rows, width, eps, write_back); \
+        else                                                                                               \
+            rmsnorm_kernel<T, W><<<count, threads, 0, stream>>>(h, delta, static_cast<const W*>(weight),  \
+                                                                 static_cast<T*>(out), rows, width, eps, write_back); \
+    } while (0)
     if (act_bf16 && w_bf16) MLR_LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else if (act_bf16) MLR_LAUNCH(__nv_bfloat16, float);
     else if (w_bf16) MLR_LAUNCH(float, __nv_bfloat16);
@@ -260,6 +369,16 @@ MLR_API int mlr_swiglu(const void* gate_up, void* out, int act_bf16, int rows, i
     MLR_REQUIRE(rows >= 0 && inter > 0, "swiglu: bad sizes rows=%d inter=%d", rows, inter);
     if (rows == 0) return 0;
     const size_t total = static_cast<size_t>(rows) * inter;
+    const bool vec = inter % 8 == 0 && reinterpret_cast<uintptr_t>(gate_up) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+    if (vec) {
+        const size_t work = total / 8;
+        const int vblocks = static_cast<int>(work / 256 + 1 < 148 * 16 ? work / 256 + 1 : 148 * 16);
+        if (act_bf16)
+            swiglu_vec8_kernel<<<vblocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, inter);
+        else
+            swiglu_vec8_kernel<<<vblocks, 256, 0, stream>>>(static_cast<const float*>(gate_up), static_cast<float*>(out), rows, inter);
+        return mlr_launched("swiglu");
+    }
     const int blocks = static_cast<int>(total / 1024 + 1 < 148 * 16 ? total / 1024 + 1 : 148 * 16);
     if (act_bf16)
         swiglu_kernel<<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, inter);

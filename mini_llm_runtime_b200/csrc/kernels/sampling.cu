@@ -37,14 +37,28 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restric
     const int row = blockIdx.x;
     const float* x = logits + static_cast<size_t>(row) * ld;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int run = (vocab + kThreads - 1) / kThreads;
+    const int run = ((vocab + kThreads - 1) / kThreads + 3) & ~3;   // a multiple of 4: runs start on 16-byte boundaries
     const int begin = min(vocab, static_cast<int>(threadIdx.x) * run), end = min(vocab, begin + run);
+    const bool vector = (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
     if (threadIdx.x == 0) nonfinite = 0;
     __syncthreads();
 
     Best best{-INFINITY, 0x7fffffff};
     bool bad = false;
-    for (int i = begin; i < end; ++i) {
+    int i = begin;
+    if (vector) {
+#pragma unroll 4
+        for (; i + 3 < end; i += 4) {
+            const float4 q = *reinterpret_cast<const float4*>(x + i);
+            const float v[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                bad |= !isfinite(v[k]);
+                if (v[k] > best.value) best = Best{v[k], i + k};
+            }
+        }
+    }
+    for (; i < end; ++i) {
         const float v = x[i];
         bad |= !isfinite(v);
         if (v > best.value) best = Best{v, i};

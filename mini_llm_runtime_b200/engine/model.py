@@ -108,6 +108,14 @@ class Model:
         self._pinned_next = 0
         self._bound = False
         self.last_h2d_bytes = 0
+        # Decode steps are replayed from CUDA graphs unless a mixer keeps state that a
+        # repeated run would advance twice (capturing runs a step more than once).
+        self.use_graphs = True
+        self._graphable = all(r.state_need is None for r in self.runs)
+        self.graph_bucket_blocks = 64          # table width of a graph, in blocks
+        self.max_graphs = 48
+        self._graphs = {}
+        self._graph_pool = None
 
     # ------------------------------------------------------------------ weights
     def _all_parts(self):
@@ -134,6 +142,7 @@ class Model:
         for part in self._all_parts():
             part.bind(tensors, self.rt)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.rt.device)
+        self._graph_pool = torch.cuda.graph_pool_handle()
         self._bound = True
 
     # ------------------------------------------------------------------ cache
@@ -218,27 +227,43 @@ class Model:
             row += count
         return segments, row
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Runs the entries' tokens as one batch from the cache and returns the float32
         logits [wanted, vocab] in the order of the entries and of each entry's `want`
         (None if nothing is wanted).  Raises `OutOfPages` before any device work if
-        the cache cannot hold the step."""
+        the cache cannot hold the step.
+
+        `device_tokens` (int32 on the device, one id per row) replaces the entries'
+        token values, whose count still says how many rows each entry brings: a
+        decode loop can feed sampled ids back without a round trip to the host.
+
+        A step of single tokens that wants every row's logits is replayed from a CUDA
+        graph (captured on first use per batch size and context bucket).  Its logits
+        live in the graph's memory: read or sample them before the next step."""
         segments, rows = self._validate(entries)
         n = len(segments)
         vocab = self.plan.vocab_size
         tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
-        if tokens.min() < 0 or tokens.max() >= vocab:
+        if device_tokens is None and (tokens.min() < 0 or tokens.max() >= vocab):
             raise StepError(f"a token id is outside the vocabulary of {vocab}")
+        if device_tokens is not None and (device_tokens.dtype is not torch.int32 or device_tokens.numel() != rows):
+            raise StepError("device_tokens must be int32 with one id per row of the step")
         want_rows = [s.row + w for s, e in zip(segments, entries) for w in e.want]
+        all_single = all(s.count == 1 for s in segments)
+        graphed = self.use_graphs and self._graphable and all_single and len(want_rows) == rows
         self.cache.prepare([s.slot for s in segments], [s.count for s in segments])
         try:
+            page = self.cache_config.page_size
             max_context = max(s.start + s.count for s in segments)
-            columns = (max_context + self.cache_config.page_size - 1) // self.cache_config.page_size
+            columns = (max_context + page - 1) // page
+            if graphed:
+                columns = min(-(-columns // self.graph_bucket_blocks) * self.graph_bucket_blocks, self.cache.max_blocks)
             n_groups = len(self.group_windows)
             # One packed int32 buffer: ids | positions | segment_of_row | info[n,4] | slots | want | tables
             sizes = [rows, rows, rows, 4 * n, n, len(want_rows)] + [n * columns] * n_groups
             offsets = np.concatenate([[0], np.cumsum(sizes)])
-            host = self._pinned_buffer(int(offsets[-1]))
+            total = int(offsets[-1])
+            host = self._pinned_buffer(total)
             view = host.numpy()
             view[offsets[0]:offsets[1]] = tokens
             for i, s in enumerate(segments):
@@ -247,27 +272,73 @@ class Model:
                 view[offsets[3] + 4 * i: offsets[3] + 4 * i + 4] = (s.row, s.count, s.start, s.slot)
                 view[offsets[4] + i] = s.slot
             view[offsets[5]:offsets[6]] = want_rows
+            slots = [s.slot for s in segments]
             for g in range(n_groups):
                 table = host[offsets[6 + g]:offsets[7 + g]].view(n, columns)
-                self.cache.fill_table(g, [s.slot for s in segments], table, columns)
-            total = int(offsets[-1])
-            device = torch.empty(total, dtype=torch.int32, device=self.rt.device)
-            device.copy_(host[:total], non_blocking=True)
+                if graphed:
+                    table.fill_(-1)
+                self.cache.fill_table(g, slots, table, min(columns, self.cache.max_blocks))
             self.last_h2d_bytes = 4 * total
-            self._pinned[self._pinned_current][1].record()
-            part = lambda k: device[offsets[k]:offsets[k + 1]]
-            step = StepContext(
-                rt=self.rt, num_rows=rows, segments=segments, token_ids=part(0), positions=part(1),
-                segment_of_row=part(2), segment_info=part(3).view(n, 4), slots=part(4),
-                tables={g: part(6 + g).view(n, columns) for g in range(n_groups)},
-                page_size=self.cache_config.page_size, status=self.status,
-                max_count=max(s.count for s in segments), max_context=max_context,
-                all_single=all(s.count == 1 for s in segments))
-            logits = self._forward(step, part(5) if want_rows else None)
+
+            def context_on(device: torch.Tensor, bound: Optional[int]) -> StepContext:
+                part = lambda k: device[offsets[k]:offsets[k + 1]]
+                return StepContext(
+                    rt=self.rt, num_rows=rows, segments=segments, token_ids=part(0), positions=part(1),
+                    segment_of_row=part(2), segment_info=part(3).view(n, 4), slots=part(4),
+                    tables={g: part(6 + g).view(n, columns) for g in range(n_groups)},
+                    page_size=page, status=self.status, max_count=max(s.count for s in segments),
+                    max_context=max_context, all_single=all_single, context_bound=bound)
+
+            if graphed:
+                logits = self._replay(host[:total], rows, columns, context_on, offsets, device_tokens)
+            else:
+                device = torch.empty(total, dtype=torch.int32, device=self.rt.device)
+                device.copy_(host[:total], non_blocking=True)
+                self._pinned[self._pinned_current][1].record()
+                if device_tokens is not None:
+                    device[:rows].copy_(device_tokens)
+                step = context_on(device, None)
+                logits = self._forward(step, device[offsets[5]:offsets[6]] if want_rows else None)
         except BaseException:
             self.cache.discard()
             raise
         self.cache.commit()
+        return logits
+
+    def _replay(self, host: torch.Tensor, rows: int, columns: int, context_on, offsets, device_tokens):
+        """Decode steps from a CUDA graph: one graph per (batch size, table width).  The
+        graph reads its metadata from a fixed device buffer that is refreshed before
+        every replay; launch shapes that depend on the context (how the keys are split)
+        are planned for the bucket's upper bound and the kernels read the true lengths
+        from the metadata."""
+        key = (rows, columns)
+        entry = self._graphs.get(key)
+        if entry is None:
+            if len(self._graphs) >= self.max_graphs:
+                self._graphs.pop(next(iter(self._graphs)))
+            static = torch.empty(host.numel(), dtype=torch.int32, device=self.rt.device)
+            static.copy_(host, non_blocking=True)
+            if device_tokens is not None:
+                static[:rows].copy_(device_tokens)
+            step = context_on(static, columns * self.cache_config.page_size)
+            want = static[offsets[5]:offsets[6]]
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self._forward(step, want)          # warm-up outside the capture (the step is idempotent)
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            step.scratch.clear()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                logits = self._forward(step, want)
+            entry = (graph, static, logits)
+            self._graphs[key] = entry
+        graph, static, logits = entry
+        static.copy_(host, non_blocking=True)
+        self._pinned[self._pinned_current][1].record()
+        if device_tokens is not None:
+            static[:rows].copy_(device_tokens)
+        graph.replay()
         return logits
 
     def _forward(self, step: StepContext, want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:

@@ -65,8 +65,11 @@ def _plan(step, group: int, kv_heads: int, window: int) -> _Plan:
         spans = []
         for i in small:
             s = step.segments[i]
-            first = max(0, s.start - window + 1) if window else 0
-            spans.append(s.start + s.count - (first // _TILE) * _TILE)
+            if step.context_bound is None:
+                first = max(0, s.start - window + 1) if window else 0
+                spans.append(s.start + s.count - (first // _TILE) * _TILE)
+            else:       # a captured step: plan for the longest context the graph may be replayed with
+                spans.append(min(step.context_bound, window + s.count + _TILE) if window else step.context_bound)
         plan.chunk, plan.max_splits = split_plan(spans, len(small) * kv_heads)
     if large:
         tiles = [(i, t) for i in large for t in range(0, step.segments[i].count, _TILE)]

@@ -71,6 +71,9 @@ class StepContext:
     max_count: int = 0                # longest segment of the step
     max_context: int = 0              # largest position + 1 of the step
     all_single: bool = False          # every segment is one token (a pure decode step)
+    context_bound: Optional[int] = None   # set when the step is captured into a CUDA graph: launch shapes
+                                          # must be planned for contexts up to this bound, not for the
+                                          # lengths of the step at hand
     scratch: Dict[str, object] = field(default_factory=dict)   # per-step memo for kernels' plans
 
 

@@ -41,3 +41,35 @@ def test_last_32_one_by_one(case, dtype):
     model = engine_model(folder, dtype, num_pages=32)
     got = run_portions(model, tokens, [len(tokens) - 32, 1])
     assert_close(got, want, dtype, "prompt then 32 single tokens")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_from_graphs_and_eagerly(case, dtype):
+    """Token by token from the first token on, past page edges and graph buckets; the
+    graph replay and the plain launches give the same bits."""
+    from mini_llm_runtime_b200.engine.model import StepEntry
+    folder, config, tokens, want = case
+    outs = {}
+    for graphs in (True, False):
+        model = engine_model(folder, dtype, num_pages=32)
+        model.use_graphs = graphs
+        model.graph_bucket_blocks = 2          # new graphs every 32 tokens
+        slot = model.open_request()
+        rows = [model.step([StepEntry(slot, [t], [0])]).float().cpu() for t in tokens]
+        model.check_status()
+        outs[graphs] = torch.cat(rows)
+        assert bool(model._graphs) == graphs
+    assert_close(outs[True], want, dtype, "one token at a time")
+    assert torch.equal(outs[True], outs[False])
+
+
+def test_device_tokens_feed_the_next_step(case):
+    from mini_llm_runtime_b200.engine.model import StepEntry
+    folder, config, tokens, want = case
+    model = engine_model(folder, "float32", num_pages=32)
+    slot = model.open_request()
+    model.step([StepEntry(slot, tokens[:20], [])])
+    for p in range(20, 30):
+        ids = torch.tensor([tokens[p]], dtype=torch.int32, device="cuda:0")
+        logits = model.step([StepEntry(slot, [0], [0])], device_tokens=ids)
+        assert_close(logits.float().cpu(), want[p:p + 1], "float32", f"position {p}")
