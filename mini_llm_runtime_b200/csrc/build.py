@@ -133,6 +133,14 @@ def _compile(name: str, out: str, command: List[str], position: str) -> None:
             os.remove(tmp)
         raise NativeBuildError(f"building {name} failed (exit {proc.returncode}):\n  {' '.join(command)} <out>\n{output}")
     os.replace(tmp, out)
+    # Older builds of the same library (other source hashes) are of no use any more.
+    stem = os.path.basename(out).rsplit("-", 1)[0] + "-"
+    for other in os.listdir(os.path.dirname(out)):
+        if other.startswith(stem) and other.endswith(".so") and other != os.path.basename(out):
+            try:
+                os.remove(os.path.join(os.path.dirname(out), other))
+            except OSError:
+                pass
     _say(f"built {name} in {time.time() - started:.1f} s")
 
 

@@ -24,6 +24,8 @@
 // materialised score matrix (src/minillm/cuda/attention.cu:97-218).
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace {
 
 constexpr int kTileKeys = 64;
@@ -78,6 +80,53 @@ struct Tile {
     }
 };
 
+// The decode kernel's tiles are filled by bulk copies of whole key rows, which cannot
+// permute chunks; there each row is padded by 16 bytes instead.  With a pitch of
+// DMAX*2 + 16 bytes the 8 rows of an ldmatrix start 4 banks apart: no conflicts.
+template <int DMAX>
+struct PaddedTile {
+    static constexpr int kPitch = DMAX * 2 + 16;
+    static constexpr int kBytes = kTileKeys * kPitch;
+    __device__ static __forceinline__ uint32_t offset(int row, int chunk) { return row * kPitch + (chunk << 4); }
+};
+
+// ---------------------------------------------------------------- mbarrier and bulk copies
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Waits for a phase of a barrier, but not for ever: after about two seconds it gives up and
+// returns false (the caller then flags the fault and leaves).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - start > 4000000000LL) return false;
+    }
+    return true;
+}
+// One row of a tile: `bytes` (a multiple of 16) from global to shared memory, completion
+// counted on `bar`.
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
 struct CacheView {
     const __nv_bfloat16* base;   // [page][2][kv_heads][page_size][head_dim]
     const int* table;            // this request's block table row
@@ -90,46 +139,64 @@ __host__ __device__ inline int log2_or_minus1(int v) {
     return (1 << s) == v ? s : -1;
 }
 
+// Copying a 64-key tile: warp w copies keys 16w .. 16w+15.  Consecutive lanes copy
+// consecutive 16-byte chunks of a key's row, so every 32-byte sector is asked for once.
+// Each lane looks up the page of key 16w + (lane & 15) one iteration ahead
+// (lookup_page); the page of the row a lane copies comes from that lane by shuffle.
+__device__ __forceinline__ int lookup_page(const CacheView& c, int tile_start, int first_key, int last_key) {
+    const int key = tile_start + ((threadIdx.x >> 5) << 4) + (threadIdx.x & 15);
+    if (key < first_key || key > last_key) return -1;
+    const int block = c.page_shift >= 0 ? key >> c.page_shift : key / c.page_size;
+    return __ldg(c.table + block);
+}
+
 // Loads keys [tile_start, tile_start + 64) of K and V into one stage.  Keys outside
-// [first_key, last_key] are zero-filled.  Called by all 128 threads of the block: two
-// threads per key, each copying half of the key's K row and half of its V row, so a
-// thread looks its page up once per tile.
+// [first_key, last_key] are zero-filled.  Called by all 128 threads of the block.
+// `page` is the thread's lookup_page() result for this tile.
 template <int DMAX>
-__device__ __forceinline__ void load_tile(const CacheView& c, int tile_start, int first_key, int last_key,
+__device__ __forceinline__ void load_tile(const CacheView& c, int tile_start, int first_key, int last_key, int page,
                                           uint32_t k_smem, uint32_t v_smem, int* bad_page) {
-    const int row = threadIdx.x >> 1, half = threadIdx.x & 1;
-    const int half_chunks = c.head_dim >> 4;            // 16-byte chunks in half a row
-    const int key = tile_start + row;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int chunks = c.head_dim >> 3;                 // 16-byte chunks in a row
     const size_t head_elems = static_cast<size_t>(c.page_size) * c.head_dim;
-    const __nv_bfloat16* src = c.base;
-    int bytes = 0;
-    if (key >= first_key && key <= last_key) {
-        const int block = c.page_shift >= 0 ? key >> c.page_shift : key / c.page_size;
-        const int in_page = c.page_shift >= 0 ? key & (c.page_size - 1) : key - block * c.page_size;
-        const int page = __ldg(c.table + block);
-        if (page >= 0 && page < c.num_pages) {
-            src = c.base + (static_cast<size_t>(page) * 2 * c.kv_heads + c.kv_head) * head_elems +
-                  static_cast<size_t>(in_page) * c.head_dim + half * half_chunks * 8;
-            bytes = 16;
-        } else {
-            *bad_page = 1;
-        }
-    }
-    const __nv_bfloat16* vsrc = bytes ? src + head_elems * c.kv_heads : src;
+    const size_t value_shift = head_elems * c.kv_heads;
+    const int total = 16 * chunks;                      // chunks this warp copies per matrix
+    const bool swizzled = mlr_cache_swizzled(true, c.head_dim);
 #pragma unroll
     for (int j = 0; j < DMAX / 16; ++j) {
-        if (j < half_chunks) {
-            const uint32_t off = Tile<DMAX>::offset(row, half * half_chunks + j);
-            cp_async_16(k_smem + off, bytes ? src + j * 8 : src, bytes);
-            cp_async_16(v_smem + off, bytes ? vsrc + j * 8 : vsrc, bytes);
+        const int idx = j * 32 + lane;
+        int local = idx / chunks;                       // key within the warp's 16 (chunks is 2..32)
+        const int chunk = idx - local * chunks;
+        const bool active = idx < total;
+        local = active ? local : 0;
+        const int row_page = __shfl_sync(0xffffffffu, page, local);
+        if (!active) continue;
+        const int row = warp * 16 + local, key = tile_start + row;
+        const __nv_bfloat16* src = c.base;
+        int bytes = 0;
+        if (key >= first_key && key <= last_key) {
+            if (row_page >= 0 && row_page < c.num_pages) {
+                const int in_page = c.page_shift >= 0 ? key & (c.page_size - 1) : key % c.page_size;
+                src = c.base + (static_cast<size_t>(row_page) * 2 * c.kv_heads + c.kv_head) * head_elems +
+                      static_cast<size_t>(in_page) * c.head_dim + chunk * 8;
+                bytes = 16;
+            } else {
+                *bad_page = 1;
+            }
         }
+        // A swizzled cache already stores chunk c at c ^ (position & 7), which is where the
+        // tile wants it (row & 7 == position & 7): copy chunk for chunk.  A plain cache is
+        // permuted on the way in.
+        const uint32_t off = swizzled ? row * Tile<DMAX>::kPitch + (chunk << 4) : Tile<DMAX>::offset(row, chunk);
+        cp_async_16(k_smem + off, src, bytes);
+        cp_async_16(v_smem + off, bytes ? src + value_shift : src, bytes);
     }
 }
 
 // One warp: S[16 rows x 16*NB keys] += Q[16 x D] K^T for keys [key0, key0 + 16*NB) of a tile.
 // The 2*NB accumulators are independent chains; walking the head dimension in the outer
 // loop keeps them all in flight.
-template <int DMAX, int NB>
+template <int DMAX, int NB, typename Layout = Tile<DMAX>>
 __device__ __forceinline__ void qk_keys(float (&s)[2 * NB][4], const uint32_t (&q)[DMAX / 16][4], uint32_t k_smem,
                                         int key0, int dim_steps) {
     const int lane = threadIdx.x & 31;
@@ -141,7 +208,7 @@ __device__ __forceinline__ void qk_keys(float (&s)[2 * NB][4], const uint32_t (&
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) {
                 uint32_t b[4];
-                ldmatrix_x4(b, k_smem + Tile<DMAX>::offset(row + nb * 16, kd * 2 + chunk_in_step));
+                ldmatrix_x4(b, k_smem + Layout::offset(row + nb * 16, kd * 2 + chunk_in_step));
                 mma_bf16(s[2 * nb], q[kd], b[0], b[1]);
                 mma_bf16(s[2 * nb + 1], q[kd], b[2], b[3]);
             }
@@ -150,7 +217,7 @@ __device__ __forceinline__ void qk_keys(float (&s)[2 * NB][4], const uint32_t (&
 }
 
 // One warp: O[16 rows x D] += P[16 x 16 keys] V for keys [key0, key0+16) of a tile.
-template <int DMAX>
+template <int DMAX, typename Layout = Tile<DMAX>>
 __device__ __forceinline__ void pv_16keys(float (&o)[DMAX / 8][4], const uint32_t (&p)[4], uint32_t v_smem,
                                           int key0, int dim_steps) {
     const int lane = threadIdx.x & 31;
@@ -160,7 +227,7 @@ __device__ __forceinline__ void pv_16keys(float (&o)[DMAX / 8][4], const uint32_
     for (int dn = 0; dn < DMAX / 16; ++dn) {
         if (dn < dim_steps) {
             uint32_t b[4];
-            ldmatrix_x4_trans(b, v_smem + Tile<DMAX>::offset(row, dn * 2 + chunk_in_pair));
+            ldmatrix_x4_trans(b, v_smem + Layout::offset(row, dn * 2 + chunk_in_pair));
             mma_bf16(o[dn * 2], p, b[0], b[1]);
             mma_bf16(o[dn * 2 + 1], p, b[2], b[3]);
         }
@@ -270,19 +337,36 @@ __device__ __forceinline__ SplitPlan plan_splits(int start, int count, int windo
 }
 
 // ---------------------------------------------------------------- decode: split-KV
-// grid = (max_splits, kv_heads, items).  Row r of the block's 16 rows is token r / group,
-// query head kv_head * group + r % group.  Partial results go to `partial`
-// [item][kv_head][split][16 rows][head_dim + 2] (the last two floats: maximum in log2
-// units and sum); an item whose keys fit one split is written to `out` directly.
-template <int DMAX>
-__global__ void __launch_bounds__(kThreads) decode_splitkv_kernel(
+// grid = (max_splits, kv_heads, items), 160 threads: warps 0-3 compute, warp 4 copies.
+// Row r of the block's 16 rows is token r / group, query head kv_head * group + r % group.
+//
+// The copy warp walks the split's 64-key tiles: for each it waits until the stage is free,
+// announces the tile's bytes on the stage's "full" barrier and issues one bulk copy per key
+// row of K and of V (two rows of each per lane; a key outside the split's range copies the
+// nearest key inside, whose score is masked).  A compute warp waits for the stage, takes
+// keys 16w .. 16w+15 of the tile with its own running softmax, and releases the stage.
+// There is no block-wide barrier in the loop.  Every wait has a time limit; a wait that
+// runs out sets MLR_STATUS_TIMEOUT and the block leaves without writing a result.
+//
+// Partial results go to `partial` [item][kv_head][split][16 rows][head_dim + 2] (the last
+// two floats: maximum in log2 units and sum); an item whose keys fit one split is written
+// to `out` directly.
+constexpr int kDecodeThreads = 160;
+
+template <int DMAX, bool BLOCKS>
+__global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
     const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat16* __restrict__ out, int ldo,
     const __nv_bfloat16* __restrict__ cache, int num_pages, const int* __restrict__ items,
     const int* __restrict__ segment_info, const int* __restrict__ block_table, int table_stride,
     int page_size, int q_heads, int kv_heads, int head_dim, int window, float scale, int chunk,
     int max_splits, float* __restrict__ partial, int* status) {
+    // BLOCKS: the cache rows are stored swizzled (head size 64, 128 or 256 = DMAX), so whole
+    // page blocks are copied byte for byte into unpadded tiles.  Otherwise rows are stored
+    // plainly and are copied one by one into padded tiles.
+    using L = typename std::conditional<BLOCKS, Tile<DMAX>, PaddedTile<DMAX>>::type;
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ int bad_page;
+    __shared__ __align__(8) unsigned long long barriers[2 * kDecodeStages];
+    __shared__ int fault;      // 1: a page outside the pool, 2: a wait ran out
     const int item = blockIdx.z, kv_head = blockIdx.y, split = blockIdx.x;
     const int segment = items ? items[item] : item;
     const int first_row = segment_info[segment * 4 + 0], count = segment_info[segment * 4 + 1];
@@ -291,99 +375,198 @@ __global__ void __launch_bounds__(kThreads) decode_splitkv_kernel(
     if (split >= plan.splits) return;
     const int group = q_heads / kv_heads;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int g = lane >> 2, t = lane & 3;
     const int dim_steps = head_dim >> 4;
-    if (threadIdx.x == 0) bad_page = 0;
 
     const int key_begin = plan.base + split * chunk;
     const int key_end = min(key_begin + chunk, plan.last_key + 1);      // exclusive
+    const int first_valid = max(key_begin, plan.first_key);
     const int tiles = (key_end - key_begin + kTileKeys - 1) / kTileKeys;
 
-    CacheView view{cache, block_table + static_cast<size_t>(segment) * table_stride, num_pages, page_size,
-                   log2_or_minus1(page_size), kv_heads, head_dim, kv_head};
     const uint32_t smem_base = smem_u32(smem);
-    auto k_stage = [&](int s) { return smem_base + s * 2 * Tile<DMAX>::kBytes; };
-    auto v_stage = [&](int s) { return smem_base + s * 2 * Tile<DMAX>::kBytes + Tile<DMAX>::kBytes; };
-
-    // Rows of this thread: g and g + 8.
-    int lo[2], hi[2];
-    const __nv_bfloat16* qptr[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const int row = g + 8 * r;
-        const int token = row / group, head = kv_head * group + row % group;
-        const bool valid = token < count;
-        hi[r] = valid ? start + token : -1;
-        lo[r] = valid ? (window > 0 ? max(0, start + token - window + 1) : 0) : 0;
-        qptr[r] = valid ? q + static_cast<size_t>(first_row + token) * ldq + static_cast<size_t>(head) * head_dim : nullptr;
+    const uint32_t bar_base = smem_u32(barriers);
+    auto k_stage = [&](int s) { return smem_base + s * 2 * L::kBytes; };
+    auto v_stage = [&](int s) { return smem_base + s * 2 * L::kBytes + L::kBytes; };
+    auto full_bar = [&](int s) { return bar_base + s * 8; };
+    auto empty_bar = [&](int s) { return bar_base + (kDecodeStages + s) * 8; };
+    if (threadIdx.x == 0) {
+        fault = 0;
+        for (int s = 0; s < kDecodeStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
-    uint32_t qf[DMAX / 16][4];
-    load_q<DMAX>(qf, qptr[0], qptr[1], dim_steps);
+    __syncthreads();
 
     float o[DMAX / 8][4];
 #pragma unroll
     for (int dn = 0; dn < DMAX / 8; ++dn) o[dn][0] = o[dn][1] = o[dn][2] = o[dn][3] = 0.0f;
     RowState st;
-    const float scale_log2 = scale * kLog2e;
-    __syncthreads();
 
+    if (warp == 4) {
+        // ---------------- the copy warp
+        const int* table = block_table + static_cast<size_t>(segment) * table_stride;
+        const int page_shift = log2_or_minus1(page_size);
+        const size_t head_elems = static_cast<size_t>(page_size) * head_dim;
+        const size_t value_shift = head_elems * kv_heads;
+        const uint32_t row_bytes = head_dim * 2;
+        bool ok = true;
+        // Page of the block this lane copies in a tile (looked up one tile ahead, so that
+        // the table read is off the critical path): block = first block of the tile + lane.
+        auto tile_page = [&](int it_) {
+            const int from_ = max(key_begin + it_ * kTileKeys, first_valid);
+            const int block_ = (page_shift >= 0 ? from_ >> page_shift : from_ / page_size) + lane;
+            const int last_ = min(key_begin + (it_ + 1) * kTileKeys, key_end) - 1;
+            const int last_block_ = page_shift >= 0 ? last_ >> page_shift : last_ / page_size;
+            return (it_ < tiles && block_ <= last_block_) ? __ldg(table + block_) : -1;
+        };
+        int ahead = BLOCKS ? tile_page(0) : -1;
+        for (int it = 0; it < tiles && ok; ++it) {
+            const int stage = it % kDecodeStages;
+            if (it >= kDecodeStages) ok = mbar_wait(empty_bar(stage), ((it / kDecodeStages) - 1) & 1);
+            if (!ok) break;
+            const int tile_start = key_begin + it * kTileKeys;
+            const int my_page = ahead;
+            if (BLOCKS) ahead = tile_page(it + 1);
+            if (BLOCKS) {
+                // Keys of this tile that exist: [from, to).  Rows of V outside them are zeroed
+                // (their scores are masked, but 0 * garbage must stay 0); K may hold anything.
+                const int from = max(tile_start, first_valid), to = min(tile_start + kTileKeys, key_end);
+                if (to - from < kTileKeys) {
+                    const int quads = (head_dim * 2) >> 4;
+                    for (int i = lane; i < kTileKeys * quads; i += 32) {
+                        const int row = i / quads;
+                        if (tile_start + row < from || tile_start + row >= to)
+                            *reinterpret_cast<uint4*>(smem + (v_stage(stage) - smem_base) + row * L::kPitch + (i - row * quads) * 16) =
+                                make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    // These plain stores and the bulk copies of later tiles touch the same bytes.
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                }
+                __syncwarp();
+                if (lane == 0) mbar_expect_tx(full_bar(stage), row_bytes * 2 * (to - from));
+                __syncwarp();
+                // One copy of K and one of V per page block that the tile's keys touch.
+                const int first_block = page_shift >= 0 ? from >> page_shift : from / page_size;
+                const int last_block = page_shift >= 0 ? (to - 1) >> page_shift : (to - 1) / page_size;
+                for (int block = first_block + lane; block <= last_block; block += 32) {
+                    const int block_start = block * page_size;
+                    const int lo_key = max(block_start, from), hi_key = min(block_start + page_size, to);
+                    int page = block == first_block + lane ? my_page : __ldg(table + block);
+                    if (page < 0 || page >= num_pages) {
+                        fault = 1;
+                        page = 0;
+                    }
+                    const __nv_bfloat16* src = cache + (static_cast<size_t>(page) * 2 * kv_heads + kv_head) * head_elems +
+                                               static_cast<size_t>(lo_key - block_start) * head_dim;
+                    const uint32_t bytes = row_bytes * (hi_key - lo_key);
+                    const uint32_t dst = (lo_key - tile_start) * L::kPitch;
+                    bulk_copy(k_stage(stage) + dst, src, bytes, full_bar(stage));
+                    bulk_copy(v_stage(stage) + dst, src + value_shift, bytes, full_bar(stage));
+                }
+            } else {
+                if (lane == 0) mbar_expect_tx(full_bar(stage), row_bytes * 2 * kTileKeys);
+                __syncwarp();
 #pragma unroll
-    for (int s = 0; s < kDecodeStages - 1; ++s) {
-        if (s < tiles) load_tile<DMAX>(view, key_begin + s * kTileKeys, plan.first_key, key_end - 1, k_stage(s), v_stage(s), &bad_page);
-        cp_async_commit();
+                for (int half = 0; half < 2; ++half) {
+                    // A key outside the split's range copies the nearest key inside it (masked later).
+                    const int row = lane + 32 * half;
+                    const int key = min(max(tile_start + row, first_valid), key_end - 1);
+                    const int block = page_shift >= 0 ? key >> page_shift : key / page_size;
+                    const int in_page = page_shift >= 0 ? key & (page_size - 1) : key - block * page_size;
+                    int page = __ldg(table + block);
+                    if (page < 0 || page >= num_pages) {
+                        fault = 1;
+                        page = 0;
+                    }
+                    const __nv_bfloat16* src = cache + (static_cast<size_t>(page) * 2 * kv_heads + kv_head) * head_elems +
+                                               static_cast<size_t>(in_page) * head_dim;
+                    bulk_copy(k_stage(stage) + row * L::kPitch, src, row_bytes, full_bar(stage));
+                    bulk_copy(v_stage(stage) + row * L::kPitch, src + value_shift, row_bytes, full_bar(stage));
+                }
+            }
+        }
+        if (!ok) fault = 2;
+    } else {
+        // ---------------- compute warps
+        const int g = lane >> 2;
+        int lo[2], hi[2];
+        const __nv_bfloat16* qptr[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = g + 8 * r;
+            const int token = row / group, head = kv_head * group + row % group;
+            const bool valid = token < count;
+            hi[r] = valid ? start + token : -1;
+            lo[r] = valid ? (window > 0 ? max(0, start + token - window + 1) : 0) : 0;
+            qptr[r] = valid ? q + static_cast<size_t>(first_row + token) * ldq + static_cast<size_t>(head) * head_dim : nullptr;
+        }
+        uint32_t qf[DMAX / 16][4];
+        load_q<DMAX>(qf, qptr[0], qptr[1], dim_steps);
+        const float scale_log2 = scale * kLog2e;
+        bool ok = true;
+        for (int it = 0; it < tiles; ++it) {
+            const int stage = it % kDecodeStages;
+            ok = mbar_wait(full_bar(stage), (it / kDecodeStages) & 1);
+            if (!ok) break;
+            const int key_base = key_begin + it * kTileKeys + warp * 16;
+            if (key_base < key_end) {
+                float s[2][4] = {};
+                qk_keys<DMAX, 1, L>(s, qf, k_stage(stage), warp * 16, dim_steps);
+                uint32_t p[1][4];
+                softmax_step<DMAX, 2>(s, st, o, p, key_base, lo, hi, scale_log2, true);
+                pv_16keys<DMAX, L>(o, p[0], v_stage(stage), warp * 16, dim_steps);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_bar(stage));
+        }
+        if (!ok) fault = 2;
     }
-    for (int it = 0; it < tiles; ++it) {
-        cp_async_wait<kDecodeStages - 2>();
-        __syncthreads();
-        const int next = it + kDecodeStages - 1;
-        if (next < tiles)
-            load_tile<DMAX>(view, key_begin + next * kTileKeys, plan.first_key, key_end - 1, k_stage(next % kDecodeStages),
-                            v_stage(next % kDecodeStages), &bad_page);
-        cp_async_commit();
-        const int stage = it % kDecodeStages;
-        const int key_base = key_begin + it * kTileKeys + warp * 16;
-        if (key_base < key_end) {
-            float s[2][4] = {};
-            qk_keys<DMAX, 1>(s, qf, k_stage(stage), warp * 16, dim_steps);
-            uint32_t p[1][4];
-            softmax_step<DMAX, 2>(s, st, o, p, key_base, lo, hi, scale_log2, true);
-            pv_16keys<DMAX>(o, p[0], v_stage(stage), warp * 16, dim_steps);
+    __syncthreads();
+    if (fault) {
+        if (threadIdx.x == 0 && status) atomicOr(status, fault == 2 ? MLR_STATUS_TIMEOUT : MLR_STATUS_BAD_PAGE);
+        if (fault == 2) {
+            // Give copies that may still be in flight time to land before the block's shared
+            // memory is handed to another block.
+            for (int i = 0; i < 100; ++i) __nanosleep(1000);
+            return;
         }
     }
-    cp_async_wait<0>();
-    __syncthreads();
 
-    // Merge the four warps through shared memory (the tile stages are free now).
+    // Merge the four compute warps through shared memory (the tile stages are free now).
+    const int g = lane >> 2, t = lane & 3;
     float* merge_o = reinterpret_cast<float*>(smem);                       // [4][16][DMAX]
     float* merge_ml = merge_o + 4 * 16 * DMAX;                             // [4][16][2]
+    if (warp < 4) {
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
-        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
-    }
+        for (int r = 0; r < 2; ++r) {
+            st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+            st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+        }
 #pragma unroll
-    for (int dn = 0; dn < DMAX / 8; ++dn) {
-        if (dn * 8 < head_dim) {
-            float* row0 = merge_o + (warp * 16 + g) * DMAX + dn * 8 + 2 * t;
-            float* row1 = merge_o + (warp * 16 + g + 8) * DMAX + dn * 8 + 2 * t;
-            row0[0] = o[dn][0];
-            row0[1] = o[dn][1];
-            row1[0] = o[dn][2];
-            row1[1] = o[dn][3];
+        for (int dn = 0; dn < DMAX / 8; ++dn) {
+            if (dn * 8 < head_dim) {
+                float* row0 = merge_o + (warp * 16 + g) * DMAX + dn * 8 + 2 * t;
+                float* row1 = merge_o + (warp * 16 + g + 8) * DMAX + dn * 8 + 2 * t;
+                row0[0] = o[dn][0];
+                row0[1] = o[dn][1];
+                row1[0] = o[dn][2];
+                row1[1] = o[dn][3];
+            }
+        }
+        if (t == 0) {
+            merge_ml[(warp * 16 + g) * 2 + 0] = st.m[0];
+            merge_ml[(warp * 16 + g) * 2 + 1] = st.l[0];
+            merge_ml[(warp * 16 + g + 8) * 2 + 0] = st.m[1];
+            merge_ml[(warp * 16 + g + 8) * 2 + 1] = st.l[1];
         }
     }
-    if (t == 0) {
-        merge_ml[(warp * 16 + g) * 2 + 0] = st.m[0];
-        merge_ml[(warp * 16 + g) * 2 + 1] = st.l[0];
-        merge_ml[(warp * 16 + g + 8) * 2 + 0] = st.m[1];
-        merge_ml[(warp * 16 + g + 8) * 2 + 1] = st.l[1];
-    }
     __syncthreads();
-    if (bad_page && threadIdx.x == 0 && status) atomicOr(status, MLR_STATUS_BAD_PAGE);
     const int rows = count * group;
     const bool direct = plan.splits == 1;
     float* part = partial + ((static_cast<size_t>(item) * kv_heads + kv_head) * max_splits + split) * 16 * (head_dim + 2);
-    for (int idx = threadIdx.x; idx < rows * head_dim; idx += kThreads) {
+    for (int idx = threadIdx.x; idx < rows * head_dim; idx += kDecodeThreads) {
         const int row = idx / head_dim, d = idx - row * head_dim;
         float m = -INFINITY;
 #pragma unroll
@@ -518,17 +701,22 @@ __global__ void __launch_bounds__(kThreads) prefill_kernel(
 
 #pragma unroll
     for (int s = 0; s < kPrefillStages - 1; ++s) {
-        if (s < n_tiles) load_tile<DMAX>(view, key_begin + s * kTileKeys, first_key, last_pos, k_stage(s), v_stage(s), &bad_page);
+        if (s < n_tiles)
+            load_tile<DMAX>(view, key_begin + s * kTileKeys, first_key, last_pos,
+                            lookup_page(view, key_begin + s * kTileKeys, first_key, last_pos), k_stage(s), v_stage(s), &bad_page);
         cp_async_commit();
     }
+    int next_page = kPrefillStages - 1 < n_tiles
+                        ? lookup_page(view, key_begin + (kPrefillStages - 1) * kTileKeys, first_key, last_pos) : -1;
     for (int it = 0; it < n_tiles; ++it) {
         cp_async_wait<kPrefillStages - 2>();
         __syncthreads();
         const int next = it + kPrefillStages - 1;
         if (next < n_tiles)
-            load_tile<DMAX>(view, key_begin + next * kTileKeys, first_key, last_pos, k_stage(next % kPrefillStages),
-                            v_stage(next % kPrefillStages), &bad_page);
+            load_tile<DMAX>(view, key_begin + next * kTileKeys, first_key, last_pos, next_page,
+                            k_stage(next % kPrefillStages), v_stage(next % kPrefillStages), &bad_page);
         cp_async_commit();
+        next_page = next + 1 < n_tiles ? lookup_page(view, key_begin + (next + 1) * kTileKeys, first_key, last_pos) : -1;
         const int stage = it % kPrefillStages;
         const int key0 = key_begin + it * kTileKeys;
         if (warp_active && key0 <= warp_last && key0 + kTileKeys - 1 >= warp_lo_min) {
@@ -567,10 +755,25 @@ constexpr size_t tile_smem(int stages) {
     return static_cast<size_t>(stages) * 2 * Tile<DMAX>::kBytes;
 }
 
+// Raises a kernel's dynamic shared memory limit; remembered per kernel and device so that
+// the attribute call is made once, not at every launch.
 template <typename Kernel>
 int allow_smem(Kernel kernel, size_t bytes, const char* what) {
+    struct Entry {
+        const void* kernel;
+        int device;
+        size_t bytes;
+    };
+    static thread_local Entry seen[64];
+    static thread_local int count = 0;
+    int device = 0;
+    cudaGetDevice(&device);
+    const void* key = reinterpret_cast<const void*>(kernel);
+    for (int i = 0; i < count; ++i)
+        if (seen[i].kernel == key && seen[i].device == device && seen[i].bytes >= bytes) return 0;
     const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
     if (e != cudaSuccess) return mlr_fail("%s: cannot use %zu bytes of shared memory: %s", what, bytes, cudaGetErrorString(e));
+    if (count < 64) seen[count++] = Entry{key, device, bytes};
     return 0;
 }
 
@@ -610,19 +813,24 @@ MLR_API int mlr_attention_decode_bf16(const void* q, int ldq, void* out, int ldo
     if (n_items == 0) return 0;
     const dim3 grid(max_splits, kv_heads, n_items);
     const dim3 combine_grid(n_items, kv_heads);
-#define MLR_LAUNCH(DMAX)                                                                                           \
+#define MLR_LAUNCH(DMAX, BLOCKS)                                                                                   \
     do {                                                                                                           \
         const size_t merge = sizeof(float) * (4 * 16 * DMAX + 4 * 16 * 2);                                         \
-        const size_t bytes = tile_smem<DMAX>(kDecodeStages) > merge ? tile_smem<DMAX>(kDecodeStages) : merge;                                \
-        if (int e = allow_smem(decode_splitkv_kernel<DMAX>, bytes, "attention_decode_bf16")) return e;            \
-        decode_splitkv_kernel<DMAX><<<grid, kThreads, bytes, stream>>>(                                            \
+        const size_t tile = BLOCKS ? Tile<DMAX>::kBytes : PaddedTile<DMAX>::kBytes;                                \
+        const size_t stages = static_cast<size_t>(kDecodeStages) * 2 * tile;                                       \
+        const size_t bytes = stages > merge ? stages : merge;                                                      \
+        if (int e = allow_smem(decode_splitkv_kernel<DMAX, BLOCKS>, bytes, "attention_decode_bf16")) return e;    \
+        decode_splitkv_kernel<DMAX, BLOCKS><<<grid, kDecodeThreads, bytes, stream>>>(                              \
             static_cast<const __nv_bfloat16*>(q), ldq, static_cast<__nv_bfloat16*>(out), ldo,                      \
             static_cast<const __nv_bfloat16*>(cache), num_pages, items, segment_info, block_table, table_stride,   \
             page_size, q_heads, kv_heads, head_dim, window, scale, chunk, max_splits, partial, status);            \
     } while (0)
-    if (head_dim <= 64) MLR_LAUNCH(64);
-    else if (head_dim <= 128) MLR_LAUNCH(128);
-    else MLR_LAUNCH(256);
+    if (head_dim == 64) MLR_LAUNCH(64, true);
+    else if (head_dim == 128) MLR_LAUNCH(128, true);
+    else if (head_dim == 256) MLR_LAUNCH(256, true);
+    else if (head_dim < 64) MLR_LAUNCH(64, false);
+    else if (head_dim < 128) MLR_LAUNCH(128, false);
+    else MLR_LAUNCH(256, false);
 #undef MLR_LAUNCH
     if (int e = mlr_launched("attention_decode_bf16")) return e;
     if (max_splits > 1) {

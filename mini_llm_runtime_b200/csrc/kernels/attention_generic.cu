@@ -46,6 +46,7 @@ __global__ void __launch_bounds__(kThreads) attention_generic_kernel(
     const size_t page_elems = static_cast<size_t>(2) * kv_heads * page_size * head_dim;
     const size_t head_elems = static_cast<size_t>(page_size) * head_dim;
     const size_t value_shift = static_cast<size_t>(kv_heads) * head_elems;  // from a K row to its V row
+    const bool swizzled = mlr_cache_swizzled(sizeof(T) == 2, head_dim);
 
     const T* qrow = q + static_cast<size_t>(row) * ldq + static_cast<size_t>(head) * head_dim;
     for (int i = threadIdx.x; i < head_dim; i += kThreads) qs[i] = mlr_load(qrow, i);
@@ -70,7 +71,7 @@ __global__ void __launch_bounds__(kThreads) attention_generic_kernel(
                                                     static_cast<size_t>(t % page_size) * head_dim);
                     const T* k = cache + offset;
                     float partial = 0.0f;
-                    for (int j = lane; j < head_dim; j += 32) partial = fmaf(qs[j], mlr_load(k, j), partial);
+                    for (int j = lane; j < head_dim; j += 32) partial = fmaf(qs[j], mlr_load(k, mlr_cache_col(j, t, swizzled)), partial);
                     score = mlr_warp_sum(partial) * scale;
                 }
             }
@@ -97,13 +98,14 @@ __global__ void __launch_bounds__(kThreads) attention_generic_kernel(
             for (int i = 0; i < kTile; ++i) {
                 const long long offset = offsets[i];
                 if (offset < 0) continue;
+                const int t = tile + i;
                 const float p = scores[i];
                 running_sum += p;
                 const T* v = cache + offset + value_shift;
 #pragma unroll
                 for (int d = 0; d < kMaxDimsPerThread; ++d) {
                     const int c = threadIdx.x + d * kThreads;
-                    if (c < head_dim) acc[d] = fmaf(p, mlr_load(v, c), acc[d]);
+                    if (c < head_dim) acc[d] = fmaf(p, mlr_load(v, mlr_cache_col(c, t, swizzled)), acc[d]);
                 }
             }
             running_max = new_max;

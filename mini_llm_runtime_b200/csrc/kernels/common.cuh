@@ -42,7 +42,22 @@ static int mlr_launched(const char* what) {
     } while (0)
 
 // Status bits kernels may set in a device status word instead of trapping.
-enum : int { MLR_STATUS_BAD_INDEX = 1, MLR_STATUS_BAD_PAGE = 2, MLR_STATUS_NONFINITE = 4 };
+enum : int { MLR_STATUS_BAD_INDEX = 1, MLR_STATUS_BAD_PAGE = 2, MLR_STATUS_NONFINITE = 4, MLR_STATUS_TIMEOUT = 8 };
+
+// ---- layout of a token's row in the paged cache ----
+// A layer's cache is [page][K|V][kv_head][token_in_page][head_dim].  In bfloat16 caches
+// with a head size of 64, 128 or 256 the 16-byte chunks of a token's row are stored
+// permuted: chunk c of the token at absolute position p lives at chunk c ^ (p & 7).  A
+// page block copied to shared memory byte for byte is then already laid out so that the
+// eight rows of an ldmatrix fall into different banks.  Other caches store rows plainly.
+// Every kernel that touches the cache derives the rule from (precision, head size) here.
+__host__ __device__ inline bool mlr_cache_swizzled(bool bf16, int head_dim) {
+    return bf16 && (head_dim == 64 || head_dim == 128 || head_dim == 256);
+}
+// Column (element index within the row) at which element `col` of the token at `position` is stored.
+__host__ __device__ inline int mlr_cache_col(int col, int position, bool swizzled) {
+    return swizzled ? col ^ ((position & 7) << 3) : col;
+}
 
 // ---- element access in either precision; arithmetic is always float ----
 __device__ __forceinline__ float mlr_load(const float* p, size_t i) { return p[i]; }

@@ -187,8 +187,9 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, int ld, int rows,
               (static_cast<size_t>(is_key ? 0 : 1) * kv_heads + kv_head) * page_size * head_dim +
               static_cast<size_t>(position % page_size) * head_dim;
     }
+    const bool swizzled = mlr_cache_swizzled(sizeof(T) == 2, head_dim);
     if (is_value) {
-        for (int i = lane; i < head_dim; i += 32) dst[i] = x[i];
+        for (int i = lane; i < head_dim; i += 32) dst[mlr_cache_col(i, position, swizzled)] = x[i];
         return;
     }
     float lo[kMaxPairsPerLane], hi[kMaxPairsPerLane];
@@ -235,8 +236,8 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, int ld, int rows,
             mlr_store(x, j, a);
             mlr_store(x, j + half, b);
             if (dst) {
-                mlr_store(dst, j, a);
-                mlr_store(dst, j + half, b);
+                mlr_store(dst, mlr_cache_col(j, position, swizzled), a);
+                mlr_store(dst, mlr_cache_col(j + half, position, swizzled), b);
             }
         }
     }

@@ -19,7 +19,6 @@ import torch
 from . import functions as F
 
 _TILE = 64
-_TARGET_BLOCKS = 148 * 4      # blocks that keep every SM of a B200 busy with a few blocks each
 _MIN_CHUNK = 128
 
 
@@ -35,12 +34,27 @@ def modules_for(dtype: torch.dtype, head_dim: int) -> List[str]:
 
 def split_plan(spans: List[int], blocks_per_split: int):
     """Keys per split (a multiple of 64) and the largest number of splits, for items
-    whose key spans (from a 64-aligned base to the last key) are `spans`."""
+    whose key spans (from a 64-aligned base to the last key) are `spans`.
+
+    `blocks_per_split` thread blocks run for every split (items times kv heads).  Two
+    blocks fit an SM.  More splits give smaller blocks (less imbalance, more SMs busy
+    when there are few requests) but each block pays a fixed start and merge cost, and a
+    last, partly filled wave of blocks costs as much as a full one.  The split count
+    with the smallest estimated time wins."""
     longest = max(spans)
-    wanted = max(1, _TARGET_BLOCKS // max(1, blocks_per_split))
-    chunk = max(_MIN_CHUNK, -(-longest // wanted))
-    chunk = -(-chunk // _TILE) * _TILE
-    return chunk, -(-longest // chunk)
+    slots = 148 * 2
+    per_key_ns, per_block_ns = 0.022, 5.0       # one block streaming beside another; start + merge
+    best = None
+    limit = max(1, min(512, -(-longest // _MIN_CHUNK)))
+    for splits in range(1, limit + 1):
+        chunk = -(-(-(-longest // splits)) // _TILE) * _TILE
+        real = -(-longest // chunk)
+        waves = -(-(real * blocks_per_split) // slots)
+        share = min(1.0, real * blocks_per_split / slots / waves * 2)      # SMs with one block stream faster
+        estimate = waves * (chunk * per_key_ns * max(share, 0.5) + per_block_ns)
+        if best is None or estimate < best[0] - 1e-9:
+            best = (estimate, chunk, real)
+    return best[1], best[2]
 
 
 class _Plan:

@@ -101,10 +101,22 @@ def test_gemm_f32_is_true_float32_and_independent_of_batching(M, N, K):
 
 
 # ------------------------------------------------------------------ paged cache helpers
+def stored_row(x, dtype):
+    """Rows [T, Hkv, D] as the cache stores them: bfloat16 caches with a head size of 64,
+    128 or 256 keep the 16-byte chunk c of the token at position p at chunk c ^ (p & 7);
+    every other cache keeps rows as they are.  (The permutation is its own inverse.)"""
+    T, _, D = x.shape
+    if dtype is not torch.bfloat16 or D not in (64, 128, 256):
+        return x
+    col = torch.arange(D)[None, None, :] ^ ((torch.arange(T) & 7) << 3)[:, None, None]
+    return torch.gather(x, 2, col.expand_as(x))
+
+
 def make_cache(kvs, page_size, dtype, seed=0, extra_pages=3):
     """kvs: list of (k, v) [T, Hkv, D] per request.  Returns cache [pages, 2, Hkv, ps, D]
     filled with NaN except the given tokens, on shuffled pages, and the block table."""
     Hkv, D = kvs[0][0].shape[1:]
+    kvs = [(stored_row(k, dtype), stored_row(v, dtype)) for k, v in kvs]
     blocks = [-(-k.shape[0] // page_size) for k, _ in kvs]
     num_pages = sum(blocks) + extra_pages
     order = torch.randperm(num_pages, generator=gen(seed)).tolist()
@@ -350,8 +362,9 @@ def test_qk_norm_rope_cache(Hq, Hkv, D, page, dtype):
     for i, (start, count) in enumerate(segs):
         for p in range(start, start + count):
             page_id, slot = host_table[i, p // page].item(), p % page
-            assert torch.allclose(host_cache[page_id, 0, :, slot], k[row], atol=tol, rtol=tol)
-            assert torch.equal(host_cache[page_id, 1, :, slot], v[row].to(dtype).float())
+            col = torch.arange(D) ^ ((p & 7) << 3) if dtype is torch.bfloat16 and D in (64, 128, 256) else torch.arange(D)
+            assert torch.allclose(host_cache[page_id, 0, :, slot][:, col], k[row], atol=tol, rtol=tol)
+            assert torch.equal(host_cache[page_id, 1, :, slot][:, col], v[row].to(dtype).float())
             written[page_id, slot] = True
             row += 1
     # Nothing else was touched.
