@@ -21,6 +21,7 @@ from __future__ import annotations
 import math
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 
@@ -112,8 +113,12 @@ def rope_table(positions: Sequence[int], head_dim: int, theta: float, dtype):
     (src/minillm/runtime.cpp:231-241); the same is done here in float32 whatever
     `dtype` is, then the table is widened to `dtype`."""
     half = head_dim // 2
-    j = torch.arange(half, dtype=torch.float32)
-    freq = torch.pow(torch.tensor(theta, dtype=torch.float32), -2.0 * j / float(head_dim))
+    # `std::pow(float, float)` is the C library's powf; numpy's float32 power calls the same
+    # function, while torch's vectorised pow may differ from it in the last bit, which the
+    # position then multiplies.
+    j = np.arange(half, dtype=np.float32)
+    exponent = (np.float32(-2.0) * j / np.float32(head_dim)).astype(np.float32)
+    freq = torch.from_numpy(np.power(np.float32(theta), exponent).astype(np.float32))
     pos = torch.as_tensor(list(positions), dtype=torch.float32)[:, None]
     angle = pos * freq[None, :]
     return torch.cos(angle).to(dtype), torch.sin(angle).to(dtype)

@@ -104,7 +104,7 @@ def test_attention_part_with_its_cache(dtype, head_dim, window):
                                    {r: f"p.self_attn.{r}_proj.weight" for r in "qkvo"} |
                                    {"q_norm": "p.self_attn.q_norm.weight", "k_norm": "p.self_attn.k_norm.weight"}))
     assert part.cache_need() == CacheNeed(window, Hkv, D) and part.state_need() is None
-    w = {s.name: ((1 + 0.1 * torch.randn(s.shape)) if s.role == "vector" else torch.randn(s.shape) * 0.2).to(torch.bfloat16)
+    w = {s.name: ((1 + 0.1 * torch.randn(s.shape)) if s.role == "vector" else torch.randn(s.shape) * 0.08).to(torch.bfloat16)
          for s in part.weight_specs()}
     assert len(w) == 6
     part.position = Rope(PartSpec("rope", {"theta": theta, "rotary_dim": D, "max_positions": 64}))
