@@ -23,6 +23,7 @@
 // position - window + 1.  The reference computes them with three SIMT kernels and a
 // materialised score matrix (src/minillm/cuda/attention.cu:97-218).
 #include "common.cuh"
+#include "attention_no_alloc.h"
 
 #include <type_traits>
 
@@ -839,6 +840,45 @@ MLR_API int mlr_attention_decode_bf16(const void* q, int ldq, void* out, int ldo
         return mlr_launched("attention_decode_bf16 combine");
     }
     return 0;
+}
+
+// ---------------------------------------------------------------- the entry point that allocates nothing
+// Scratch for mlr_attention_decode_bf16_no_alloc (see attention_no_alloc.h).  In host code
+// this name is only a handle for the runtime: the device address comes from
+// cudaGetSymbolAddress.
+static __device__ __align__(256) float mlr_static_scratch[MLR_ATTENTION_STATIC_SCRATCH_FLOATS];
+
+MLR_API int mlr_attention_decode_bf16_no_alloc(const void* q, int ldq, void* out, int ldo, const void* cache,
+                                               int num_pages, const int* items, int n_items,
+                                               const int* segment_info, const int* block_table, int table_stride,
+                                               int page_size, int q_heads, int kv_heads, int head_dim, int window,
+                                               float scale, int chunk, int max_splits, int* status,
+                                               cudaStream_t stream) {
+    MLR_REQUIRE(n_items >= 0 && kv_heads > 0 && head_dim > 0 && max_splits >= 1,
+                "attention_decode_bf16_no_alloc: bad sizes items=%d kv_heads=%d head_dim=%d splits=%d", n_items, kv_heads,
+                head_dim, max_splits);
+    const long long need = mlr_attention_decode_scratch_floats(n_items, kv_heads, head_dim, max_splits);
+    MLR_REQUIRE(need <= MLR_ATTENTION_STATIC_SCRATCH_FLOATS,
+                "attention_decode_bf16_no_alloc: the call needs %lld floats of scratch, the built-in array holds %d; "
+                "use fewer requests per call, fewer splits, or mlr_attention_decode_bf16 with a buffer of your own",
+                need, MLR_ATTENTION_STATIC_SCRATCH_FLOATS);
+    // Device address of the array, looked up once per device with that device current.
+    constexpr int kMaxDevices = 64;
+    static float* address[kMaxDevices] = {};
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return mlr_fail("attention_decode_bf16_no_alloc: cudaGetDevice: %s", cudaGetErrorString(e));
+    MLR_REQUIRE(device >= 0 && device < kMaxDevices, "attention_decode_bf16_no_alloc: device index %d is not below %d", device, kMaxDevices);
+    if (address[device] == nullptr) {
+        void* found = nullptr;
+        e = cudaGetSymbolAddress(&found, mlr_static_scratch);
+        if (e != cudaSuccess || found == nullptr)
+            return mlr_fail("attention_decode_bf16_no_alloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        address[device] = static_cast<float*>(found);
+    }
+    return mlr_attention_decode_bf16(q, ldq, out, ldo, cache, num_pages, items, n_items, segment_info, block_table,
+                                     table_stride, page_size, q_heads, kv_heads, head_dim, window, scale, chunk,
+                                     max_splits, address[device], status, stream);
 }
 
 // tiles: n_tiles pairs {segment, first token of a 64-row tile of that segment}.
