@@ -1,0 +1,370 @@
+// bfloat16 matrix product on the fifth-generation tensor cores of sm_100a:
+//     out[p, q] = sum_k Pm[p, k] * Qm[q, k]        (both operands row-major, K contiguous)
+// written to out[p * ldo + q], or, "swapped", to out[q * ldo + p].  With Pm = activations
+// and Qm = weights this is y = x W^T for prompt portions; with Pm = weights, Qm = the few
+// activations of a decode step and the swapped store it is the same product arranged so
+// that the weight matrix fills the 128-row side of the instruction and is streamed once.
+//
+// One persistent block per SM, six warps:
+//   warp 0      one lane issues TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of a
+//               128 x 64 tile of Pm and a BN x 64 tile of Qm per stage, completion counted
+//               on the stage's "full" mbarrier;
+//   warp 1      allocates tensor memory (two accumulators of BN float32 columns each); one
+//               lane issues tcgen05.mma (M = 128, N = BN, K = 16, four per stage) with
+//               shared-memory descriptors, frees a stage with tcgen05.commit on its "empty"
+//               barrier, and hands a finished accumulator over with tcgen05.commit;
+//   warps 2-5   read the accumulator with tcgen05.ld (each warp its quarter of the 128
+//               lanes), convert and store, and give the accumulator back.
+// The main loop of the next tile overlaps the stores of the last.  Rows and columns beyond
+// the operands are zero-filled by TMA on the way in and not stored on the way out; so is a
+// K that is no multiple of 64.  Every barrier wait gives up after about two seconds, sets
+// MLR_STATUS_TIMEOUT and lets the block leave through the common exit, which frees the
+// tensor memory.
+//
+// The reference has no kernel of this kind: it calls cublasGemmEx for every product
+// (src/minillm/cuda/matrix.cpp:30-36).
+#include "common.cuh"
+
+#include <cuda.h>
+
+namespace {
+
+constexpr int kThreads = 192;
+constexpr int kTileP = 128;     // rows of Pm per tile (the M of the instruction)
+constexpr int kTileK = 64;      // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kTilePBytes = kTileP * kTileK * 2;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - start > 4000000000LL) return false;
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::
+                     "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_load16(uint32_t addr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(addr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+// Shared-memory descriptor of a K-major tile stored as rows of 128 bytes with the 128-byte
+// swizzle (what TMA writes): start address / 16 in bits 0-13, leading offset (unused for
+// swizzled K-major, set to 1) in bits 16-29, stride between groups of 8 rows = 1024 bytes
+// (/16 = 64) in bits 32-45, descriptor version 1 in bits 46-47, layout 2 (128-byte
+// swizzle) in bits 61-63.
+__device__ __forceinline__ uint64_t smem_descriptor(uint32_t addr) {
+    const uint64_t lo = ((addr >> 4) & 0x3FFFu) | (1u << 16);
+    const uint64_t hi = 64u | (1u << 14) | (2u << 29);
+    return lo | (hi << 32);
+}
+
+// Instruction descriptor: float32 accumulator (bits 4-5 = 1), bfloat16 A and B (bits 7-9 and
+// 10-12 = 1), both K-major (bits 15, 16 = 0), N / 8 in bits 17-22, M / 16 in bits 24-28.
+__host__ __device__ constexpr uint32_t instruction_descriptor(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kTileP >> 4) << 24);
+}
+
+template <int BN>
+struct Shape {
+    static constexpr int kTileQBytes = BN * kTileK * 2;
+    static constexpr int kStageBytes = kTilePBytes + kTileQBytes;
+    static constexpr int kStages = (200 * 1024 / kStageBytes) < 8 ? (200 * 1024 / kStageBytes) : 8;
+    static constexpr int kTmemColumns = 2 * BN < 32 ? 32 : 2 * BN;      // two accumulators; a power of two >= 32
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p,
+                                                                const __grid_constant__ CUtensorMap map_q,
+                                                                void* __restrict__ out, long long ldo, int P, int Q, int K,
+                                                                int out_f32, int swapped, int* status) {
+    using S = Shape<BN>;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long barriers[2 * S::kStages + 4];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int fault;
+    // The tiles want 1024-byte alignment (the swizzle pattern repeats every 8 rows of 128 bytes).
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar_base = smem_u32(barriers);
+    auto full_bar = [&](int s) { return bar_base + s * 8; };
+    auto empty_bar = [&](int s) { return bar_base + (S::kStages + s) * 8; };
+    auto acc_full_bar = [&](int a) { return bar_base + (2 * S::kStages + a) * 8; };
+    auto acc_empty_bar = [&](int a) { return bar_base + (2 * S::kStages + 2 + a) * 8; };
+    auto tile_p = [&](int s) { return smem_base + s * S::kStageBytes; };
+    auto tile_q = [&](int s) { return smem_base + s * S::kStageBytes + kTilePBytes; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        fault = 0;
+        for (int s = 0; s < S::kStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(acc_full_bar(a), 1);
+            mbar_init(acc_empty_bar(a), 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_slot)),
+                     "r"(S::kTmemColumns));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    tmem_fence_before();
+    __syncthreads();
+    tmem_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    const int tiles_p = (P + kTileP - 1) / kTileP, tiles_q = (Q + BN - 1) / BN;
+    const int tiles = tiles_p * tiles_q;
+    const int k_blocks = (K + kTileK - 1) / kTileK;
+
+    if (warp == 0) {
+        // ---------------- loads
+        if (lane == 0) {
+            bool ok = true;
+            int it = 0;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                const int p0 = (tile % tiles_p) * kTileP, q0 = (tile / tiles_p) * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int stage = it % S::kStages;
+                    if (it >= S::kStages) ok = mbar_wait(empty_bar(stage), ((it / S::kStages) - 1) & 1);
+                    if (!ok) break;
+                    mbar_expect_tx(full_bar(stage), S::kStageBytes);
+                    tma_load_2d(tile_p(stage), &map_p, kb * kTileK, p0, full_bar(stage));
+                    tma_load_2d(tile_q(stage), &map_q, kb * kTileK, q0, full_bar(stage));
+                }
+            }
+            if (!ok) fault = 2;
+        }
+    } else if (warp == 1) {
+        // ---------------- tensor-core instructions
+        if (lane == 0) {
+            constexpr uint32_t idesc = instruction_descriptor(BN);
+            bool ok = true;
+            int it = 0, local = 0;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+                const int acc = local & 1;
+                if (local >= 2) ok = mbar_wait(acc_empty_bar(acc), ((local >> 1) - 1) & 1);
+                if (!ok) break;
+                tmem_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int stage = it % S::kStages;
+                    ok = mbar_wait(full_bar(stage), (it / S::kStages) & 1);
+                    if (!ok) break;
+                    tmem_fence_after();
+                    const uint64_t desc_p = smem_descriptor(tile_p(stage)), desc_q = smem_descriptor(tile_q(stage));
+#pragma unroll
+                    for (int k = 0; k < kTileK / 16; ++k)      // 16 bf16 = 32 bytes = 2 descriptor units further along K
+                        umma_bf16(tmem_d, desc_p + 2 * k, desc_q + 2 * k, idesc, (kb | k) != 0);
+                    umma_commit(empty_bar(stage));             // the stage is free once these instructions have read it
+                }
+                if (!ok) break;
+                umma_commit(acc_full_bar(acc));                // the accumulator is complete once all of them are done
+            }
+            if (!ok) fault = 2;
+        }
+    } else {
+        // ---------------- stores: warp w reads lanes 32 (w % 4) .. of the accumulator
+        const int quarter = warp & 3;
+        bool ok = true;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+            const int acc = local & 1;
+            const int p0 = (tile % tiles_p) * kTileP, q0 = (tile / tiles_p) * BN;
+            ok = mbar_wait(acc_full_bar(acc), (local >> 1) & 1);
+            if (!ok) break;
+            tmem_fence_after();
+            const int p = p0 + quarter * 32 + lane;
+#pragma unroll
+            for (int c = 0; c < BN; c += 16) {
+                uint32_t r[16];
+                tmem_load16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + c, r);
+                if (p < P) {
+                    if (swapped) {
+                        // out[q][p]: for a fixed q the 32 lanes of a warp write consecutive addresses.
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int q = q0 + c + j;
+                            if (q < Q) {
+                                const float v = __uint_as_float(r[j]);
+                                if (out_f32) static_cast<float*>(out)[q * ldo + p] = v;
+                                else static_cast<__nv_bfloat16*>(out)[q * ldo + p] = __float2bfloat16_rn(v);
+                            }
+                        }
+                    } else if (q0 + c + 16 <= Q && (ldo & 7) == 0) {
+                        // out[p][q0 + c ..]: 16 consecutive values of the thread's row.
+                        if (out_f32) {
+                            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(out) + p * ldo + q0 + c);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                     __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                        } else {
+                            uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(out) + p * ldo + q0 + c);
+                            uint32_t w[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                                w[j] = *reinterpret_cast<const uint32_t*>(&h);
+                            }
+                            dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                            dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int q = q0 + c + j;
+                            if (q < Q) {
+                                const float v = __uint_as_float(r[j]);
+                                if (out_f32) static_cast<float*>(out)[p * ldo + q] = v;
+                                else static_cast<__nv_bfloat16*>(out)[p * ldo + q] = __float2bfloat16_rn(v);
+                            }
+                        }
+                    }
+                }
+            }
+            tmem_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+        }
+        if (!ok) fault = 2;
+    }
+    tmem_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (fault) {
+            // Give work that may still be in flight time to finish before the memory goes back.
+            for (int i = 0; i < 100; ++i) __nanosleep(1000);
+        }
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(S::kTmemColumns));
+    }
+    if (fault && threadIdx.x == 0 && status) atomicOr(status, MLR_STATUS_TIMEOUT);
+}
+
+// ---------------------------------------------------------------- host side
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* found = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &found, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(found);
+    }
+    return fn;
+}
+
+// A map over a row-major bf16 matrix [rows, cols] (row stride ld elements) that loads boxes
+// of `box_rows` x 64 with the 128-byte swizzle; what lies outside the matrix reads as zero.
+int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
+    EncodeTiled encode = encode_tiled();
+    MLR_REQUIRE(encode != nullptr, "gemm_bf16_tcgen05: the driver does not offer cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+    const cuuint32_t box[2] = {kTileK, static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    MLR_REQUIRE(r == CUDA_SUCCESS, "gemm_bf16_tcgen05: cuTensorMapEncodeTiled failed with code %d", static_cast<int>(r));
+    return 0;
+}
+
+template <int BN>
+int launch(const CUtensorMap& map_p, const CUtensorMap& map_q, void* out, long long ldo, int P, int Q, int K, int out_f32,
+           int swapped, int* status, int sms, cudaStream_t stream) {
+    using S = Shape<BN>;
+    const size_t bytes = static_cast<size_t>(S::kStages) * S::kStageBytes + 1024;
+    static thread_local bool allowed = false;
+    if (!allowed) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   static_cast<int>(bytes));
+        if (e != cudaSuccess) return mlr_fail("gemm_bf16_tcgen05: cannot use %zu bytes of shared memory: %s", bytes, cudaGetErrorString(e));
+        allowed = true;
+    }
+    const int tiles = ((P + kTileP - 1) / kTileP) * ((Q + BN - 1) / BN);
+    const int grid = tiles < sms ? tiles : sms;
+    gemm_tcgen05_kernel<BN><<<grid, kThreads, bytes, stream>>>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, status);
+    return mlr_launched("gemm_bf16_tcgen05");
+}
+
+}  // namespace
+
+// out[p, q] = sum_k Pm[p, k] Qm[q, k]; stored at out[p * ldo + q] (swapped = 0) or
+// out[q * ldo + p] (swapped = 1), as bfloat16 or float32.  Pm is [P, K] with row stride ldp,
+// Qm is [Q, K] with row stride ldq (elements).  tile_q: 16, 32, 64, 128 or 256 columns of Qm
+// per tile (0 lets the function choose).
+MLR_API int mlr_gemm_bf16_tcgen05(const void* Pm, long long ldp, int P, const void* Qm, long long ldq, int Q, int K, void* out,
+                                  long long ldo, int out_f32, int swapped, int tile_q, int* status, cudaStream_t stream) {
+    MLR_REQUIRE(P >= 1 && Q >= 1 && K >= 8, "gemm_bf16_tcgen05: bad sizes P=%d Q=%d K=%d", P, Q, K);
+    MLR_REQUIRE(K % 8 == 0 && ldp % 8 == 0 && ldq % 8 == 0 && ldp >= K && ldq >= K,
+                "gemm_bf16_tcgen05: K and the operand row strides must be multiples of 8 elements (16 bytes), got K=%d", K);
+    MLR_REQUIRE(reinterpret_cast<uintptr_t>(Pm) % 16 == 0 && reinterpret_cast<uintptr_t>(Qm) % 16 == 0,
+                "gemm_bf16_tcgen05: the operands must be 16-byte aligned");
+    MLR_REQUIRE(ldo >= (swapped ? P : Q), "gemm_bf16_tcgen05: the output row stride is smaller than the row");
+    MLR_REQUIRE(reinterpret_cast<uintptr_t>(out) % 16 == 0, "gemm_bf16_tcgen05: the output must be 16-byte aligned");
+    if (tile_q == 0) tile_q = Q <= 16 ? 16 : Q <= 32 ? 32 : Q <= 64 ? 64 : Q <= 128 ? 128 : 256;
+    MLR_REQUIRE(tile_q == 16 || tile_q == 32 || tile_q == 64 || tile_q == 128 || tile_q == 256,
+                "gemm_bf16_tcgen05: tile_q must be 16, 32, 64, 128 or 256, got %d", tile_q);
+    int device = 0, sms = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    CUtensorMap map_p, map_q;
+    if (int e = make_map(&map_p, Pm, P, K, ldp, kTileP)) return e;
+    if (int e = make_map(&map_q, Qm, Q, K, ldq, tile_q)) return e;
+    switch (tile_q) {
+        case 16: return launch<16>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, status, sms, stream);
+        case 32: return launch<32>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, status, sms, stream);
+        case 64: return launch<64>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, status, sms, stream);
+        case 128: return launch<128>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, status, sms, stream);
+        default: return launch<256>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, status, sms, stream);
+    }
+}

@@ -142,6 +142,7 @@ class Model:
         for part in self._all_parts():
             part.bind(tensors, self.rt)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.rt.device)
+        self.rt.status = self.status
         self._graph_pool = torch.cuda.graph_pool_handle()
         self._bound = True
 

@@ -10,7 +10,7 @@ logits are float32.
 Matrix products of the bfloat16 path go to the vendor library (cuBLAS through
 `torch.mm`), as the reference sends all of its products to cuBLAS
 (src/minillm/cuda/matrix.cpp:30-36), unless a hand-written kernel of this package
-covers the shape (`ops/linear_bf16.py` decides).
+covers the shape: products for at most 16 tokens run on `csrc/kernels/gemv_bf16.cu`.
 """
 from __future__ import annotations
 
@@ -33,7 +33,8 @@ class Runtime:
         # The 32-bit path must not be silently lowered by library defaults either.
         torch.backends.cuda.matmul.allow_tf32 = False
         torch.backends.cudnn.allow_tf32 = False
-        self.linear_bf16 = None   # set by ops.linear_bf16 when hand-written products are enabled
+        self.use_gemv = False     # few-token products on the package's mma.sync weight streamer (slower than the library today)
+        self.status = None        # the model's device status word (set at bind time)
         self._shared = {}
 
     @property
@@ -69,10 +70,21 @@ class Runtime:
             out = torch.empty((x.shape[0], w.shape[0]), dtype=torch.float32, device=self.device)
             F.gemm_f32(x, w, out)
             return out
-        if self.linear_bf16 is not None:
-            out = self.linear_bf16(x, w, out_dtype)
-            if out is not None:
-                return out
+        if self.use_gemv and self.status is not None and F.gemv_applies(x, w):
+            out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=self.device)
+            F.gemv_bf16(x, w, out, self.status)
+            return out
         if out_dtype is torch.bfloat16:
             return torch.mm(x, w.t())
         return torch.mm(x, w.t(), out_dtype=out_dtype)
+
+    def gated_linear(self, x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+        """silu(x Wgate^T) * (x Wup^T) for the stacked matrix [2 I, K]: one fused kernel for a
+        few tokens, else the product followed by the gate kernel."""
+        inter = w_gate_up.shape[0] // 2
+        out = torch.empty((x.shape[0], inter), dtype=self.dtype, device=self.device)
+        if self.dtype is torch.bfloat16 and self.use_gemv and self.status is not None and F.gemv_applies(x, w_gate_up):
+            F.gemv_bf16(x, w_gate_up, out, self.status, swiglu=True)
+            return out
+        F.swiglu(self.linear(x, w_gate_up), out)
+        return out

@@ -32,7 +32,7 @@ class SwiGLU(FeedForward):
                 WeightSpec(w["down"], (self.width, self.inter))]
 
     def kernel_modules(self, dtype) -> List[str]:
-        return ["elementwise"] + (["gemm_f32"] if dtype is torch.float32 else [])
+        return ["elementwise"] + (["gemm_f32"] if dtype is torch.float32 else ["gemv_bf16"])
 
     def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
         w = self.spec.weights
@@ -41,9 +41,7 @@ class SwiGLU(FeedForward):
 
     def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
         rt = step.rt
-        gate_up = rt.linear(x, self.w_gate_up)
-        act = rt.empty(x.shape[0], self.inter)
-        F.swiglu(gate_up, act)
+        act = rt.gated_linear(x, self.w_gate_up)
         return rt.linear(act, self.w_down, out_dtype=torch.float32)
 
 
