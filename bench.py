@@ -241,13 +241,14 @@ def main() -> int:
         for _ in range(warmup):
             one_step()
         native.launch_count = 0
+        model.graph_launches = 0
         if with_clocks:
             with ClockSampler() as clocks:
                 ms = timed(one_step, steps)
             clock_summary = clocks.summary()
         else:
             ms, clock_summary = timed(one_step, steps), None
-        launches = native.launch_count
+        launches = native.launch_count + model.graph_launches
         for s in slots:
             model.close_request(s)
         return batch / ms * 1e3, ms, launches, clock_summary
@@ -268,11 +269,14 @@ def main() -> int:
             points[f"decode_b{b}_ctx2048"] = decode_rate(b, min(2048, context), short, 3)[0]
 
     # ---------------------------------------------------------------- end to end through the engine
-    engine = Engine(model, max_batch_tokens=max(2048, args.batch), prefill_chunk=2048)
+    # Prompts first, then all requests decode together (policy prefill_first), so that every
+    # timed step is a decode step of the whole batch.
+    engine = Engine(model, max_batch_tokens=max(2048, args.batch), prefill_chunk=2048, policy="prefill_first")
     for _ in range(args.batch):
         engine.submit(prompt_of(context - 1), SamplingParams(max_tokens=horizon, ignore_eos=True))
     while any(r.prefill_remaining for r in engine.scheduler.active) or engine.scheduler.waiting:
         engine.step()
+    assert all(len(r.generated) == 1 for r in engine.scheduler.active) and len(engine.scheduler.active) == args.batch
     for _ in range(args.warmup):
         engine.step()
     torch.cuda.synchronize()

@@ -56,8 +56,16 @@ __global__ void embed_gather_vec8_kernel(float* __restrict__ out, const W* __res
 // ------------------------------------------------------------------ rms norm
 // out[r,:] = rmsnorm(h[row,:] + delta[row,:]) * w, row = rows ? rows[r] : r.
 // With write_back the sum replaces h[row,:] (the residual stream moves on).
+// `delta` may come in `slices` parts, `slice_stride` elements apart (a product whose K was cut
+// into ranges leaves one partial sum per range); they are added in order, then to h.
+__device__ __forceinline__ float sliced(const float* p, int slices, size_t slice_stride) {
+    float d = p[0];
+    for (int s = 1; s < slices; ++s) d += p[s * slice_stride];
+    return d;
+}
+
 template <typename T, typename W>
-__global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta,
+__global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int slices, size_t slice_stride,
                                const W* __restrict__ weight, T* __restrict__ out,
                                const int* __restrict__ rows, int width, float eps, int write_back) {
     __shared__ float scratch[32];
@@ -67,14 +75,14 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ 
     const float* dr = delta ? delta + row * width : nullptr;
     float sum = 0.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        const float x = dr ? hr[i] + dr[i] : hr[i];
+        const float x = dr ? hr[i] + sliced(dr + i, slices, slice_stride) : hr[i];
         sum = fmaf(x, x, sum);
     }
     sum = mlr_block_sum(sum, scratch);
     const float scale = 1.0f / sqrtf(sum / static_cast<float>(width) + eps);
     T* dst = out + static_cast<size_t>(r) * width;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        const float x = dr ? hr[i] + dr[i] : hr[i];
+        const float x = dr ? hr[i] + sliced(dr + i, slices, slice_stride) : hr[i];
         if (write_back && dr) hr[i] = x;
         mlr_store(dst, i, (x * scale) * mlr_load(weight, i));
     }
@@ -85,6 +93,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ 
 // load of the row is in flight at the same time.  One block per row.
 template <typename T, typename W>
 __global__ void __launch_bounds__(1024) rmsnorm_cached_kernel(float* __restrict__ h, const float* __restrict__ delta,
+                                                             int slices, size_t slice_stride,
                                                              const W* __restrict__ weight, T* __restrict__ out,
                                                              const int* __restrict__ rows, int width, float eps,
                                                              int write_back) {
@@ -103,7 +112,11 @@ __global__ void __launch_bounds__(1024) rmsnorm_cached_kernel(float* __restrict_
         if (i < quads) {
             x[k] = hr[i];
             if (dr) {
-                const float4 d = dr[i];
+                float4 d = dr[i];
+                for (int s = 1; s < slices; ++s) {
+                    const float4 e = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(dr) + s * slice_stride)[i];
+                    d.x += e.x; d.y += e.y; d.z += e.z; d.w += e.w;
+                }
                 x[k].x += d.x; x[k].y += d.y; x[k].z += d.z; x[k].w += d.w;
             }
         }
@@ -148,8 +161,12 @@ __global__ void residual_add_kernel(float* __restrict__ h, const float* __restri
 // block_table[segment][position / page_size].
 constexpr int kMaxPairsPerLane = 4;  // D/2 <= 128
 
+// With `partials`, the input is not qkv itself but `slices` float32 partial sums of it
+// ([slices][rows][ld_partial]); they are added in order as they are read, and qkv only
+// receives the results.
 template <typename T, typename W>
-__global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, int ld, int rows, int q_heads, int kv_heads,
+__global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ partials, int slices,
+                                          size_t slice_stride, int ld_partial, int rows, int q_heads, int kv_heads,
                                           int head_dim, const W* __restrict__ q_weight,
                                           const W* __restrict__ k_weight, float eps,
                                           const float* __restrict__ cos_sin, int table_positions,
@@ -167,6 +184,8 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, int ld, int rows,
     const int half = head_dim >> 1;
     const int position = positions[row];
     T* x = qkv + static_cast<size_t>(row) * ld + static_cast<size_t>(head) * head_dim;
+    const float* xp = partials ? partials + static_cast<size_t>(row) * ld_partial + static_cast<size_t>(head) * head_dim : nullptr;
+    auto input = [&](int i) { return xp ? sliced(xp + i, slices, slice_stride) : mlr_load(x, i); };
     const bool is_query = head < q_heads;
     const bool is_key = !is_query && head < q_heads + kv_heads;
     const bool is_value = !is_query && !is_key;
@@ -189,7 +208,7 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, int ld, int rows,
     }
     const bool swizzled = mlr_cache_swizzled(sizeof(T) == 2, head_dim);
     if (is_value) {
-        for (int i = lane; i < head_dim; i += 32) dst[mlr_cache_col(i, position, swizzled)] = x[i];
+        for (int i = lane; i < head_dim; i += 32) mlr_store(dst, mlr_cache_col(i, position, swizzled), input(i));
         return;
     }
     float lo[kMaxPairsPerLane], hi[kMaxPairsPerLane];
@@ -199,8 +218,8 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, int ld, int rows,
         const int j = lane + 32 * k;
         lo[k] = hi[k] = 0.0f;
         if (j < half) {
-            lo[k] = mlr_load(x, j);
-            hi[k] = mlr_load(x, j + half);
+            lo[k] = input(j);
+            hi[k] = input(j + half);
             sum = fmaf(lo[k], lo[k], sum);
             sum = fmaf(hi[k], hi[k], sum);
         }
@@ -273,6 +292,20 @@ __global__ void swiglu_vec8_kernel(const T* __restrict__ gate_up, T* __restrict_
     }
 }
 
+// The same from `slices` float32 partial sums of gate_up ([slices][rows][2*inter]).
+template <typename T>
+__global__ void swiglu_sliced_kernel(const float* __restrict__ partials, int slices, size_t slice_stride,
+                                     T* __restrict__ out, int rows, int inter) {
+    const size_t total = static_cast<size_t>(rows) * inter;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t r = i / inter, c = i - r * inter;
+        const float g = sliced(partials + r * 2 * inter + c, slices, slice_stride);
+        const float u = sliced(partials + r * 2 * inter + inter + c, slices, slice_stride);
+        mlr_store(out, i, (g / (1.0f + expf(-g))) * u);
+    }
+}
+
 int row_threads(int width) {
     int t = 32;
     while (t < 256 && t * 4 < width) t <<= 1;
@@ -298,9 +331,11 @@ MLR_API int mlr_embed_gather(float* out, const void* table, int w_bf16, const in
     return mlr_launched("embed_gather");
 }
 
-MLR_API int mlr_rmsnorm(float* h, const float* delta, const void* weight, int w_bf16, void* out, int act_bf16,
-                        const int* rows, int count, int width, float eps, int write_back, cudaStream_t stream) {
+MLR_API int mlr_rmsnorm(float* h, const float* delta, int slices, long long slice_stride, const void* weight, int w_bf16,
+                        void* out, int act_bf16, const int* rows, int count, int width, float eps, int write_back,
+                        cudaStream_t stream) {
     MLR_REQUIRE(count >= 0 && width > 0, "rmsnorm: bad sizes count=%d width=%d", count, width);
+    MLR_REQUIRE(!delta || (slices >= 1 && (slices == 1 || slice_stride >= 1)), "rmsnorm: bad delta slices %d", slices);
     MLR_REQUIRE(eps > 0.0f, "rmsnorm: eps must be positive, got %g", static_cast<double>(eps));
     if (count == 0) return 0;
     const int threads = row_threads(width);
@@ -309,15 +344,17 @@ MLR_API int mlr_rmsnorm(float* h, const float* delta, const void* weight, int w_
     int cached_threads = 32;
     while (cached_threads < 1024 && cached_threads * 4 < width) cached_threads <<= 1;
     const bool cached = width % 4 == 0 && width <= cached_threads * 16 && reinterpret_cast<uintptr_t>(h) % 16 == 0 &&
-                        (!delta || reinterpret_cast<uintptr_t>(delta) % 16 == 0) &&
+                        (!delta || (reinterpret_cast<uintptr_t>(delta) % 16 == 0 && slice_stride % 4 == 0)) &&
                         reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(weight) % 16 == 0;
 #define MLR_LAUNCH(T, W)                                                                                   \
     do {                                                                                                   \
         if (cached)                                                                                        \
             rmsnorm_cached_kernel<T, W><<<count, cached_threads, 0, stream>>>(                             \
-                h, delta, static_cast<const W*>(weight), static_cast<T*>(out), rows, width, eps, write_back); \
+                h, delta, slices, static_cast<size_t>(slice_stride), static_cast<const W*>(weight),       \
+                static_cast<T*>(out), rows, width, eps, write_back);                                       \
         else                                                                                               \
-            rmsnorm_kernel<T, W><<<count, threads, 0, stream>>>(h, delta, static_cast<const W*>(weight),  \
+            rmsnorm_kernel<T, W><<<count, threads, 0, stream>>>(h, delta, slices, static_cast<size_t>(slice_stride), \
+                                                                 static_cast<const W*>(weight),            \
                                                                  static_cast<T*>(out), rows, width, eps, write_back); \
     } while (0)
     if (act_bf16 && w_bf16) MLR_LAUNCH(__nv_bfloat16, __nv_bfloat16);
@@ -336,7 +373,8 @@ MLR_API int mlr_residual_add(float* h, const float* delta, long long count, cuda
     return mlr_launched("residual_add");
 }
 
-MLR_API int mlr_qk_norm_rope_cache(void* qkv, int act_bf16, int ld, int rows, int q_heads, int kv_heads,
+MLR_API int mlr_qk_norm_rope_cache(void* qkv, int act_bf16, int ld, const float* partials, int slices,
+                                   long long slice_stride, int ld_partial, int rows, int q_heads, int kv_heads,
                                    int head_dim, const void* q_weight, const void* k_weight, int w_bf16,
                                    float eps, const float* cos_sin, int rotary_dim, int table_positions,
                                    const int* positions, const int* segment_of_row, const int* block_table,
@@ -348,6 +386,8 @@ MLR_API int mlr_qk_norm_rope_cache(void* qkv, int act_bf16, int ld, int rows, in
     MLR_REQUIRE(cos_sin == nullptr || rotary_dim == head_dim,
                 "qk_norm_rope_cache: rotary size %d differs from head size %d (partial rotation is not built)", rotary_dim, head_dim);
     MLR_REQUIRE(ld >= (q_heads + 2 * kv_heads) * head_dim, "qk_norm_rope_cache: row stride %d is smaller than the qkv width", ld);
+    MLR_REQUIRE(!partials || (slices >= 1 && ld_partial >= (q_heads + 2 * kv_heads) * head_dim),
+                "qk_norm_rope_cache: bad partial sums (%d slices, row stride %d)", slices, ld_partial);
     MLR_REQUIRE((q_weight == nullptr) == (k_weight == nullptr), "qk_norm_rope_cache: q and k norm weights must both be given or both be absent");
     MLR_REQUIRE(!write_cache || (cache && block_table && page_size > 0 && num_pages > 0), "qk_norm_rope_cache: cache write without a cache");
     if (rows == 0) return 0;
@@ -355,7 +395,8 @@ MLR_API int mlr_qk_norm_rope_cache(void* qkv, int act_bf16, int ld, int rows, in
     const dim3 grid(rows, (q_heads + 2 * kv_heads + warps - 1) / warps);
 #define MLR_LAUNCH(T, W)                                                                                       \
     qk_norm_rope_cache_kernel<T, W><<<grid, warps * 32, 0, stream>>>(                                          \
-        static_cast<T*>(qkv), ld, rows, q_heads, kv_heads, head_dim, static_cast<const W*>(q_weight),         \
+        static_cast<T*>(qkv), ld, partials, slices, static_cast<size_t>(slice_stride), ld_partial, rows, q_heads,  \
+        kv_heads, head_dim, static_cast<const W*>(q_weight),                                                   \
         static_cast<const W*>(k_weight), eps, cos_sin, table_positions, positions, segment_of_row, block_table, \
         table_stride, page_size, static_cast<T*>(cache), num_pages, write_cache, status)
     if (act_bf16 && w_bf16) MLR_LAUNCH(__nv_bfloat16, __nv_bfloat16);
@@ -386,4 +427,21 @@ MLR_API int mlr_swiglu(const void* gate_up, void* out, int act_bf16, int rows, i
     else
         swiglu_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float*>(gate_up), static_cast<float*>(out), rows, inter);
     return mlr_launched("swiglu");
+}
+
+// out[rows, inter] = silu(gate) * up from `slices` float32 partial sums of the stacked
+// product [slices][rows][2 * inter].
+MLR_API int mlr_swiglu_sliced(const float* partials, int slices, long long slice_stride, void* out, int act_bf16, int rows,
+                              int inter, cudaStream_t stream) {
+    MLR_REQUIRE(rows >= 0 && inter > 0 && slices >= 1, "swiglu_sliced: bad sizes rows=%d inter=%d slices=%d", rows, inter, slices);
+    if (rows == 0) return 0;
+    const size_t total = static_cast<size_t>(rows) * inter;
+    const int blocks = static_cast<int>(total / 256 + 1 < 148 * 16 ? total / 256 + 1 : 148 * 16);
+    if (act_bf16)
+        swiglu_sliced_kernel<<<blocks, 256, 0, stream>>>(partials, slices, static_cast<size_t>(slice_stride),
+                                                         static_cast<__nv_bfloat16*>(out), rows, inter);
+    else
+        swiglu_sliced_kernel<<<blocks, 256, 0, stream>>>(partials, slices, static_cast<size_t>(slice_stride),
+                                                         static_cast<float*>(out), rows, inter);
+    return mlr_launched("swiglu_sliced");
 }

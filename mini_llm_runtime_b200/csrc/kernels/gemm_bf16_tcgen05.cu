@@ -116,8 +116,9 @@ struct Shape {
 template <int BN>
 __global__ void __launch_bounds__(kThreads) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p,
                                                                 const __grid_constant__ CUtensorMap map_q,
-                                                                void* __restrict__ out, long long ldo, int P, int Q, int K,
-                                                                int out_f32, int swapped, int* status) {
+                                                                void* __restrict__ out_base, long long ldo, int P, int Q, int K,
+                                                                int out_f32, int swapped, int k_splits,
+                                                                long long split_stride, int* status) {
     using S = Shape<BN>;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long barriers[2 * S::kStages + 4];
@@ -157,18 +158,24 @@ __global__ void __launch_bounds__(kThreads) gemm_tcgen05_kernel(const __grid_con
     tmem_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
 
+    // A unit of work is an output tile and one of `k_splits` ranges of K.  With more than one
+    // range, each range's sum goes to its own float32 slice of `out` (split_stride elements
+    // apart); whoever reads the result adds the slices up in order.
     const int tiles_p = (P + kTileP - 1) / kTileP, tiles_q = (Q + BN - 1) / BN;
-    const int tiles = tiles_p * tiles_q;
-    const int k_blocks = (K + kTileK - 1) / kTileK;
+    const int tiles = tiles_p * tiles_q * k_splits;
+    const int all_k_blocks = (K + kTileK - 1) / kTileK;
+    auto split_of = [&](int unit) { return unit / (tiles_p * tiles_q); };
+    auto first_block = [&](int split) { return static_cast<int>(static_cast<long long>(all_k_blocks) * split / k_splits); };
 
     if (warp == 0) {
         // ---------------- loads
         if (lane == 0) {
             bool ok = true;
             int it = 0;
-            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+            for (int unit = blockIdx.x; unit < tiles && ok; unit += gridDim.x) {
+                const int tile = unit % (tiles_p * tiles_q), split = split_of(unit);
                 const int p0 = (tile % tiles_p) * kTileP, q0 = (tile / tiles_p) * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                for (int kb = first_block(split); kb < first_block(split + 1); ++kb, ++it) {
                     const int stage = it % S::kStages;
                     if (it >= S::kStages) ok = mbar_wait(empty_bar(stage), ((it / S::kStages) - 1) & 1);
                     if (!ok) break;
@@ -185,13 +192,14 @@ __global__ void __launch_bounds__(kThreads) gemm_tcgen05_kernel(const __grid_con
             constexpr uint32_t idesc = instruction_descriptor(BN);
             bool ok = true;
             int it = 0, local = 0;
-            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+            for (int unit = blockIdx.x; unit < tiles && ok; unit += gridDim.x, ++local) {
                 const int acc = local & 1;
                 if (local >= 2) ok = mbar_wait(acc_empty_bar(acc), ((local >> 1) - 1) & 1);
                 if (!ok) break;
                 tmem_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int kb0 = first_block(split_of(unit)), kb1 = first_block(split_of(unit) + 1);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int stage = it % S::kStages;
                     ok = mbar_wait(full_bar(stage), (it / S::kStages) & 1);
                     if (!ok) break;
@@ -199,7 +207,7 @@ __global__ void __launch_bounds__(kThreads) gemm_tcgen05_kernel(const __grid_con
                     const uint64_t desc_p = smem_descriptor(tile_p(stage)), desc_q = smem_descriptor(tile_q(stage));
 #pragma unroll
                     for (int k = 0; k < kTileK / 16; ++k)      // 16 bf16 = 32 bytes = 2 descriptor units further along K
-                        umma_bf16(tmem_d, desc_p + 2 * k, desc_q + 2 * k, idesc, (kb | k) != 0);
+                        umma_bf16(tmem_d, desc_p + 2 * k, desc_q + 2 * k, idesc, kb > kb0 || k > 0);
                     umma_commit(empty_bar(stage));             // the stage is free once these instructions have read it
                 }
                 if (!ok) break;
@@ -212,9 +220,11 @@ __global__ void __launch_bounds__(kThreads) gemm_tcgen05_kernel(const __grid_con
         const int quarter = warp & 3;
         bool ok = true;
         int local = 0;
-        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+        for (int unit = blockIdx.x; unit < tiles; unit += gridDim.x, ++local) {
             const int acc = local & 1;
+            const int tile = unit % (tiles_p * tiles_q);
             const int p0 = (tile % tiles_p) * kTileP, q0 = (tile / tiles_p) * BN;
+            void* out = static_cast<char*>(out_base) + static_cast<size_t>(split_of(unit)) * split_stride * (out_f32 ? 4 : 2);
             ok = mbar_wait(acc_full_bar(acc), (local >> 1) & 1);
             if (!ok) break;
             tmem_fence_after();
@@ -320,7 +330,7 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
 
 template <int BN>
 int launch(const CUtensorMap& map_p, const CUtensorMap& map_q, void* out, long long ldo, int P, int Q, int K, int out_f32,
-           int swapped, int* status, int sms, cudaStream_t stream) {
+           int swapped, int k_splits, long long split_stride, int* status, int sms, cudaStream_t stream) {
     using S = Shape<BN>;
     const size_t bytes = static_cast<size_t>(S::kStages) * S::kStageBytes + 1024;
     static thread_local bool allowed = false;
@@ -330,9 +340,10 @@ int launch(const CUtensorMap& map_p, const CUtensorMap& map_q, void* out, long l
         if (e != cudaSuccess) return mlr_fail("gemm_bf16_tcgen05: cannot use %zu bytes of shared memory: %s", bytes, cudaGetErrorString(e));
         allowed = true;
     }
-    const int tiles = ((P + kTileP - 1) / kTileP) * ((Q + BN - 1) / BN);
+    const int tiles = ((P + kTileP - 1) / kTileP) * ((Q + BN - 1) / BN) * k_splits;
     const int grid = tiles < sms ? tiles : sms;
-    gemm_tcgen05_kernel<BN><<<grid, kThreads, bytes, stream>>>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, status);
+    gemm_tcgen05_kernel<BN><<<grid, kThreads, bytes, stream>>>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, k_splits,
+                                                               split_stride, status);
     return mlr_launched("gemm_bf16_tcgen05");
 }
 
@@ -341,9 +352,13 @@ int launch(const CUtensorMap& map_p, const CUtensorMap& map_q, void* out, long l
 // out[p, q] = sum_k Pm[p, k] Qm[q, k]; stored at out[p * ldo + q] (swapped = 0) or
 // out[q * ldo + p] (swapped = 1), as bfloat16 or float32.  Pm is [P, K] with row stride ldp,
 // Qm is [Q, K] with row stride ldq (elements).  tile_q: 16, 32, 64, 128 or 256 columns of Qm
-// per tile (0 lets the function choose).
+// per tile (0 lets the function choose).  k_splits > 1 cuts K into that many ranges; range s
+// writes its sum to the float32 slice out + s * split_stride, and the reader adds the slices.
 MLR_API int mlr_gemm_bf16_tcgen05(const void* Pm, long long ldp, int P, const void* Qm, long long ldq, int Q, int K, void* out,
-                                  long long ldo, int out_f32, int swapped, int tile_q, int* status, cudaStream_t stream) {
+                                  long long ldo, int out_f32, int swapped, int tile_q, int k_splits, long long split_stride,
+                                  int* status, cudaStream_t stream) {
+    MLR_REQUIRE(k_splits >= 1 && k_splits <= (K + kTileK - 1) / kTileK, "gemm_bf16_tcgen05: %d splits of K = %d", k_splits, K);
+    MLR_REQUIRE(k_splits == 1 || (out_f32 && split_stride >= 1), "gemm_bf16_tcgen05: split results are float32 slices");
     MLR_REQUIRE(P >= 1 && Q >= 1 && K >= 8, "gemm_bf16_tcgen05: bad sizes P=%d Q=%d K=%d", P, Q, K);
     MLR_REQUIRE(K % 8 == 0 && ldp % 8 == 0 && ldq % 8 == 0 && ldp >= K && ldq >= K,
                 "gemm_bf16_tcgen05: K and the operand row strides must be multiples of 8 elements (16 bytes), got K=%d", K);
@@ -361,10 +376,10 @@ MLR_API int mlr_gemm_bf16_tcgen05(const void* Pm, long long ldp, int P, const vo
     if (int e = make_map(&map_p, Pm, P, K, ldp, kTileP)) return e;
     if (int e = make_map(&map_q, Qm, Q, K, ldq, tile_q)) return e;
     switch (tile_q) {
-        case 16: return launch<16>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, status, sms, stream);
-        case 32: return launch<32>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, status, sms, stream);
-        case 64: return launch<64>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, status, sms, stream);
-        case 128: return launch<128>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, status, sms, stream);
-        default: return launch<256>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, status, sms, stream);
+        case 16: return launch<16>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, k_splits, split_stride, status, sms, stream);
+        case 32: return launch<32>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, k_splits, split_stride, status, sms, stream);
+        case 64: return launch<64>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, k_splits, split_stride, status, sms, stream);
+        case 128: return launch<128>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, k_splits, split_stride, status, sms, stream);
+        default: return launch<256>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, k_splits, split_stride, status, sms, stream);
     }
 }

@@ -116,6 +116,7 @@ class Model:
         self.max_graphs = 48
         self._graphs = {}
         self._graph_pool = None
+        self.graph_launches = 0
 
     # ------------------------------------------------------------------ weights
     def _all_parts(self):
@@ -330,11 +331,14 @@ class Model:
             torch.cuda.current_stream().wait_stream(side)
             graph = torch.cuda.CUDAGraph()
             step.scratch.clear()
+            from ..ops import native
+            before = native.launch_count
             with torch.cuda.graph(graph, pool=self._graph_pool):
                 logits = self._forward(step, want)
-            entry = (graph, static, logits)
+            entry = (graph, static, logits, native.launch_count - before)
             self._graphs[key] = entry
-        graph, static, logits = entry
+        graph, static, logits, kernels = entry
+        self.graph_launches += kernels      # launches of this package's kernels a replay stands for
         static.copy_(host, non_blocking=True)
         self._pinned[self._pinned_current][1].record()
         if device_tokens is not None:

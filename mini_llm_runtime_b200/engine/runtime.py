@@ -33,7 +33,11 @@ class Runtime:
         # The 32-bit path must not be silently lowered by library defaults either.
         torch.backends.cuda.matmul.allow_tf32 = False
         torch.backends.cudnn.allow_tf32 = False
-        self.use_gemv = False     # few-token products on the package's mma.sync weight streamer (slower than the library today)
+        self.use_tcgen05 = True       # bf16 products on the package's tcgen05/TMA kernel
+        self.tcgen05_prefill = False  # ... also for prompt portions (else the vendor library takes those)
+        self.decode_rows = 64         # up to this many rows a product streams the weights (swapped operands, split K)
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self._splits = {}
         self.status = None        # the model's device status word (set at bind time)
         self._shared = {}
 
@@ -64,27 +68,51 @@ class Runtime:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
 
     # ---- y = x @ w.T
+    def _own_gemm(self, x: torch.Tensor, w: torch.Tensor) -> bool:
+        """Whether this bf16 product runs on the package's tcgen05 kernel: always for the few
+        rows of a decode step; for prompt portions only when `tcgen05_prefill` is set (the
+        vendor library's two-SM kernels are still faster there)."""
+        return (self.use_tcgen05 and self.status is not None and F.gemm_tcgen05_applies(x, w)
+                and (x.shape[0] <= self.decode_rows or self.tcgen05_prefill))
+
     def linear(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         out_dtype = out_dtype or self.dtype
         if self.dtype is torch.float32:
             out = torch.empty((x.shape[0], w.shape[0]), dtype=torch.float32, device=self.device)
             F.gemm_f32(x, w, out)
             return out
-        if self.use_gemv and self.status is not None and F.gemv_applies(x, w):
+        if self._own_gemm(x, w):
             out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=self.device)
-            F.gemv_bf16(x, w, out, self.status)
+            F.gemm_bf16_tcgen05(x, w, out, self.status)
             return out
         if out_dtype is torch.bfloat16:
             return torch.mm(x, w.t())
         return torch.mm(x, w.t(), out_dtype=out_dtype)
 
+    def linear_partials(self, x: torch.Tensor, w: torch.Tensor) -> Optional[torch.Tensor]:
+        """For the few rows of a decode step: the product as float32 partial sums [S, M, N]
+        over S ranges of K (so that a small weight matrix still occupies every SM); the
+        kernel that reads them adds them up.  None when the product is not of that kind."""
+        if self.dtype is not torch.bfloat16 or x.shape[0] > self.decode_rows or not self._own_gemm(x, w):
+            return None
+        key = (w.shape[0], w.shape[1])
+        splits = self._splits.get(key)
+        if splits is None:
+            splits = self._splits[key] = F.k_splits_for(w.shape[0], w.shape[1], self.sm_count)
+        out = torch.empty((splits, x.shape[0], w.shape[0]), dtype=torch.float32, device=self.device)
+        F.gemm_bf16_tcgen05(x, w, out, self.status)
+        return out
+
+    def linear_delta(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """A float32 contribution to the residual stream: [M, N], or [S, M, N] partial sums
+        that the next norm adds up."""
+        parts = self.linear_partials(x, w)
+        return parts if parts is not None else self.linear(x, w, out_dtype=torch.float32)
+
     def gated_linear(self, x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
-        """silu(x Wgate^T) * (x Wup^T) for the stacked matrix [2 I, K]: one fused kernel for a
-        few tokens, else the product followed by the gate kernel."""
+        """silu(x Wgate^T) * (x Wup^T) for the stacked matrix [2 I, K]."""
         inter = w_gate_up.shape[0] // 2
         out = torch.empty((x.shape[0], inter), dtype=self.dtype, device=self.device)
-        if self.dtype is torch.bfloat16 and self.use_gemv and self.status is not None and F.gemv_applies(x, w_gate_up):
-            F.gemv_bf16(x, w_gate_up, out, self.status, swiglu=True)
-            return out
-        F.swiglu(self.linear(x, w_gate_up), out)
+        parts = self.linear_partials(x, w_gate_up)
+        F.swiglu(parts if parts is not None else self.linear(x, w_gate_up), out)
         return out

@@ -27,17 +27,21 @@ def rmsnorm(h: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
             delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
             write_back: bool = True) -> None:
     """out[r] = rmsnorm(h[row] + delta[row]) * weight with row = rows[r] (or r).  With
-    `write_back` the sum is stored to h[row], which moves the residual stream on."""
+    `write_back` the sum is stored to h[row], which moves the residual stream on.
+    `delta` may be [S, M, H]: S partial sums that are added in order first."""
     on_gpu(h, weight, out, delta, rows)
     expect(h, torch.float32, "the residual stream")
+    slices, slice_stride = 1, 0
     if delta is not None:
         expect(delta, torch.float32, "the residual delta")
-        if delta.shape != h.shape:
+        if delta.dim() == 3:
+            slices, slice_stride = delta.shape[0], delta.stride(0)
+        if tuple(delta.shape[-2:]) != tuple(h.shape):
             raise KernelError("residual delta and residual stream differ in shape")
     if rows is not None:
         expect(rows, torch.int32, "row indices")
     count = out.shape[0]
-    call("elementwise", "mlr_rmsnorm", ptr(h), ptr(delta), ptr(weight), is_bf16(weight), ptr(out), is_bf16(out),
+    call("elementwise", "mlr_rmsnorm", ptr(h), ptr(delta), slices, slice_stride, ptr(weight), is_bf16(weight), ptr(out), is_bf16(out),
          ptr(rows), count, h.shape[1], float(eps), int(write_back), stream())
 
 
@@ -52,11 +56,18 @@ def qk_norm_rope_cache(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim:
                        q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                        cos_sin: Optional[torch.Tensor], positions: torch.Tensor, segment_of_row: torch.Tensor,
                        block_table: Optional[torch.Tensor], page_size: int, cache: Optional[torch.Tensor],
-                       write_cache: bool, status: torch.Tensor) -> None:
+                       write_cache: bool, status: torch.Tensor, partials: Optional[torch.Tensor] = None) -> None:
     """In place on qkv [M, (Hq + 2 Hkv) D]: per-head RMS norm of q and k, rotation by
     the table row of each position, and the write of k and v into the layer's cache
-    [page, 2, Hkv, page_size, D]."""
-    on_gpu(qkv, q_weight, k_weight, cos_sin, positions, segment_of_row, block_table, cache, status)
+    [page, 2, Hkv, page_size, D].  With `partials` (float32 [S, M, width]) the input is the
+    sum of those slices instead, and qkv only receives the results."""
+    on_gpu(qkv, q_weight, k_weight, cos_sin, positions, segment_of_row, block_table, cache, status, partials)
+    slices, slice_stride, ld_partial = 0, 0, 0
+    if partials is not None:
+        expect(partials, torch.float32, "the partial sums")
+        if partials.dim() != 3 or partials.shape[1] != qkv.shape[0]:
+            raise KernelError("qk_norm_rope_cache: partial sums must be [S, M, width]")
+        slices, slice_stride, ld_partial = partials.shape[0], partials.stride(0), partials.stride(1)
     expect(positions, torch.int32, "positions")
     expect(segment_of_row, torch.int32, "segment_of_row")
     if cos_sin is not None:
@@ -66,7 +77,8 @@ def qk_norm_rope_cache(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim:
         if cache.dtype is not qkv.dtype:
             raise KernelError(f"cache dtype {cache.dtype} differs from activation dtype {qkv.dtype}")
     w_bf16 = is_bf16(q_weight) if q_weight is not None else 0
-    call("elementwise", "mlr_qk_norm_rope_cache", ptr(qkv), is_bf16(qkv), qkv.stride(0), qkv.shape[0], q_heads,
+    call("elementwise", "mlr_qk_norm_rope_cache", ptr(qkv), is_bf16(qkv), qkv.stride(0), ptr(partials), slices,
+         slice_stride, ld_partial, qkv.shape[0], q_heads,
          kv_heads, head_dim, ptr(q_weight), ptr(k_weight), w_bf16, float(eps), ptr(cos_sin),
          cos_sin.shape[1] if cos_sin is not None else 0, cos_sin.shape[0] if cos_sin is not None else 0,
          ptr(positions), ptr(segment_of_row), ptr(block_table),
@@ -75,8 +87,16 @@ def qk_norm_rope_cache(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim:
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+    """out = silu(gate_up[:, :I]) * gate_up[:, I:].  gate_up may also be float32
+    [S, M, 2 I]: S partial sums that are added in order first."""
     on_gpu(gate_up, out)
+    if gate_up.dim() == 3:
+        expect(gate_up, torch.float32, "the partial sums")
+        if not out.is_contiguous() or gate_up.shape[2] != 2 * out.shape[1] or gate_up.shape[1] != out.shape[0]:
+            raise KernelError("swiglu: partial sums [S, M, 2 I] do not fit the output [M, I]")
+        call("elementwise", "mlr_swiglu_sliced", ptr(gate_up), gate_up.shape[0], gate_up.stride(0), ptr(out), is_bf16(out),
+             out.shape[0], out.shape[1], stream())
+        return
     if not gate_up.is_contiguous() or not out.is_contiguous() or gate_up.dtype is not out.dtype:
         raise KernelError("swiglu wants contiguous tensors of one dtype")
     call("elementwise", "mlr_swiglu", ptr(gate_up), ptr(out), is_bf16(out), out.shape[0], out.shape[1], stream())
@@ -210,20 +230,47 @@ def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, statu
     """out[M, N] = x[M, K] @ w[N, K]^T on the tcgen05 tensor cores (bf16 in, float32
     accumulate in tensor memory, out bf16 or float32).  With up to 64 rows of x the weight
     matrix takes the 128-row side of the instruction and the result is stored transposed
-    (the product is then a single pass over the weights); otherwise x takes that side."""
+    (the product is then a single pass over the weights); otherwise x takes that side.
+
+    `out` may also be float32 [S, M, N]: K is then cut into S ranges and slice s holds the
+    sum over range s (more thread blocks share a small matrix); the reader adds the slices."""
     on_gpu(x, w, out, status)
     if not gemm_tcgen05_applies(x, w):
         raise KernelError("gemm_bf16_tcgen05: operands must be bfloat16, K-contiguous, 16-byte aligned, K % 8 == 0")
-    if out.dtype not in (torch.bfloat16, torch.float32) or out.stride(1) != 1:
+    if out.dtype not in (torch.bfloat16, torch.float32) or out.stride(-1) != 1:
         raise KernelError("gemm_bf16_tcgen05: the output must be bfloat16 or float32 with unit inner stride")
     M, K = x.shape
     N = w.shape[0]
-    if w.shape[1] != K or out.shape != (M, N):
+    splits, split_stride = 1, 0
+    if out.dim() == 3:
+        splits, split_stride = out.shape[0], out.stride(0)
+        if out.dtype is not torch.float32:
+            raise KernelError("gemm_bf16_tcgen05: split results must be float32")
+    if w.shape[1] != K or tuple(out.shape[-2:]) != (M, N):
         raise KernelError(f"gemm_bf16_tcgen05: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} do not fit")
     f32 = int(out.dtype is torch.float32)
+    ldo = out.stride(-2)
     if M <= 64:
         call("gemm_bf16_tcgen05", "mlr_gemm_bf16_tcgen05", ptr(w), w.stride(0), N, ptr(x), x.stride(0), M, K, ptr(out),
-             out.stride(0), f32, 1, tile_q, ptr(status), stream())
+             ldo, f32, 1, tile_q, splits, split_stride, ptr(status), stream())
     else:
         call("gemm_bf16_tcgen05", "mlr_gemm_bf16_tcgen05", ptr(x), x.stride(0), M, ptr(w), w.stride(0), N, K, ptr(out),
-             out.stride(0), f32, 0, tile_q, ptr(status), stream())
+             ldo, f32, 0, tile_q, splits, split_stride, ptr(status), stream())
+
+
+def k_splits_for(rows: int, K: int, sms: int = 148) -> int:
+    """How many ranges to cut K into when a weight matrix of `rows` rows is streamed in tiles
+    of 128 rows: the smallest count whose units fill whole rounds of `sms` blocks to 93 % or
+    better, with at least four 64-wide blocks of K per range and at most 16 ranges."""
+    tiles = -(-rows // 128)
+    best, best_fill = 1, 0.0
+    for s in range(1, 17):
+        if s > 1 and -(-K // 64) // s < 4:
+            break
+        units = tiles * s
+        fill = units / (sms * -(-units // sms))
+        if fill > best_fill + 1e-9:
+            best, best_fill = s, fill
+        if fill >= 0.93:
+            return s
+    return best

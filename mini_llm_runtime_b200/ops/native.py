@@ -25,9 +25,12 @@ class KernelError(RuntimeError):
 _SIGNATURES = {
     "elementwise": {
         "mlr_embed_gather": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
-        "mlr_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+        "mlr_rmsnorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
+                        c_float, c_int, c_void_p],
+        "mlr_swiglu_sliced": [c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
         "mlr_residual_add": [c_void_p, c_void_p, c_longlong, c_void_p],
-        "mlr_qk_norm_rope_cache": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+        "mlr_qk_norm_rope_cache": [c_void_p, c_int, c_int, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int,
+                                   c_void_p, c_void_p, c_int,
                                    c_float, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                    c_void_p, c_int, c_int, c_void_p, c_void_p],
         "mlr_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -51,7 +54,7 @@ _SIGNATURES = {
     },
     "gemm_bf16_tcgen05": {
         "mlr_gemm_bf16_tcgen05": [c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong,
-                                  c_int, c_int, c_int, c_void_p, c_void_p],
+                                  c_int, c_int, c_int, c_int, c_longlong, c_void_p, c_void_p],
     },
     "sampling": {
         "mlr_sample": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],

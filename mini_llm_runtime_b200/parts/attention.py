@@ -55,7 +55,8 @@ class AttentionMixer(Mixer):
         return specs
 
     def kernel_modules(self, dtype) -> List[str]:
-        return ["elementwise"] + A.modules_for(dtype, self.head_dim) + (["gemm_f32"] if dtype is torch.float32 else [])
+        return ["elementwise"] + A.modules_for(dtype, self.head_dim) + (
+            ["gemm_f32"] if dtype is torch.float32 else ["gemm_bf16_tcgen05"])
 
     def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
         w = self.spec.weights
@@ -70,17 +71,18 @@ class AttentionMixer(Mixer):
     def forward(self, x: torch.Tensor, step: StepContext, run: RunContext) -> torch.Tensor:
         rt = step.rt
         D = self.head_dim
-        qkv = rt.linear(x, self.w_qkv)
+        partials = rt.linear_partials(x, self.w_qkv)
+        qkv = rt.empty(x.shape[0], self.w_qkv.shape[0]) if partials is not None else rt.linear(x, self.w_qkv)
         table = step.tables[run.group]
         rotation = self.position.rotation_table() if self.position is not None else None
         F.qk_norm_rope_cache(qkv, self.heads, self.kv_heads, D, self.q_norm, self.k_norm,
                              self.qk_norm_eps if self.qk_norm_eps is not None else 1.0, rotation,
                              step.positions, step.segment_of_row, table, step.page_size, run.cache,
-                             run.write_cache, step.status)
+                             run.write_cache, step.status, partials=partials)
         out = rt.empty(x.shape[0], self.heads * D)
         A.paged_attention(qkv, out, run.cache, table, step, self.heads, self.kv_heads, D,
                           self.window or 0, self.scale, cache_group=run.group)
-        return rt.linear(out, self.w_o, out_dtype=torch.float32)
+        return rt.linear_delta(out, self.w_o)
 
 
 register_part("mixer", "attention", AttentionMixer)

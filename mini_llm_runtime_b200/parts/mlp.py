@@ -32,7 +32,7 @@ class SwiGLU(FeedForward):
                 WeightSpec(w["down"], (self.width, self.inter))]
 
     def kernel_modules(self, dtype) -> List[str]:
-        return ["elementwise"] + (["gemm_f32"] if dtype is torch.float32 else ["gemv_bf16"])
+        return ["elementwise"] + (["gemm_f32"] if dtype is torch.float32 else ["gemm_bf16_tcgen05"])
 
     def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
         w = self.spec.weights
@@ -42,7 +42,7 @@ class SwiGLU(FeedForward):
     def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
         rt = step.rt
         act = rt.gated_linear(x, self.w_gate_up)
-        return rt.linear(act, self.w_down, out_dtype=torch.float32)
+        return rt.linear_delta(act, self.w_down)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

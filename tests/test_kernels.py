@@ -66,6 +66,49 @@ def test_rmsnorm_with_residual_add(rows, width, out_dtype, w_dtype):
     assert torch.allclose(out2[:1].double().cpu(), P.rms_norm(h[rows - 1:].double(), w.double(), eps), rtol=tol, atol=tol)
 
 
+def test_consumers_add_up_partial_sums():
+    """A product whose K was cut into ranges leaves float32 partial sums; the norm, the
+    gate and the q/k kernel add them up (in order) as they read them."""
+    from mini_llm_runtime_b200.parts.rotary import rotation_table
+    S, M, H = 3, 5, 96
+    parts = torch.randn(S, M, H, generator=gen(0))
+    h = torch.randn(M, H, generator=gen(1))
+    w = (1 + 0.1 * torch.randn(H, generator=gen(2)))
+    total = (parts[0] + parts[1]) + parts[2]
+    for width in (96, 70):                           # the register-cached kernel and the plain one
+        hd, out = h[:, :width].contiguous().to(DEV), torch.empty(M, width, device=DEV)
+        F().rmsnorm(hd, w[:width].contiguous().to(DEV), 1e-5, out, delta=parts[:, :, :width].contiguous().to(DEV))
+        want_h = h[:, :width] + total[:, :width]
+        assert torch.equal(hd.cpu(), want_h)
+        assert torch.allclose(out.cpu(), P.rms_norm(want_h, w[:width], 1e-5), atol=1e-5, rtol=1e-5)
+    # The gate.
+    I = 40
+    gu = torch.randn(S, M, 2 * I, generator=gen(3))
+    act = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    F().swiglu(gu.to(DEV), act)
+    t = (gu[0] + gu[1]) + gu[2]
+    want = t[:, :I] / (1 + torch.exp(-t[:, :I])) * t[:, I:]
+    assert torch.allclose(act.float().cpu(), want, atol=2e-2, rtol=2e-2)
+    # q/k norm, rotation and cache write from partial sums equal the same from their sum.
+    Hq, Hkv, D, page = 4, 2, 64, 8
+    segs = [(3, 4), (0, 2)]
+    rows = 6
+    qkv_parts = torch.randn(S, rows, (Hq + 2 * Hkv) * D, generator=gen(4))
+    summed = ((qkv_parts[0] + qkv_parts[1]) + qkv_parts[2])
+    positions, seg_of_row, info = segments_meta(segs)
+    table_cs = rotation_table(1e4, D, 32).to(DEV)
+    wq, wk = torch.ones(D, device=DEV), torch.ones(D, device=DEV)
+    results = []
+    for use_parts in (True, False):
+        cache, table = make_cache([(torch.zeros(s + c, Hkv, D), torch.zeros(s + c, Hkv, D)) for s, c in segs], page,
+                                  torch.float32, seed=1)
+        qkv = torch.zeros(rows, (Hq + 2 * Hkv) * D, device=DEV) if use_parts else summed.to(DEV)
+        F().qk_norm_rope_cache(qkv, Hq, Hkv, D, wq, wk, 1e-5, table_cs, positions, seg_of_row, table, page, cache, True,
+                               status(), partials=qkv_parts.to(DEV) if use_parts else None)
+        results.append((qkv[:, :(Hq + Hkv) * D].cpu(), torch.nan_to_num(cache).cpu()))
+    assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
+
+
 @pytest.mark.parametrize("rows,inter", [(3, 176), (17, 12288), (1, 7)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_swiglu(rows, inter, dtype):
@@ -164,6 +207,13 @@ def test_gemm_bf16_tcgen05(M, N, K, out_dtype):
     out2 = torch.empty_like(out)
     F().gemm_bf16_tcgen05(wide[:, :K], w, out2, st)
     assert torch.equal(out2, out)
+    # K cut into ranges: the slices add up to the product.
+    if K >= 256 and out_dtype is torch.float32:
+        for splits in (2, 3):
+            parts = torch.full((splits, M, N), float("nan"), device=DEV)
+            F().gemm_bf16_tcgen05(x, w, parts, st)
+            assert st.item() == 0
+            assert torch.allclose(parts.double().sum(0), want, atol=tol * (1 + want.abs().max().item()), rtol=tol)
 
 
 def test_gemm_bf16_tcgen05_every_tile_width():
