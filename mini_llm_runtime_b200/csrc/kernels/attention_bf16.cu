@@ -361,6 +361,8 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
     const int* __restrict__ segment_info, const int* __restrict__ block_table, int table_stride,
     int page_size, int q_heads, int kv_heads, int head_dim, int window, float scale, int chunk,
     int max_splits, float* __restrict__ partial, int* status) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
     // BLOCKS: the cache rows are stored swizzled (head size 64, 128 or 256 = DMAX), so whole
     // page blocks are copied byte for byte into unpadded tiles.  Otherwise rows are stored
     // plainly and are copied one by one into padded tiles.
@@ -600,6 +602,8 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
 __global__ void __launch_bounds__(kThreads) combine_kernel(
     __nv_bfloat16* __restrict__ out, int ldo, const int* __restrict__ items, const int* __restrict__ segment_info,
     int q_heads, int kv_heads, int head_dim, int window, int chunk, int max_splits, const float* __restrict__ partial) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
     extern __shared__ float factor[];   // [splits][16]
     const int item = blockIdx.x, kv_head = blockIdx.y;
     const int segment = items ? items[item] : item;
@@ -650,6 +654,8 @@ __global__ void __launch_bounds__(kThreads) prefill_kernel(
     const __nv_bfloat16* __restrict__ cache, int num_pages, const int* __restrict__ tiles,
     const int* __restrict__ segment_info, const int* __restrict__ block_table, int table_stride,
     int page_size, int q_heads, int kv_heads, int head_dim, int window, float scale, int* status) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int bad_page;
     const int head = blockIdx.y;
@@ -821,7 +827,7 @@ MLR_API int mlr_attention_decode_bf16(const void* q, int ldq, void* out, int ldo
         const size_t stages = static_cast<size_t>(kDecodeStages) * 2 * tile;                                       \
         const size_t bytes = stages > merge ? stages : merge;                                                      \
         if (int e = allow_smem(decode_splitkv_kernel<DMAX, BLOCKS>, bytes, "attention_decode_bf16")) return e;    \
-        decode_splitkv_kernel<DMAX, BLOCKS><<<grid, kDecodeThreads, bytes, stream>>>(                              \
+        mlr_launch((decode_splitkv_kernel<DMAX, BLOCKS>), dim3(grid), dim3(kDecodeThreads), bytes, stream,                               \
             static_cast<const __nv_bfloat16*>(q), ldq, static_cast<__nv_bfloat16*>(out), ldo,                      \
             static_cast<const __nv_bfloat16*>(cache), num_pages, items, segment_info, block_table, table_stride,   \
             page_size, q_heads, kv_heads, head_dim, window, scale, chunk, max_splits, partial, status);            \
@@ -835,7 +841,7 @@ MLR_API int mlr_attention_decode_bf16(const void* q, int ldq, void* out, int ldo
 #undef MLR_LAUNCH
     if (int e = mlr_launched("attention_decode_bf16")) return e;
     if (max_splits > 1) {
-        combine_kernel<<<combine_grid, kThreads, sizeof(float) * 16 * max_splits, stream>>>(static_cast<__nv_bfloat16*>(out), ldo, items, segment_info,
+        mlr_launch((combine_kernel), dim3(combine_grid), dim3(kThreads), sizeof(float) * 16 * max_splits, stream, static_cast<__nv_bfloat16*>(out), ldo, items, segment_info,
                                                              q_heads, kv_heads, head_dim, window, chunk, max_splits, partial);
         return mlr_launched("attention_decode_bf16 combine");
     }
@@ -894,7 +900,7 @@ MLR_API int mlr_attention_prefill_bf16(const void* q, int ldq, void* out, int ld
 #define MLR_LAUNCH(DMAX)                                                                                          \
     do {                                                                                                          \
         if (int e = allow_smem(prefill_kernel<DMAX>, tile_smem<DMAX>(kPrefillStages), "attention_prefill_bf16")) return e; \
-        prefill_kernel<DMAX><<<grid, kThreads, tile_smem<DMAX>(kPrefillStages), stream>>>(                        \
+        mlr_launch((prefill_kernel<DMAX>), dim3(grid), dim3(kThreads), tile_smem<DMAX>(kPrefillStages), stream,                         \
             static_cast<const __nv_bfloat16*>(q), ldq, static_cast<__nv_bfloat16*>(out), ldo,                     \
             static_cast<const __nv_bfloat16*>(cache), num_pages, tiles, segment_info, block_table, table_stride,  \
             page_size, q_heads, kv_heads, head_dim, window, scale, status);                                       \

@@ -30,6 +30,8 @@ __global__ void __launch_bounds__(kThreads) attention_generic_kernel(
     int num_pages, const int* __restrict__ positions, const int* __restrict__ segment_of_row,
     const int* __restrict__ block_table, int table_stride, int page_size, int q_heads, int kv_heads,
     int head_dim, int window, float scale, int* status) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
     extern __shared__ __align__(16) unsigned char smem[];
     long long* offsets = reinterpret_cast<long long*>(smem);  // [kTile] element offset of the token's K row
     float* scores = reinterpret_cast<float*>(offsets + kTile);  // [kTile]
@@ -139,12 +141,12 @@ MLR_API int mlr_attention_generic(const void* q, int ldq, void* out, int ldo, in
     const size_t shared = sizeof(float) * (head_dim + kTile) + sizeof(long long) * kTile + 16;
     const dim3 grid(rows, q_heads);
     if (act_bf16)
-        attention_generic_kernel<<<grid, kThreads, shared, stream>>>(
+        mlr_launch((attention_generic_kernel<__nv_bfloat16>), dim3(grid), dim3(kThreads), shared, stream, 
             static_cast<const __nv_bfloat16*>(q), ldq, static_cast<__nv_bfloat16*>(out), ldo,
             static_cast<const __nv_bfloat16*>(cache), num_pages, positions, segment_of_row, block_table,
             table_stride, page_size, q_heads, kv_heads, head_dim, window, scale, status);
     else
-        attention_generic_kernel<<<grid, kThreads, shared, stream>>>(
+        mlr_launch((attention_generic_kernel<float>), dim3(grid), dim3(kThreads), shared, stream, 
             static_cast<const float*>(q), ldq, static_cast<float*>(out), ldo, static_cast<const float*>(cache),
             num_pages, positions, segment_of_row, block_table, table_stride, page_size, q_heads, kv_heads,
             head_dim, window, scale, status);

@@ -14,6 +14,8 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
+#include <utility>
 
 #define MLR_API extern "C" __attribute__((visibility("default")))
 
@@ -34,6 +36,43 @@ static int mlr_launched(const char* what) {
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return mlr_fail("%s: launch failed: %s", what, cudaGetErrorString(e));
     return 0;
+}
+
+// ---- programmatic dependent launch ----
+// Every kernel of the package is launched with the attribute that lets the NEXT kernel of
+// the stream be set up and scheduled while this one still runs.  In exchange each kernel
+//   * calls mlr_grid_dependents_may_start() at its top: once all blocks of a grid have done
+//     so, the blocks of the following grid may be placed on free SM resources, and
+//   * calls mlr_grid_wait() before it first reads or writes memory that earlier kernels
+//     touch: the call returns when all earlier grids have finished and their writes are
+//     visible.  What a kernel does before that call (barrier set-up, tensor memory, loads of
+//     weights, which no kernel writes) overlaps the tail of its predecessor.
+// MLR_PDL=0 in the environment launches kernels the ordinary way (both calls are then no-ops
+// in effect).
+__device__ __forceinline__ void mlr_grid_dependents_may_start() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+__device__ __forceinline__ void mlr_grid_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+static bool mlr_pdl_enabled() {
+    static const bool enabled = [] {
+        const char* v = getenv("MLR_PDL");
+        return !(v && v[0] == '0');
+    }();
+    return enabled;
+}
+
+template <typename... KArgs, typename... Args>
+static void mlr_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = mlr_pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);   // an error shows in mlr_launched()
 }
 
 #define MLR_REQUIRE(condition, ...) \

@@ -19,6 +19,8 @@ namespace {
 template <typename W>
 __global__ void embed_gather_kernel(float* __restrict__ out, const W* __restrict__ table,
                                     const int* __restrict__ ids, int width, int vocab, int* status) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
     const int row = blockIdx.x;
     const int id = ids[row];
     float* dst = out + static_cast<size_t>(row) * width;
@@ -35,6 +37,8 @@ __global__ void embed_gather_kernel(float* __restrict__ out, const W* __restrict
 template <typename W>
 __global__ void embed_gather_vec8_kernel(float* __restrict__ out, const W* __restrict__ table,
                                          const int* __restrict__ ids, int width, int vocab, int* status) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
     const int row = blockIdx.x;
     const int id = ids[row];
     float4* dst = reinterpret_cast<float4*>(out + static_cast<size_t>(row) * width);
@@ -68,6 +72,8 @@ template <typename T, typename W>
 __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int slices, size_t slice_stride,
                                const W* __restrict__ weight, T* __restrict__ out,
                                const int* __restrict__ rows, int width, float eps, int write_back) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const size_t row = rows ? static_cast<size_t>(rows[r]) : static_cast<size_t>(r);
@@ -97,6 +103,8 @@ __global__ void __launch_bounds__(1024) rmsnorm_cached_kernel(float* __restrict_
                                                              const W* __restrict__ weight, T* __restrict__ out,
                                                              const int* __restrict__ rows, int width, float eps,
                                                              int write_back) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const size_t row = rows ? static_cast<size_t>(rows[r]) : static_cast<size_t>(r);
@@ -148,6 +156,8 @@ __global__ void __launch_bounds__(1024) rmsnorm_cached_kernel(float* __restrict_
 
 // h[row,:] += delta[row,:] for all rows (when no norm follows).
 __global__ void residual_add_kernel(float* __restrict__ h, const float* __restrict__ delta, size_t count) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < count;
          i += static_cast<size_t>(gridDim.x) * blockDim.x)
         h[i] += delta[i];
@@ -175,6 +185,8 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, int ld, const flo
                                           const int* __restrict__ block_table, int table_stride,
                                           int page_size, T* __restrict__ cache, int num_pages,
                                           int write_cache, int* status) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
     const int warps = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x;
@@ -266,6 +278,8 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, int ld, const flo
 // gate_up is [rows, 2*inter]: the gate in the first `inter` columns, up in the rest.
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inter) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
     const size_t total = static_cast<size_t>(rows) * inter;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -278,6 +292,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 
 template <typename T>
 __global__ void swiglu_vec8_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inter) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
     const int per_row = inter >> 3;
     const size_t total = static_cast<size_t>(rows) * per_row;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -296,6 +312,8 @@ __global__ void swiglu_vec8_kernel(const T* __restrict__ gate_up, T* __restrict_
 template <typename T>
 __global__ void swiglu_sliced_kernel(const float* __restrict__ partials, int slices, size_t slice_stride,
                                      T* __restrict__ out, int rows, int inter) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
     const size_t total = static_cast<size_t>(rows) * inter;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -321,13 +339,13 @@ MLR_API int mlr_embed_gather(float* out, const void* table, int w_bf16, const in
     const int threads = row_threads(width);
     const bool vec = width % 8 == 0 && reinterpret_cast<uintptr_t>(table) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
     if (vec && w_bf16)
-        embed_gather_vec8_kernel<<<rows, row_threads(width / 2), 0, stream>>>(out, static_cast<const __nv_bfloat16*>(table), ids, width, vocab, status);
+        mlr_launch((embed_gather_vec8_kernel<__nv_bfloat16>), dim3(rows), dim3(row_threads(width / 2)), 0, stream, out, static_cast<const __nv_bfloat16*>(table), ids, width, vocab, status);
     else if (vec)
-        embed_gather_vec8_kernel<<<rows, row_threads(width / 2), 0, stream>>>(out, static_cast<const float*>(table), ids, width, vocab, status);
+        mlr_launch((embed_gather_vec8_kernel<float>), dim3(rows), dim3(row_threads(width / 2)), 0, stream, out, static_cast<const float*>(table), ids, width, vocab, status);
     else if (w_bf16)
-        embed_gather_kernel<<<rows, threads, 0, stream>>>(out, static_cast<const __nv_bfloat16*>(table), ids, width, vocab, status);
+        mlr_launch((embed_gather_kernel<__nv_bfloat16>), dim3(rows), dim3(threads), 0, stream, out, static_cast<const __nv_bfloat16*>(table), ids, width, vocab, status);
     else
-        embed_gather_kernel<<<rows, threads, 0, stream>>>(out, static_cast<const float*>(table), ids, width, vocab, status);
+        mlr_launch((embed_gather_kernel<float>), dim3(rows), dim3(threads), 0, stream, out, static_cast<const float*>(table), ids, width, vocab, status);
     return mlr_launched("embed_gather");
 }
 
@@ -349,11 +367,11 @@ MLR_API int mlr_rmsnorm(float* h, const float* delta, int slices, long long slic
 #define MLR_LAUNCH(T, W)                                                                                   \
     do {                                                                                                   \
         if (cached)                                                                                        \
-            rmsnorm_cached_kernel<T, W><<<count, cached_threads, 0, stream>>>(                             \
+            mlr_launch((rmsnorm_cached_kernel<T, W>), dim3(count), dim3(cached_threads), 0, stream,                              \
                 h, delta, slices, static_cast<size_t>(slice_stride), static_cast<const W*>(weight),       \
                 static_cast<T*>(out), rows, width, eps, write_back);                                       \
         else                                                                                               \
-            rmsnorm_kernel<T, W><<<count, threads, 0, stream>>>(h, delta, slices, static_cast<size_t>(slice_stride), \
+            mlr_launch((rmsnorm_kernel<T, W>), dim3(count), dim3(threads), 0, stream, h, delta, slices, static_cast<size_t>(slice_stride), \
                                                                  static_cast<const W*>(weight),            \
                                                                  static_cast<T*>(out), rows, width, eps, write_back); \
     } while (0)
@@ -369,7 +387,7 @@ MLR_API int mlr_residual_add(float* h, const float* delta, long long count, cuda
     MLR_REQUIRE(count >= 0, "residual_add: negative count");
     if (count == 0) return 0;
     const int blocks = static_cast<int>(count / 1024 + 1 < 4096 ? count / 1024 + 1 : 4096);
-    residual_add_kernel<<<blocks, 256, 0, stream>>>(h, delta, static_cast<size_t>(count));
+    mlr_launch((residual_add_kernel), dim3(blocks), dim3(256), 0, stream, h, delta, static_cast<size_t>(count));
     return mlr_launched("residual_add");
 }
 
@@ -394,7 +412,7 @@ MLR_API int mlr_qk_norm_rope_cache(void* qkv, int act_bf16, int ld, const float*
     const int warps = 4;
     const dim3 grid(rows, (q_heads + 2 * kv_heads + warps - 1) / warps);
 #define MLR_LAUNCH(T, W)                                                                                       \
-    qk_norm_rope_cache_kernel<T, W><<<grid, warps * 32, 0, stream>>>(                                          \
+    mlr_launch((qk_norm_rope_cache_kernel<T, W>), dim3(grid), dim3(warps * 32), 0, stream,                                           \
         static_cast<T*>(qkv), ld, partials, slices, static_cast<size_t>(slice_stride), ld_partial, rows, q_heads,  \
         kv_heads, head_dim, static_cast<const W*>(q_weight),                                                   \
         static_cast<const W*>(k_weight), eps, cos_sin, table_positions, positions, segment_of_row, block_table, \
@@ -416,16 +434,16 @@ MLR_API int mlr_swiglu(const void* gate_up, void* out, int act_bf16, int rows, i
         const size_t work = total / 8;
         const int vblocks = static_cast<int>(work / 256 + 1 < 148 * 16 ? work / 256 + 1 : 148 * 16);
         if (act_bf16)
-            swiglu_vec8_kernel<<<vblocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, inter);
+            mlr_launch((swiglu_vec8_kernel<__nv_bfloat16>), dim3(vblocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, inter);
         else
-            swiglu_vec8_kernel<<<vblocks, 256, 0, stream>>>(static_cast<const float*>(gate_up), static_cast<float*>(out), rows, inter);
+            mlr_launch((swiglu_vec8_kernel<float>), dim3(vblocks), dim3(256), 0, stream, static_cast<const float*>(gate_up), static_cast<float*>(out), rows, inter);
         return mlr_launched("swiglu");
     }
     const int blocks = static_cast<int>(total / 1024 + 1 < 148 * 16 ? total / 1024 + 1 : 148 * 16);
     if (act_bf16)
-        swiglu_kernel<<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, inter);
+        mlr_launch((swiglu_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, inter);
     else
-        swiglu_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float*>(gate_up), static_cast<float*>(out), rows, inter);
+        mlr_launch((swiglu_kernel<float>), dim3(blocks), dim3(256), 0, stream, static_cast<const float*>(gate_up), static_cast<float*>(out), rows, inter);
     return mlr_launched("swiglu");
 }
 
@@ -438,10 +456,10 @@ MLR_API int mlr_swiglu_sliced(const float* partials, int slices, long long slice
     const size_t total = static_cast<size_t>(rows) * inter;
     const int blocks = static_cast<int>(total / 256 + 1 < 148 * 16 ? total / 256 + 1 : 148 * 16);
     if (act_bf16)
-        swiglu_sliced_kernel<<<blocks, 256, 0, stream>>>(partials, slices, static_cast<size_t>(slice_stride),
+        mlr_launch((swiglu_sliced_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream, partials, slices, static_cast<size_t>(slice_stride),
                                                          static_cast<__nv_bfloat16*>(out), rows, inter);
     else
-        swiglu_sliced_kernel<<<blocks, 256, 0, stream>>>(partials, slices, static_cast<size_t>(slice_stride),
+        mlr_launch((swiglu_sliced_kernel<float>), dim3(blocks), dim3(256), 0, stream, partials, slices, static_cast<size_t>(slice_stride),
                                                          static_cast<float*>(out), rows, inter);
     return mlr_launched("swiglu_sliced");
 }

@@ -118,7 +118,8 @@ __global__ void __launch_bounds__(kThreads) gemm_tcgen05_kernel(const __grid_con
                                                                 const __grid_constant__ CUtensorMap map_q,
                                                                 void* __restrict__ out_base, long long ldo, int P, int Q, int K,
                                                                 int out_f32, int swapped, int k_splits,
-                                                                long long split_stride, int* status) {
+                                                                long long split_stride, int static_operand, int* status) {
+    mlr_grid_dependents_may_start();
     using S = Shape<BN>;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long barriers[2 * S::kStages + 4];
@@ -170,6 +171,22 @@ __global__ void __launch_bounds__(kThreads) gemm_tcgen05_kernel(const __grid_con
     if (warp == 0) {
         // ---------------- loads
         if (lane == 0) {
+            // `static_operand` (1 = Pm, 2 = Qm) names an operand that no kernel writes (the
+            // weights).  Its tiles for the first stages are fetched before the wait for the
+            // preceding kernels, so the pipeline is full when the other operand may be read.
+            int prefetched = 0;
+            if (static_operand) {
+                for (int unit = blockIdx.x; unit < tiles && prefetched < S::kStages; unit += gridDim.x) {
+                    const int tile = unit % (tiles_p * tiles_q), split = split_of(unit);
+                    const int p0 = (tile % tiles_p) * kTileP, q0 = (tile / tiles_p) * BN;
+                    for (int kb = first_block(split); kb < first_block(split + 1) && prefetched < S::kStages; ++kb, ++prefetched) {
+                        mbar_expect_tx(full_bar(prefetched), S::kStageBytes);
+                        if (static_operand == 1) tma_load_2d(tile_p(prefetched), &map_p, kb * kTileK, p0, full_bar(prefetched));
+                        else tma_load_2d(tile_q(prefetched), &map_q, kb * kTileK, q0, full_bar(prefetched));
+                    }
+                }
+            }
+            mlr_grid_wait();
             bool ok = true;
             int it = 0;
             for (int unit = blockIdx.x; unit < tiles && ok; unit += gridDim.x) {
@@ -177,11 +194,12 @@ __global__ void __launch_bounds__(kThreads) gemm_tcgen05_kernel(const __grid_con
                 const int p0 = (tile % tiles_p) * kTileP, q0 = (tile / tiles_p) * BN;
                 for (int kb = first_block(split); kb < first_block(split + 1); ++kb, ++it) {
                     const int stage = it % S::kStages;
-                    if (it >= S::kStages) ok = mbar_wait(empty_bar(stage), ((it / S::kStages) - 1) & 1);
+                    const bool fresh = it >= prefetched;       // else the stage is announced and half loaded already
+                    if (fresh && it >= S::kStages) ok = mbar_wait(empty_bar(stage), ((it / S::kStages) - 1) & 1);
                     if (!ok) break;
-                    mbar_expect_tx(full_bar(stage), S::kStageBytes);
-                    tma_load_2d(tile_p(stage), &map_p, kb * kTileK, p0, full_bar(stage));
-                    tma_load_2d(tile_q(stage), &map_q, kb * kTileK, q0, full_bar(stage));
+                    if (fresh) mbar_expect_tx(full_bar(stage), S::kStageBytes);
+                    if (fresh || static_operand != 1) tma_load_2d(tile_p(stage), &map_p, kb * kTileK, p0, full_bar(stage));
+                    if (fresh || static_operand != 2) tma_load_2d(tile_q(stage), &map_q, kb * kTileK, q0, full_bar(stage));
                 }
             }
             if (!ok) fault = 2;
@@ -189,6 +207,7 @@ __global__ void __launch_bounds__(kThreads) gemm_tcgen05_kernel(const __grid_con
     } else if (warp == 1) {
         // ---------------- tensor-core instructions
         if (lane == 0) {
+            mlr_grid_wait();
             constexpr uint32_t idesc = instruction_descriptor(BN);
             bool ok = true;
             int it = 0, local = 0;
@@ -218,6 +237,7 @@ __global__ void __launch_bounds__(kThreads) gemm_tcgen05_kernel(const __grid_con
     } else {
         // ---------------- stores: warp w reads lanes 32 (w % 4) .. of the accumulator
         const int quarter = warp & 3;
+        mlr_grid_wait();
         bool ok = true;
         int local = 0;
         for (int unit = blockIdx.x; unit < tiles; unit += gridDim.x, ++local) {
@@ -330,7 +350,7 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
 
 template <int BN>
 int launch(const CUtensorMap& map_p, const CUtensorMap& map_q, void* out, long long ldo, int P, int Q, int K, int out_f32,
-           int swapped, int k_splits, long long split_stride, int* status, int sms, cudaStream_t stream) {
+           int swapped, int k_splits, long long split_stride, int static_operand, int* status, int sms, cudaStream_t stream) {
     using S = Shape<BN>;
     const size_t bytes = static_cast<size_t>(S::kStages) * S::kStageBytes + 1024;
     static thread_local bool allowed = false;
@@ -342,8 +362,8 @@ int launch(const CUtensorMap& map_p, const CUtensorMap& map_q, void* out, long l
     }
     const int tiles = ((P + kTileP - 1) / kTileP) * ((Q + BN - 1) / BN) * k_splits;
     const int grid = tiles < sms ? tiles : sms;
-    gemm_tcgen05_kernel<BN><<<grid, kThreads, bytes, stream>>>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, k_splits,
-                                                               split_stride, status);
+    mlr_launch((gemm_tcgen05_kernel<BN>), dim3(grid), dim3(kThreads), bytes, stream, map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, k_splits,
+                                                               split_stride, static_operand, status);
     return mlr_launched("gemm_bf16_tcgen05");
 }
 
@@ -354,9 +374,12 @@ int launch(const CUtensorMap& map_p, const CUtensorMap& map_q, void* out, long l
 // Qm is [Q, K] with row stride ldq (elements).  tile_q: 16, 32, 64, 128 or 256 columns of Qm
 // per tile (0 lets the function choose).  k_splits > 1 cuts K into that many ranges; range s
 // writes its sum to the float32 slice out + s * split_stride, and the reader adds the slices.
+// static_operand: 1 if no kernel in flight writes Pm (it holds weights), 2 the same for Qm, 0
+// neither; the kernel fetches that operand before it waits for the kernels before it.
 MLR_API int mlr_gemm_bf16_tcgen05(const void* Pm, long long ldp, int P, const void* Qm, long long ldq, int Q, int K, void* out,
                                   long long ldo, int out_f32, int swapped, int tile_q, int k_splits, long long split_stride,
-                                  int* status, cudaStream_t stream) {
+                                  int static_operand, int* status, cudaStream_t stream) {
+    MLR_REQUIRE(static_operand >= 0 && static_operand <= 2, "gemm_bf16_tcgen05: static_operand must be 0, 1 or 2");
     MLR_REQUIRE(k_splits >= 1 && k_splits <= (K + kTileK - 1) / kTileK, "gemm_bf16_tcgen05: %d splits of K = %d", k_splits, K);
     MLR_REQUIRE(k_splits == 1 || (out_f32 && split_stride >= 1), "gemm_bf16_tcgen05: split results are float32 slices");
     MLR_REQUIRE(P >= 1 && Q >= 1 && K >= 8, "gemm_bf16_tcgen05: bad sizes P=%d Q=%d K=%d", P, Q, K);
@@ -376,10 +399,10 @@ MLR_API int mlr_gemm_bf16_tcgen05(const void* Pm, long long ldp, int P, const vo
     if (int e = make_map(&map_p, Pm, P, K, ldp, kTileP)) return e;
     if (int e = make_map(&map_q, Qm, Q, K, ldq, tile_q)) return e;
     switch (tile_q) {
-        case 16: return launch<16>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, k_splits, split_stride, status, sms, stream);
-        case 32: return launch<32>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, k_splits, split_stride, status, sms, stream);
-        case 64: return launch<64>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, k_splits, split_stride, status, sms, stream);
-        case 128: return launch<128>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, k_splits, split_stride, status, sms, stream);
-        default: return launch<256>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, k_splits, split_stride, status, sms, stream);
+        case 16: return launch<16>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, k_splits, split_stride, static_operand, status, sms, stream);
+        case 32: return launch<32>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, k_splits, split_stride, static_operand, status, sms, stream);
+        case 64: return launch<64>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, k_splits, split_stride, static_operand, status, sms, stream);
+        case 128: return launch<128>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, k_splits, split_stride, static_operand, status, sms, stream);
+        default: return launch<256>(map_p, map_q, out, ldo, P, Q, K, out_f32, swapped, k_splits, split_stride, static_operand, status, sms, stream);
     }
 }

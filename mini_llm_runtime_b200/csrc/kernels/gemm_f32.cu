@@ -17,6 +17,8 @@ template <bool kVector>
 __global__ void __launch_bounds__(256) gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W,
                                                        float* __restrict__ C, int M, int N, int K, int lda,
                                                        int ldw, int ldc) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -90,8 +92,8 @@ MLR_API int mlr_gemm_f32(const float* A, const float* W, float* C, int M, int N,
     const bool vector = lda % 4 == 0 && ldw % 4 == 0 && reinterpret_cast<uintptr_t>(A) % 16 == 0 &&
                         reinterpret_cast<uintptr_t>(W) % 16 == 0;
     if (vector)
-        gemm_f32_kernel<true><<<grid, 256, 0, stream>>>(A, W, C, M, N, K, lda, ldw, ldc);
+        mlr_launch((gemm_f32_kernel<true>), dim3(grid), dim3(256), 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
     else
-        gemm_f32_kernel<false><<<grid, 256, 0, stream>>>(A, W, C, M, N, K, lda, ldw, ldc);
+        mlr_launch((gemm_f32_kernel<false>), dim3(grid), dim3(256), 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
     return mlr_launched("gemm_f32");
 }

@@ -100,6 +100,8 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const __nv_bfloat16* __r
                                                         const __nv_bfloat16* __restrict__ W, int ldw, int n_rows,
                                                         int K, void* __restrict__ out, int ldo, int epilogue,
                                                         int tiles, int* status) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) unsigned long long barriers[2 * kStages];
     __shared__ float reduce[2][4][16][8 * NT];
@@ -264,7 +266,7 @@ MLR_API int mlr_gemv_bf16(const void* x, int ldx, int M, const void* W, int ldw,
                                                   cudaGetErrorString(e));                                          \
             allowed[NT - 1] = true;                                                                                \
         }                                                                                                          \
-        gemv_kernel<NT><<<grid, kThreads, bytes, stream>>>(static_cast<const __nv_bfloat16*>(x), ldx, M,          \
+        mlr_launch((gemv_kernel<NT>), dim3(grid), dim3(kThreads), bytes, stream, static_cast<const __nv_bfloat16*>(x), ldx, M,          \
                                                            static_cast<const __nv_bfloat16*>(W), ldw, n_rows, K,  \
                                                            out, ldo, epilogue, tiles, status);                     \
     } while (0)

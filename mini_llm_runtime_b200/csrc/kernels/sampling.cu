@@ -29,6 +29,8 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restric
                                                           const float* __restrict__ temperature,
                                                           const double* __restrict__ uniform,
                                                           int* __restrict__ out, int* status) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
     __shared__ Best best_of_warp[32];
     __shared__ double sums[kThreads];
     __shared__ int nonfinite;
@@ -137,6 +139,6 @@ MLR_API int mlr_sample(const float* logits, int ld, int rows, int vocab, const f
     MLR_REQUIRE(rows >= 0 && vocab > 0 && ld >= vocab, "sample: bad sizes rows=%d vocab=%d ld=%d", rows, vocab, ld);
     MLR_REQUIRE(temperature == nullptr || uniform != nullptr, "sample: temperatures without uniform numbers");
     if (rows == 0) return 0;
-    sample_kernel<<<rows, kThreads, 0, stream>>>(logits, ld, vocab, temperature, uniform, out, status);
+    mlr_launch((sample_kernel), dim3(rows), dim3(kThreads), 0, stream, logits, ld, vocab, temperature, uniform, out, status);
     return mlr_launched("sample");
 }

@@ -233,7 +233,10 @@ def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, statu
     (the product is then a single pass over the weights); otherwise x takes that side.
 
     `out` may also be float32 [S, M, N]: K is then cut into S ranges and slice s holds the
-    sum over range s (more thread blocks share a small matrix); the reader adds the slices."""
+    sum over range s (more thread blocks share a small matrix); the reader adds the slices.
+
+    `w` must hold weights: nothing that runs before this call on the stream may still be
+    writing it, because the kernel starts to fetch it before the kernels before it are done."""
     on_gpu(x, w, out, status)
     if not gemm_tcgen05_applies(x, w):
         raise KernelError("gemm_bf16_tcgen05: operands must be bfloat16, K-contiguous, 16-byte aligned, K % 8 == 0")
@@ -252,10 +255,10 @@ def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, statu
     ldo = out.stride(-2)
     if M <= 64:
         call("gemm_bf16_tcgen05", "mlr_gemm_bf16_tcgen05", ptr(w), w.stride(0), N, ptr(x), x.stride(0), M, K, ptr(out),
-             ldo, f32, 1, tile_q, splits, split_stride, ptr(status), stream())
+             ldo, f32, 1, tile_q, splits, split_stride, 1, ptr(status), stream())
     else:
         call("gemm_bf16_tcgen05", "mlr_gemm_bf16_tcgen05", ptr(x), x.stride(0), M, ptr(w), w.stride(0), N, K, ptr(out),
-             ldo, f32, 0, tile_q, splits, split_stride, ptr(status), stream())
+             ldo, f32, 0, tile_q, splits, split_stride, 2, ptr(status), stream())
 
 
 def k_splits_for(rows: int, K: int, sms: int = 148) -> int:

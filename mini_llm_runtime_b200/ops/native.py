@@ -54,7 +54,7 @@ _SIGNATURES = {
     },
     "gemm_bf16_tcgen05": {
         "mlr_gemm_bf16_tcgen05": [c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong,
-                                  c_int, c_int, c_int, c_int, c_longlong, c_void_p, c_void_p],
+                                  c_int, c_int, c_int, c_int, c_longlong, c_int, c_void_p, c_void_p],
     },
     "sampling": {
         "mlr_sample": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
