@@ -3,20 +3,23 @@
 //
 //   decode_splitkv   for requests that bring few rows (tokens x query heads per kv head
 //                    <= 16: a decoded token, or a portion of two or three tokens).  One
-//                    block per (request, kv head, split of the keys); its four warps walk
-//                    disjoint keys of each 64-key tile with their own running softmax and
-//                    are merged at the end; splits are merged by `combine`.  The bytes of
-//                    the cache are what it is bound by.
+//                    block per (request, kv head, split of the keys); its four compute warps
+//                    walk disjoint keys of each 64-key tile with their own running softmax
+//                    and are merged at the end; splits are merged by `combine`.  The bytes
+//                    of the cache are what it is bound by.
 //   prefill          for prompt portions.  One block per (64 query rows, query head); its
-//                    four warps own 16 rows each and walk the keys up to the diagonal
-//                    (flash attention: running maximum and sum, no score matrix).
+//                    four compute warps own 16 rows each and walk the keys up to the
+//                    diagonal (flash attention: running maximum and sum, no score matrix).
 //
-// Both read K and V tiles of 64 keys through the block table with 16-byte cp.async into
-// XOR-swizzled shared memory (two or three stages), take fragments with ldmatrix, and
-// multiply with mma.sync m16n8k16 (bf16 in, float32 accumulate).  Scores, maxima, sums and
-// the output accumulators are float32.  Keys outside a row's [lo, position] are filled
-// with zeros in shared memory and masked in the scores, so unused or stale cache memory
-// cannot reach a result.
+// In both, a fifth warp streams K and V tiles of 64 keys through the block table into a ring
+// of three shared-memory stages with bulk copies (cp.async.bulk) whose completion an
+// mbarrier counts; the compute warps take fragments with ldmatrix and multiply with
+// mma.sync m16n8k16 (bf16 in, float32 accumulate).  For head sizes 64, 128 and 256 the cache
+// stores rows pre-swizzled (common.cuh), so a whole page block is one copy and lands
+// bank-conflict-free; other head sizes copy row by row into padded tiles.  Scores, maxima,
+// sums and the output accumulators are float32.  Keys outside a row's [lo, position] are
+// masked in the scores and their V rows are zero or finite, so unused or stale cache memory
+// cannot reach a result.  Every wait on a barrier is bounded.
 //
 // Semantics are those of src/minillm/runtime.cpp:283-310 (scores scaled by `scale`,
 // softmax over t in [lo, position], weighted sum of V), with lo = 0 or
@@ -31,21 +34,12 @@ namespace {
 
 constexpr int kTileKeys = 64;
 constexpr int kThreads = 128;
-constexpr int kDecodeStages = 3;   // 3 x 32 KB at head size 128: two blocks per SM
-constexpr int kPrefillStages = 2;  // two stages leave room for three blocks per SM
+constexpr int kDecodeStages = 3;   // stages of a block's tile ring; 3 x 32 KB at head size 128: two blocks per SM
 constexpr float kLog2e = 1.4426950408889634f;
 
 // ---------------------------------------------------------------- PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
 }
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -128,70 +122,10 @@ __device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_
                  : "memory");
 }
 
-struct CacheView {
-    const __nv_bfloat16* base;   // [page][2][kv_heads][page_size][head_dim]
-    const int* table;            // this request's block table row
-    int num_pages, page_size, page_shift, kv_heads, head_dim, kv_head;   // page_shift: log2(page_size) or -1
-};
-
 __host__ __device__ inline int log2_or_minus1(int v) {
     int s = 0;
     while ((1 << s) < v) ++s;
     return (1 << s) == v ? s : -1;
-}
-
-// Copying a 64-key tile: warp w copies keys 16w .. 16w+15.  Consecutive lanes copy
-// consecutive 16-byte chunks of a key's row, so every 32-byte sector is asked for once.
-// Each lane looks up the page of key 16w + (lane & 15) one iteration ahead
-// (lookup_page); the page of the row a lane copies comes from that lane by shuffle.
-__device__ __forceinline__ int lookup_page(const CacheView& c, int tile_start, int first_key, int last_key) {
-    const int key = tile_start + ((threadIdx.x >> 5) << 4) + (threadIdx.x & 15);
-    if (key < first_key || key > last_key) return -1;
-    const int block = c.page_shift >= 0 ? key >> c.page_shift : key / c.page_size;
-    return __ldg(c.table + block);
-}
-
-// Loads keys [tile_start, tile_start + 64) of K and V into one stage.  Keys outside
-// [first_key, last_key] are zero-filled.  Called by all 128 threads of the block.
-// `page` is the thread's lookup_page() result for this tile.
-template <int DMAX>
-__device__ __forceinline__ void load_tile(const CacheView& c, int tile_start, int first_key, int last_key, int page,
-                                          uint32_t k_smem, uint32_t v_smem, int* bad_page) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int chunks = c.head_dim >> 3;                 // 16-byte chunks in a row
-    const size_t head_elems = static_cast<size_t>(c.page_size) * c.head_dim;
-    const size_t value_shift = head_elems * c.kv_heads;
-    const int total = 16 * chunks;                      // chunks this warp copies per matrix
-    const bool swizzled = mlr_cache_swizzled(true, c.head_dim);
-#pragma unroll
-    for (int j = 0; j < DMAX / 16; ++j) {
-        const int idx = j * 32 + lane;
-        int local = idx / chunks;                       // key within the warp's 16 (chunks is 2..32)
-        const int chunk = idx - local * chunks;
-        const bool active = idx < total;
-        local = active ? local : 0;
-        const int row_page = __shfl_sync(0xffffffffu, page, local);
-        if (!active) continue;
-        const int row = warp * 16 + local, key = tile_start + row;
-        const __nv_bfloat16* src = c.base;
-        int bytes = 0;
-        if (key >= first_key && key <= last_key) {
-            if (row_page >= 0 && row_page < c.num_pages) {
-                const int in_page = c.page_shift >= 0 ? key & (c.page_size - 1) : key % c.page_size;
-                src = c.base + (static_cast<size_t>(row_page) * 2 * c.kv_heads + c.kv_head) * head_elems +
-                      static_cast<size_t>(in_page) * c.head_dim + chunk * 8;
-                bytes = 16;
-            } else {
-                *bad_page = 1;
-            }
-        }
-        // A swizzled cache already stores chunk c at c ^ (position & 7), which is where the
-        // tile wants it (row & 7 == position & 7): copy chunk for chunk.  A plain cache is
-        // permuted on the way in.
-        const uint32_t off = swizzled ? row * Tile<DMAX>::kPitch + (chunk << 4) : Tile<DMAX>::offset(row, chunk);
-        cp_async_16(k_smem + off, src, bytes);
-        cp_async_16(v_smem + off, bytes ? src + value_shift : src, bytes);
-    }
 }
 
 // One warp: S[16 rows x 16*NB keys] += Q[16 x D] K^T for keys [key0, key0 + 16*NB) of a tile.
@@ -264,9 +198,11 @@ struct RowState {
     float l[2] = {0.0f, 0.0f};
 };
 
-// Scales and masks the scores of `NT` n8-tiles (keys key_base + 8*nt + 2*t + {0,1}),
-// updates the running maxima, turns scores into probabilities, rescales O, and packs P
-// into A fragments (one per 16 keys).
+// One step of the running softmax over `NT` n8-tiles of raw scores (keys key_base + 8*nt +
+// 2*t + {0,1}): masks, updates the running maxima (kept in log2 units, i.e. multiplied by
+// scale * log2 e), turns scores into probabilities exp2(s * scale_log2 - m), and packs them
+// into A fragments (one per 16 keys).  The accumulators are rescaled only when some row of
+// the warp saw a new maximum, which after the first tiles is rare.
 template <int DMAX, int NT>
 __device__ __forceinline__ void softmax_step(float (&s)[NT][4], RowState& st, float (&o)[DMAX / 8][4],
                                              uint32_t (&p)[NT / 2][4], int key_base, const int (&lo)[2],
@@ -278,42 +214,48 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], RowState& st, fl
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int r = j >> 1;
-            float v = s[nt][j] * scale_log2;
             if (need_mask) {
                 const int key = key_base + nt * 8 + 2 * t + (j & 1);
-                if (key < lo[r] || key > hi[r]) v = -INFINITY;
+                if (key < lo[r] || key > hi[r]) s[nt][j] = -INFINITY;
             }
-            s[nt][j] = v;
-            tile_max[r] = fmaxf(tile_max[r], v);
+            tile_max[r] = fmaxf(tile_max[r], s[nt][j]);
         }
     }
-    float alpha[2], m_use[2];
+    float m_use[2], m_new[2];
+    bool changed = false;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
         tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
-        const float m_new = fmaxf(st.m[r], tile_max[r]);
-        m_use[r] = m_new == -INFINITY ? 0.0f : m_new;
-        alpha[r] = exp2f(st.m[r] - m_use[r]);
-        st.m[r] = m_new;
-        st.l[r] *= alpha[r];
+        m_new[r] = fmaxf(st.m[r], tile_max[r] * scale_log2);      // scale_log2 > 0
+        changed |= m_new[r] > st.m[r];
+        m_use[r] = m_new[r] == -INFINITY ? 0.0f : m_new[r];
+    }
+    if (__any_sync(0xffffffffu, changed)) {
+        float alpha[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            alpha[r] = exp2f(st.m[r] - m_use[r]);      // 1 for a row whose maximum stayed, 0 for a row's first keys
+            st.m[r] = m_new[r];
+            st.l[r] *= alpha[r];
+        }
+#pragma unroll
+        for (int dn = 0; dn < DMAX / 8; ++dn) {
+            o[dn][0] *= alpha[0];
+            o[dn][1] *= alpha[0];
+            o[dn][2] *= alpha[1];
+            o[dn][3] *= alpha[1];
+        }
     }
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int r = j >> 1;
-            const float e = exp2f(s[nt][j] - m_use[r]);
+            const float e = exp2f(fmaf(s[nt][j], scale_log2, -m_use[r]));
             s[nt][j] = e;
             st.l[r] += e;
         }
-    }
-#pragma unroll
-    for (int dn = 0; dn < DMAX / 8; ++dn) {
-        o[dn][0] *= alpha[0];
-        o[dn][1] *= alpha[0];
-        o[dn][2] *= alpha[1];
-        o[dn][3] *= alpha[1];
     }
 #pragma unroll
     for (int kk = 0; kk < NT / 2; ++kk) {
@@ -335,6 +277,120 @@ __device__ __forceinline__ SplitPlan plan_splits(int start, int count, int windo
     p.base = (p.first_key / kTileKeys) * kTileKeys;
     p.splits = (p.last_key + 1 - p.base + chunk - 1) / chunk;
     return p;
+}
+
+// ---------------------------------------------------------------- the copy warp
+// Fills the stages of a block with the 64-key tiles of keys [key_begin, key_end) of one
+// request and kv head, tile after tile, for the compute warps of the same block.  Per tile:
+// wait until the stage is free, announce the tile's bytes on the stage's "full" barrier,
+// issue the bulk copies.  BLOCKS (swizzled cache, head size == DMAX): one copy of K and one
+// of V per page block the tile touches, byte for byte into an unpadded tile; rows of V
+// outside [first_valid, key_end) are zeroed (their scores are masked, but 0 * garbage must
+// stay 0).  Otherwise: one copy per key row into a padded tile; a key outside the range
+// copies the nearest key inside it.  Returns false if a wait ran out.
+struct StageRing {
+    uint32_t smem_base, bar_base;
+    unsigned char* smem;
+    int tile_bytes;
+    __device__ __forceinline__ uint32_t k_stage(int s) const { return smem_base + s * 2 * tile_bytes; }
+    __device__ __forceinline__ uint32_t v_stage(int s) const { return smem_base + s * 2 * tile_bytes + tile_bytes; }
+    __device__ __forceinline__ uint32_t full_bar(int s) const { return bar_base + s * 8; }
+    __device__ __forceinline__ uint32_t empty_bar(int s) const { return bar_base + (kDecodeStages + s) * 8; }
+};
+
+template <int DMAX, bool BLOCKS>
+__device__ __forceinline__ bool copy_warp(const StageRing& ring, const __nv_bfloat16* __restrict__ cache, const int* __restrict__ table,
+                                          int num_pages, int page_size, int kv_heads, int head_dim, int kv_head, int key_begin,
+                                          int key_end, int first_valid, int tiles, int* fault) {
+    using L = typename std::conditional<BLOCKS, Tile<DMAX>, PaddedTile<DMAX>>::type;
+    const int lane = threadIdx.x & 31;
+    const int page_shift = log2_or_minus1(page_size);
+    const size_t head_elems = static_cast<size_t>(page_size) * head_dim;
+    const size_t value_shift = head_elems * kv_heads;
+    const uint32_t row_bytes = head_dim * 2;
+    bool ok = true;
+    // Page of the block this lane copies in a tile (looked up one tile ahead, so that the
+    // table read is off the critical path): block = first block of the tile + lane.
+    auto tile_page = [&](int it_) {
+        const int from_ = max(key_begin + it_ * kTileKeys, first_valid);
+        const int block_ = (page_shift >= 0 ? from_ >> page_shift : from_ / page_size) + lane;
+        const int last_ = min(key_begin + (it_ + 1) * kTileKeys, key_end) - 1;
+        const int last_block_ = page_shift >= 0 ? last_ >> page_shift : last_ / page_size;
+        return (it_ < tiles && block_ <= last_block_) ? __ldg(table + block_) : -1;
+    };
+    int ahead = BLOCKS ? tile_page(0) : -1;
+    for (int it = 0; it < tiles && ok; ++it) {
+        const int stage = it % kDecodeStages;
+        if (it >= kDecodeStages) ok = mbar_wait(ring.empty_bar(stage), ((it / kDecodeStages) - 1) & 1);
+        if (!ok) break;
+        const int tile_start = key_begin + it * kTileKeys;
+        const int my_page = ahead;
+        if (BLOCKS) ahead = tile_page(it + 1);
+        if (BLOCKS) {
+            const int from = max(tile_start, first_valid), to = min(tile_start + kTileKeys, key_end);
+            if (to - from < kTileKeys) {
+                const int quads = (head_dim * 2) >> 4;
+                for (int i = lane; i < kTileKeys * quads; i += 32) {
+                    const int row = i / quads;
+                    if (tile_start + row < from || tile_start + row >= to)
+                        *reinterpret_cast<uint4*>(ring.smem + (ring.v_stage(stage) - ring.smem_base) + row * L::kPitch +
+                                                  (i - row * quads) * 16) = make_uint4(0u, 0u, 0u, 0u);
+                }
+                // These plain stores and the bulk copies of later tiles touch the same bytes.
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            }
+            __syncwarp();
+            if (lane == 0) mbar_expect_tx(ring.full_bar(stage), row_bytes * 2 * (to - from));
+            __syncwarp();
+            const int first_block = page_shift >= 0 ? from >> page_shift : from / page_size;
+            const int last_block = page_shift >= 0 ? (to - 1) >> page_shift : (to - 1) / page_size;
+            for (int block = first_block + lane; block <= last_block; block += 32) {
+                const int block_start = block * page_size;
+                const int lo_key = max(block_start, from), hi_key = min(block_start + page_size, to);
+                int page = block == first_block + lane ? my_page : __ldg(table + block);
+                if (page < 0 || page >= num_pages) {
+                    *fault = 1;
+                    page = 0;
+                }
+                const __nv_bfloat16* src = cache + (static_cast<size_t>(page) * 2 * kv_heads + kv_head) * head_elems +
+                                           static_cast<size_t>(lo_key - block_start) * head_dim;
+                const uint32_t bytes = row_bytes * (hi_key - lo_key);
+                const uint32_t dst = (lo_key - tile_start) * L::kPitch;
+                bulk_copy(ring.k_stage(stage) + dst, src, bytes, ring.full_bar(stage));
+                bulk_copy(ring.v_stage(stage) + dst, src + value_shift, bytes, ring.full_bar(stage));
+            }
+        } else {
+            if (lane == 0) mbar_expect_tx(ring.full_bar(stage), row_bytes * 2 * kTileKeys);
+            __syncwarp();
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int row = lane + 32 * half;
+                const int key = min(max(tile_start + row, first_valid), key_end - 1);
+                const int block = page_shift >= 0 ? key >> page_shift : key / page_size;
+                const int in_page = page_shift >= 0 ? key & (page_size - 1) : key - block * page_size;
+                int page = __ldg(table + block);
+                if (page < 0 || page >= num_pages) {
+                    *fault = 1;
+                    page = 0;      // still copy something so that the tile's byte count is met
+                }
+                const __nv_bfloat16* src = cache + (static_cast<size_t>(page) * 2 * kv_heads + kv_head) * head_elems +
+                                           static_cast<size_t>(in_page) * head_dim;
+                bulk_copy(ring.k_stage(stage) + row * L::kPitch, src, row_bytes, ring.full_bar(stage));
+                bulk_copy(ring.v_stage(stage) + row * L::kPitch, src + value_shift, row_bytes, ring.full_bar(stage));
+            }
+        }
+    }
+    return ok;
+}
+
+// Barriers of a StageRing; called by one thread before the block's first __syncthreads().
+__device__ __forceinline__ void init_ring(const StageRing& ring, int consumers) {
+    for (int s = 0; s < kDecodeStages; ++s) {
+        mbar_init(ring.full_bar(s), 1);
+        mbar_init(ring.empty_bar(s), consumers);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
 }
 
 // ---------------------------------------------------------------- decode: split-KV
@@ -378,27 +434,21 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
     if (split >= plan.splits) return;
     const int group = q_heads / kv_heads;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int dim_steps = head_dim >> 4;
+    const int dim_steps = BLOCKS ? DMAX / 16 : head_dim >> 4;       // a constant when the head size is the template's
 
     const int key_begin = plan.base + split * chunk;
     const int key_end = min(key_begin + chunk, plan.last_key + 1);      // exclusive
     const int first_valid = max(key_begin, plan.first_key);
     const int tiles = (key_end - key_begin + kTileKeys - 1) / kTileKeys;
 
-    const uint32_t smem_base = smem_u32(smem);
-    const uint32_t bar_base = smem_u32(barriers);
-    auto k_stage = [&](int s) { return smem_base + s * 2 * L::kBytes; };
-    auto v_stage = [&](int s) { return smem_base + s * 2 * L::kBytes + L::kBytes; };
-    auto full_bar = [&](int s) { return bar_base + s * 8; };
-    auto empty_bar = [&](int s) { return bar_base + (kDecodeStages + s) * 8; };
+    const StageRing ring{smem_u32(smem), smem_u32(barriers), smem, L::kBytes};
+    auto k_stage = [&](int s) { return ring.k_stage(s); };
+    auto v_stage = [&](int s) { return ring.v_stage(s); };
+    auto full_bar = [&](int s) { return ring.full_bar(s); };
+    auto empty_bar = [&](int s) { return ring.empty_bar(s); };
     if (threadIdx.x == 0) {
         fault = 0;
-        for (int s = 0; s < kDecodeStages; ++s) {
-            mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), 4);
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        init_ring(ring, 4);
     }
     __syncthreads();
 
@@ -408,89 +458,9 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
     RowState st;
 
     if (warp == 4) {
-        // ---------------- the copy warp
-        const int* table = block_table + static_cast<size_t>(segment) * table_stride;
-        const int page_shift = log2_or_minus1(page_size);
-        const size_t head_elems = static_cast<size_t>(page_size) * head_dim;
-        const size_t value_shift = head_elems * kv_heads;
-        const uint32_t row_bytes = head_dim * 2;
-        bool ok = true;
-        // Page of the block this lane copies in a tile (looked up one tile ahead, so that
-        // the table read is off the critical path): block = first block of the tile + lane.
-        auto tile_page = [&](int it_) {
-            const int from_ = max(key_begin + it_ * kTileKeys, first_valid);
-            const int block_ = (page_shift >= 0 ? from_ >> page_shift : from_ / page_size) + lane;
-            const int last_ = min(key_begin + (it_ + 1) * kTileKeys, key_end) - 1;
-            const int last_block_ = page_shift >= 0 ? last_ >> page_shift : last_ / page_size;
-            return (it_ < tiles && block_ <= last_block_) ? __ldg(table + block_) : -1;
-        };
-        int ahead = BLOCKS ? tile_page(0) : -1;
-        for (int it = 0; it < tiles && ok; ++it) {
-            const int stage = it % kDecodeStages;
-            if (it >= kDecodeStages) ok = mbar_wait(empty_bar(stage), ((it / kDecodeStages) - 1) & 1);
-            if (!ok) break;
-            const int tile_start = key_begin + it * kTileKeys;
-            const int my_page = ahead;
-            if (BLOCKS) ahead = tile_page(it + 1);
-            if (BLOCKS) {
-                // Keys of this tile that exist: [from, to).  Rows of V outside them are zeroed
-                // (their scores are masked, but 0 * garbage must stay 0); K may hold anything.
-                const int from = max(tile_start, first_valid), to = min(tile_start + kTileKeys, key_end);
-                if (to - from < kTileKeys) {
-                    const int quads = (head_dim * 2) >> 4;
-                    for (int i = lane; i < kTileKeys * quads; i += 32) {
-                        const int row = i / quads;
-                        if (tile_start + row < from || tile_start + row >= to)
-                            *reinterpret_cast<uint4*>(smem + (v_stage(stage) - smem_base) + row * L::kPitch + (i - row * quads) * 16) =
-                                make_uint4(0u, 0u, 0u, 0u);
-                    }
-                    // These plain stores and the bulk copies of later tiles touch the same bytes.
-                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                }
-                __syncwarp();
-                if (lane == 0) mbar_expect_tx(full_bar(stage), row_bytes * 2 * (to - from));
-                __syncwarp();
-                // One copy of K and one of V per page block that the tile's keys touch.
-                const int first_block = page_shift >= 0 ? from >> page_shift : from / page_size;
-                const int last_block = page_shift >= 0 ? (to - 1) >> page_shift : (to - 1) / page_size;
-                for (int block = first_block + lane; block <= last_block; block += 32) {
-                    const int block_start = block * page_size;
-                    const int lo_key = max(block_start, from), hi_key = min(block_start + page_size, to);
-                    int page = block == first_block + lane ? my_page : __ldg(table + block);
-                    if (page < 0 || page >= num_pages) {
-                        fault = 1;
-                        page = 0;
-                    }
-                    const __nv_bfloat16* src = cache + (static_cast<size_t>(page) * 2 * kv_heads + kv_head) * head_elems +
-                                               static_cast<size_t>(lo_key - block_start) * head_dim;
-                    const uint32_t bytes = row_bytes * (hi_key - lo_key);
-                    const uint32_t dst = (lo_key - tile_start) * L::kPitch;
-                    bulk_copy(k_stage(stage) + dst, src, bytes, full_bar(stage));
-                    bulk_copy(v_stage(stage) + dst, src + value_shift, bytes, full_bar(stage));
-                }
-            } else {
-                if (lane == 0) mbar_expect_tx(full_bar(stage), row_bytes * 2 * kTileKeys);
-                __syncwarp();
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    // A key outside the split's range copies the nearest key inside it (masked later).
-                    const int row = lane + 32 * half;
-                    const int key = min(max(tile_start + row, first_valid), key_end - 1);
-                    const int block = page_shift >= 0 ? key >> page_shift : key / page_size;
-                    const int in_page = page_shift >= 0 ? key & (page_size - 1) : key - block * page_size;
-                    int page = __ldg(table + block);
-                    if (page < 0 || page >= num_pages) {
-                        fault = 1;
-                        page = 0;
-                    }
-                    const __nv_bfloat16* src = cache + (static_cast<size_t>(page) * 2 * kv_heads + kv_head) * head_elems +
-                                               static_cast<size_t>(in_page) * head_dim;
-                    bulk_copy(k_stage(stage) + row * L::kPitch, src, row_bytes, full_bar(stage));
-                    bulk_copy(v_stage(stage) + row * L::kPitch, src + value_shift, row_bytes, full_bar(stage));
-                }
-            }
-        }
-        if (!ok) fault = 2;
+        if (!copy_warp<DMAX, BLOCKS>(ring, cache, block_table + static_cast<size_t>(segment) * table_stride, num_pages,
+                                     page_size, kv_heads, head_dim, kv_head, key_begin, key_end, first_valid, tiles, &fault))
+            fault = 2;
     } else {
         // ---------------- compute warps
         const int g = lane >> 2;
@@ -508,6 +478,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
         uint32_t qf[DMAX / 16][4];
         load_q<DMAX>(qf, qptr[0], qptr[1], dim_steps);
         const float scale_log2 = scale * kLog2e;
+        const int last_lo = window > 0 ? max(0, start + count - window) : 0;
         bool ok = true;
         for (int it = 0; it < tiles; ++it) {
             const int stage = it % kDecodeStages;
@@ -518,7 +489,10 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
                 float s[2][4] = {};
                 qk_keys<DMAX, 1, L>(s, qf, k_stage(stage), warp * 16, dim_steps);
                 uint32_t p[1][4];
-                softmax_step<DMAX, 2>(s, st, o, p, key_base, lo, hi, scale_log2, true);
+                // No key of these 16 needs a mask if all are at or before the first token's
+                // position and at or after the last token's window start.
+                const bool need_mask = key_base + 15 > start || key_base < last_lo;
+                softmax_step<DMAX, 2>(s, st, o, p, key_base, lo, hi, scale_log2, need_mask);
                 pv_16keys<DMAX, L>(o, p[0], v_stage(stage), warp * 16, dim_steps);
             }
             __syncwarp();
@@ -646,27 +620,29 @@ __global__ void __launch_bounds__(kThreads) combine_kernel(
 }
 
 // ---------------------------------------------------------------- prefill: flash attention
-// grid = (tiles, q_heads).  tiles[i] = {segment, first token of the 64-row tile within the
-// segment}.  Warp w owns rows 16w .. 16w+15 of the tile.
-template <int DMAX>
-__global__ void __launch_bounds__(kThreads) prefill_kernel(
+// grid = (tiles, q_heads), 160 threads.  tiles[i] = {segment, first token of the 64-row tile
+// within the segment}.  Warp 4 copies the key tiles (copy_warp); compute warp w owns rows
+// 16w .. 16w+15 of the query tile and walks the keys up to the diagonal with a running
+// softmax.  No block-wide barrier in the loop; waits are bounded.
+template <int DMAX, bool BLOCKS>
+__global__ void __launch_bounds__(kDecodeThreads) prefill_kernel(
     const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat16* __restrict__ out, int ldo,
     const __nv_bfloat16* __restrict__ cache, int num_pages, const int* __restrict__ tiles,
     const int* __restrict__ segment_info, const int* __restrict__ block_table, int table_stride,
     int page_size, int q_heads, int kv_heads, int head_dim, int window, float scale, int* status) {
     mlr_grid_dependents_may_start();
     mlr_grid_wait();
+    using L = typename std::conditional<BLOCKS, Tile<DMAX>, PaddedTile<DMAX>>::type;
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ int bad_page;
+    __shared__ __align__(8) unsigned long long barriers[2 * kDecodeStages];
+    __shared__ int fault;
     const int head = blockIdx.y;
     const int segment = tiles[blockIdx.x * 2], tile_token = tiles[blockIdx.x * 2 + 1];
     const int first_row = segment_info[segment * 4 + 0], count = segment_info[segment * 4 + 1];
     const int start = segment_info[segment * 4 + 2];
     const int kv_head = head / (q_heads / kv_heads);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int g = lane >> 2, t = lane & 3;
-    const int dim_steps = head_dim >> 4;
-    if (threadIdx.x == 0) bad_page = 0;
+    const int dim_steps = BLOCKS ? DMAX / 16 : head_dim >> 4;
 
     const int tile_rows = min(kTileKeys, count - tile_token);
     const int first_pos = start + tile_token, last_pos = first_pos + tile_rows - 1;
@@ -674,92 +650,91 @@ __global__ void __launch_bounds__(kThreads) prefill_kernel(
     const int key_begin = (first_key / kTileKeys) * kTileKeys;
     const int n_tiles = (last_pos + 1 - key_begin + kTileKeys - 1) / kTileKeys;
 
-    CacheView view{cache, block_table + static_cast<size_t>(segment) * table_stride, num_pages, page_size,
-                   log2_or_minus1(page_size), kv_heads, head_dim, kv_head};
-    const uint32_t smem_base = smem_u32(smem);
-    auto k_stage = [&](int s) { return smem_base + s * 2 * Tile<DMAX>::kBytes; };
-    auto v_stage = [&](int s) { return smem_base + s * 2 * Tile<DMAX>::kBytes + Tile<DMAX>::kBytes; };
-
-    int lo[2], hi[2];
-    const __nv_bfloat16* qptr[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const int row = warp * 16 + g + 8 * r;
-        const bool valid = row < tile_rows;
-        hi[r] = valid ? first_pos + row : -1;
-        lo[r] = valid ? (window > 0 ? max(0, first_pos + row - window + 1) : 0) : 0;
-        qptr[r] = valid ? q + static_cast<size_t>(first_row + tile_token + row) * ldq + static_cast<size_t>(head) * head_dim
-                        : nullptr;
+    const StageRing ring{smem_u32(smem), smem_u32(barriers), smem, L::kBytes};
+    if (threadIdx.x == 0) {
+        fault = 0;
+        init_ring(ring, 4);
     }
-    uint32_t qf[DMAX / 16][4];
-    load_q<DMAX>(qf, qptr[0], qptr[1], dim_steps);
-    float o[DMAX / 8][4];
-#pragma unroll
-    for (int dn = 0; dn < DMAX / 8; ++dn) o[dn][0] = o[dn][1] = o[dn][2] = o[dn][3] = 0.0f;
-    RowState st;
-    const float scale_log2 = scale * kLog2e;
-    // Rows of this warp: their lowest lower bound and highest position decide which key
-    // tiles the warp can skip and which need no mask at all.
-    const int warp_first = first_pos + warp * 16, warp_last = min(last_pos, warp_first + 15);
-    const int warp_lo_min = window > 0 ? max(0, warp_first - window + 1) : 0;
-    const int warp_lo_max = window > 0 ? max(0, warp_last - window + 1) : 0;
-    const bool warp_active = warp * 16 < tile_rows;
     __syncthreads();
 
+    if (warp == 4) {
+        if (!copy_warp<DMAX, BLOCKS>(ring, cache, block_table + static_cast<size_t>(segment) * table_stride, num_pages,
+                                     page_size, kv_heads, head_dim, kv_head, key_begin, last_pos + 1, max(first_key, key_begin),
+                                     n_tiles, &fault))
+            fault = 2;
+    } else {
+        const int g = lane >> 2, t = lane & 3;
+        int lo[2], hi[2];
+        const __nv_bfloat16* qptr[2];
 #pragma unroll
-    for (int s = 0; s < kPrefillStages - 1; ++s) {
-        if (s < n_tiles)
-            load_tile<DMAX>(view, key_begin + s * kTileKeys, first_key, last_pos,
-                            lookup_page(view, key_begin + s * kTileKeys, first_key, last_pos), k_stage(s), v_stage(s), &bad_page);
-        cp_async_commit();
-    }
-    int next_page = kPrefillStages - 1 < n_tiles
-                        ? lookup_page(view, key_begin + (kPrefillStages - 1) * kTileKeys, first_key, last_pos) : -1;
-    for (int it = 0; it < n_tiles; ++it) {
-        cp_async_wait<kPrefillStages - 2>();
-        __syncthreads();
-        const int next = it + kPrefillStages - 1;
-        if (next < n_tiles)
-            load_tile<DMAX>(view, key_begin + next * kTileKeys, first_key, last_pos, next_page,
-                            k_stage(next % kPrefillStages), v_stage(next % kPrefillStages), &bad_page);
-        cp_async_commit();
-        next_page = next + 1 < n_tiles ? lookup_page(view, key_begin + (next + 1) * kTileKeys, first_key, last_pos) : -1;
-        const int stage = it % kPrefillStages;
-        const int key0 = key_begin + it * kTileKeys;
-        if (warp_active && key0 <= warp_last && key0 + kTileKeys - 1 >= warp_lo_min) {
-            float s[8][4] = {};
-            qk_keys<DMAX, 4>(s, qf, k_stage(stage), 0, dim_steps);
-            const bool need_mask = key0 + kTileKeys - 1 > warp_first || key0 < warp_lo_max;
-            uint32_t p[4][4];
-            softmax_step<DMAX, 8>(s, st, o, p, key0, lo, hi, scale_log2, need_mask);
+        for (int r = 0; r < 2; ++r) {
+            const int row = warp * 16 + g + 8 * r;
+            const bool valid = row < tile_rows;
+            hi[r] = valid ? first_pos + row : -1;
+            lo[r] = valid ? (window > 0 ? max(0, first_pos + row - window + 1) : 0) : 0;
+            qptr[r] = valid ? q + static_cast<size_t>(first_row + tile_token + row) * ldq + static_cast<size_t>(head) * head_dim
+                            : nullptr;
+        }
+        uint32_t qf[DMAX / 16][4];
+        load_q<DMAX>(qf, qptr[0], qptr[1], dim_steps);
+        float o[DMAX / 8][4];
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) pv_16keys<DMAX>(o, p[kk], v_stage(stage), kk * 16, dim_steps);
+        for (int dn = 0; dn < DMAX / 8; ++dn) o[dn][0] = o[dn][1] = o[dn][2] = o[dn][3] = 0.0f;
+        RowState st;
+        const float scale_log2 = scale * kLog2e;
+        // Rows of this warp: their lowest lower bound and highest position decide which key
+        // tiles the warp can skip and which need no mask at all.
+        const int warp_first = first_pos + warp * 16, warp_last = min(last_pos, warp_first + 15);
+        const int warp_lo_min = window > 0 ? max(0, warp_first - window + 1) : 0;
+        const int warp_lo_max = window > 0 ? max(0, warp_last - window + 1) : 0;
+        const bool warp_active = warp * 16 < tile_rows;
+        bool ok = true;
+        for (int it = 0; it < n_tiles; ++it) {
+            const int stage = it % kDecodeStages;
+            ok = mbar_wait(ring.full_bar(stage), (it / kDecodeStages) & 1);
+            if (!ok) break;
+            const int key0 = key_begin + it * kTileKeys;
+            if (warp_active && key0 <= warp_last && key0 + kTileKeys - 1 >= warp_lo_min) {
+                float s[8][4] = {};
+                qk_keys<DMAX, 4, L>(s, qf, ring.k_stage(stage), 0, dim_steps);
+                // Rows 16w.. are all at or after warp_first; a tile wholly before it and wholly
+                // inside every row's window needs no mask (rows past the tile's end are not stored).
+                const bool need_mask = key0 + kTileKeys - 1 > warp_first || key0 < warp_lo_max;
+                uint32_t p[4][4];
+                softmax_step<DMAX, 8>(s, st, o, p, key0, lo, hi, scale_log2, need_mask);
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) pv_16keys<DMAX, L>(o, p[kk], ring.v_stage(stage), kk * 16, dim_steps);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ring.empty_bar(stage));
+        }
+        if (!ok) fault = 2;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+            st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+        }
+        if (ok) {
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int row = warp * 16 + g + 8 * r;
+                if (row >= tile_rows) continue;
+                const float inv = st.l[r] > 0.0f ? 1.0f / st.l[r] : 0.0f;
+                __nv_bfloat16* dst = out + static_cast<size_t>(first_row + tile_token + row) * ldo + static_cast<size_t>(head) * head_dim;
+#pragma unroll
+                for (int dn = 0; dn < DMAX / 8; ++dn) {
+                    if (dn * 8 < head_dim)
+                        *reinterpret_cast<uint32_t*>(dst + dn * 8 + 2 * t) = pack_bf16(o[dn][2 * r] * inv, o[dn][2 * r + 1] * inv);
+                }
+            }
         }
     }
-    cp_async_wait<0>();
-    if (bad_page && threadIdx.x == 0 && status) atomicOr(status, MLR_STATUS_BAD_PAGE);
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
-        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+    __syncthreads();
+    if (fault && threadIdx.x == 0) {
+        if (status) atomicOr(status, fault == 2 ? MLR_STATUS_TIMEOUT : MLR_STATUS_BAD_PAGE);
+        if (fault == 2)
+            for (int i = 0; i < 100; ++i) __nanosleep(1000);   // let copies in flight land before the block ends
     }
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const int row = warp * 16 + g + 8 * r;
-        if (row >= tile_rows) continue;
-        const float inv = st.l[r] > 0.0f ? 1.0f / st.l[r] : 0.0f;
-        __nv_bfloat16* dst = out + static_cast<size_t>(first_row + tile_token + row) * ldo + static_cast<size_t>(head) * head_dim;
-#pragma unroll
-        for (int dn = 0; dn < DMAX / 8; ++dn) {
-            if (dn * 8 < head_dim)
-                *reinterpret_cast<uint32_t*>(dst + dn * 8 + 2 * t) = pack_bf16(o[dn][2 * r] * inv, o[dn][2 * r + 1] * inv);
-        }
-    }
-}
-
-template <int DMAX>
-constexpr size_t tile_smem(int stages) {
-    return static_cast<size_t>(stages) * 2 * Tile<DMAX>::kBytes;
 }
 
 // Raises a kernel's dynamic shared memory limit; remembered per kernel and device so that
@@ -785,11 +760,12 @@ int allow_smem(Kernel kernel, size_t bytes, const char* what) {
 }
 
 int check_common(const char* what, int q_heads, int kv_heads, int head_dim, int page_size, int num_pages, int window,
-                 int ldq, int ldo) {
+                 int ldq, int ldo, float scale) {
     MLR_REQUIRE(q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0, "%s: %d query heads cannot share %d kv heads", what, q_heads, kv_heads);
     MLR_REQUIRE(head_dim >= 16 && head_dim <= 256 && head_dim % 16 == 0,
                 "%s: head size %d is not a multiple of 16 in [16, 256]", what, head_dim);
     MLR_REQUIRE(page_size > 0 && num_pages > 0 && window >= 0, "%s: bad page size, page count or window", what);
+    MLR_REQUIRE(scale > 0.0f, "%s: the score scale must be positive, got %g", what, static_cast<double>(scale));
     MLR_REQUIRE(ldq >= q_heads * head_dim && ldo >= q_heads * head_dim && ldq % 2 == 0 && ldo % 2 == 0,
                 "%s: a row stride is smaller than the row or odd", what);
     MLR_REQUIRE(kv_heads <= 65535 && q_heads <= 65535, "%s: more than 65535 heads", what);
@@ -812,7 +788,7 @@ MLR_API int mlr_attention_decode_bf16(const void* q, int ldq, void* out, int ldo
                                       const int* block_table, int table_stride, int page_size, int q_heads,
                                       int kv_heads, int head_dim, int window, float scale, int chunk,
                                       int max_splits, float* partial, int* status, cudaStream_t stream) {
-    if (int e = check_common("attention_decode_bf16", q_heads, kv_heads, head_dim, page_size, num_pages, window, ldq, ldo)) return e;
+    if (int e = check_common("attention_decode_bf16", q_heads, kv_heads, head_dim, page_size, num_pages, window, ldq, ldo, scale)) return e;
     MLR_REQUIRE(q_heads / kv_heads <= 16, "attention_decode_bf16: %d query heads per kv head exceed the 16 rows of a block", q_heads / kv_heads);
     MLR_REQUIRE(chunk > 0 && chunk % kTileKeys == 0, "attention_decode_bf16: chunk %d is not a positive multiple of %d", chunk, kTileKeys);
     MLR_REQUIRE(max_splits >= 1 && max_splits <= 512 && (max_splits == 1 || partial), "attention_decode_bf16: the split count must be in [1, 512], with scratch when above 1");
@@ -893,21 +869,26 @@ MLR_API int mlr_attention_prefill_bf16(const void* q, int ldq, void* out, int ld
                                        const int* block_table, int table_stride, int page_size, int q_heads,
                                        int kv_heads, int head_dim, int window, float scale, int* status,
                                        cudaStream_t stream) {
-    if (int e = check_common("attention_prefill_bf16", q_heads, kv_heads, head_dim, page_size, num_pages, window, ldq, ldo)) return e;
+    if (int e = check_common("attention_prefill_bf16", q_heads, kv_heads, head_dim, page_size, num_pages, window, ldq, ldo, scale)) return e;
     MLR_REQUIRE(n_tiles >= 0, "attention_prefill_bf16: negative tile count");
     if (n_tiles == 0) return 0;
     const dim3 grid(n_tiles, q_heads);
-#define MLR_LAUNCH(DMAX)                                                                                          \
-    do {                                                                                                          \
-        if (int e = allow_smem(prefill_kernel<DMAX>, tile_smem<DMAX>(kPrefillStages), "attention_prefill_bf16")) return e; \
-        mlr_launch((prefill_kernel<DMAX>), dim3(grid), dim3(kThreads), tile_smem<DMAX>(kPrefillStages), stream,                         \
-            static_cast<const __nv_bfloat16*>(q), ldq, static_cast<__nv_bfloat16*>(out), ldo,                     \
-            static_cast<const __nv_bfloat16*>(cache), num_pages, tiles, segment_info, block_table, table_stride,  \
-            page_size, q_heads, kv_heads, head_dim, window, scale, status);                                       \
+#define MLR_LAUNCH(DMAX, BLOCKS)                                                                                   \
+    do {                                                                                                           \
+        const size_t tile = BLOCKS ? Tile<DMAX>::kBytes : PaddedTile<DMAX>::kBytes;                                \
+        const size_t bytes = static_cast<size_t>(kDecodeStages) * 2 * tile;                                        \
+        if (int e = allow_smem(prefill_kernel<DMAX, BLOCKS>, bytes, "attention_prefill_bf16")) return e;          \
+        mlr_launch((prefill_kernel<DMAX, BLOCKS>), dim3(grid), dim3(kDecodeThreads), bytes, stream,               \
+                   static_cast<const __nv_bfloat16*>(q), ldq, static_cast<__nv_bfloat16*>(out), ldo,               \
+                   static_cast<const __nv_bfloat16*>(cache), num_pages, tiles, segment_info, block_table,          \
+                   table_stride, page_size, q_heads, kv_heads, head_dim, window, scale, status);                   \
     } while (0)
-    if (head_dim <= 64) MLR_LAUNCH(64);
-    else if (head_dim <= 128) MLR_LAUNCH(128);
-    else MLR_LAUNCH(256);
+    if (head_dim == 64) MLR_LAUNCH(64, true);
+    else if (head_dim == 128) MLR_LAUNCH(128, true);
+    else if (head_dim == 256) MLR_LAUNCH(256, true);
+    else if (head_dim < 64) MLR_LAUNCH(64, false);
+    else if (head_dim < 128) MLR_LAUNCH(128, false);
+    else MLR_LAUNCH(256, false);
 #undef MLR_LAUNCH
     return mlr_launched("attention_prefill_bf16");
 }
