@@ -33,8 +33,9 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-Wall"]
 
-# Extra link flags of kernel modules that call the driver API (tensor maps for TMA).
-MODULE_LINK = {"gemm_bf16_tcgen05": ["-lcuda"]}
+# Extra link flags per kernel module (none needs any today: the tensor-map encoder of the
+# driver is looked up at run time through cudaGetDriverEntryPoint).
+MODULE_LINK = {}
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()

@@ -7,10 +7,14 @@ the serving path: matrices, activations and the cache are bfloat16, products
 accumulate in float32.  In both, the residual stream, norms, softmax, rotation and
 logits are float32.
 
-Matrix products of the bfloat16 path go to the vendor library (cuBLAS through
-`torch.mm`), as the reference sends all of its products to cuBLAS
-(src/minillm/cuda/matrix.cpp:30-36), unless a hand-written kernel of this package
-covers the shape: products for at most 16 tokens run on `csrc/kernels/gemv_bf16.cu`.
+bfloat16 products of a decode step (up to 64 rows) run on the package's tcgen05/TMA
+kernel (`csrc/kernels/gemm_bf16_tcgen05.cu`): the weight matrix takes the 128-row side
+of the instruction, K is cut into ranges so that a small matrix still occupies every
+SM, and the kernel that reads the result adds the ranges' partial sums.  Products of
+prompt portions go to the vendor library (cuBLAS through `torch.mm`), as the reference
+sends all of its products to cuBLAS (src/minillm/cuda/matrix.cpp:30-36); the package's
+kernel takes those too when `tcgen05_prefill` is set (it reaches about 85 % of the
+library's two-SM kernels there).
 """
 from __future__ import annotations
 

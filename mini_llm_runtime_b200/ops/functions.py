@@ -190,36 +190,6 @@ def attention_prefill_bf16(q: torch.Tensor, out: torch.Tensor, cache: torch.Tens
          page_size, q_heads, kv_heads, head_dim, int(window), float(scale), ptr(status), stream())
 
 
-GEMV_MAX_TOKENS = 16
-
-
-def gemv_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether the weight-streaming kernel takes this product (else the library does)."""
-    return (x.dtype is torch.bfloat16 and w.dtype is torch.bfloat16 and 1 <= x.shape[0] <= GEMV_MAX_TOKENS
-            and x.shape[1] % 32 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and w.is_contiguous()
-            and x.data_ptr() % 16 == 0)
-
-
-def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor, swiglu: bool = False) -> None:
-    """out[M, N] = x[M, K] @ w[N, K]^T for M <= 16 (bf16 in, float32 accumulate; out bf16 or
-    float32).  With `swiglu`, w is the stacked gate/up matrix [2 I, K] and
-    out[M, I] = silu(x Wgate^T) * (x Wup^T) in bf16."""
-    on_gpu(x, w, out, status)
-    if not gemv_applies(x, w):
-        raise KernelError("gemv_bf16: this product is not one the kernel takes (bf16, 1..16 tokens, K % 32 == 0)")
-    if swiglu:
-        mode = 2
-        expect(out, torch.bfloat16, "the gated output")
-    else:
-        mode = 0 if out.dtype is torch.bfloat16 else 1
-        if out.dtype not in (torch.bfloat16, torch.float32):
-            raise KernelError("gemv_bf16: the output must be bfloat16 or float32")
-    if out.stride(1) != 1:
-        raise KernelError("gemv_bf16: the output needs unit inner stride")
-    call("gemv_bf16", "mlr_gemv_bf16", ptr(x), x.stride(0), x.shape[0], ptr(w), w.stride(0), w.shape[0], x.shape[1],
-         ptr(out), out.stride(0), mode, ptr(status), stream())
-
-
 def gemm_tcgen05_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
     return (x.dtype is torch.bfloat16 and w.dtype is torch.bfloat16 and x.shape[1] % 8 == 0 and x.shape[1] >= 8
             and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0

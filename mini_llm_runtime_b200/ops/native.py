@@ -49,9 +49,6 @@ _SIGNATURES = {
         "mlr_attention_prefill_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
                                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     },
-    "gemv_bf16": {
-        "mlr_gemv_bf16": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
-    },
     "gemm_bf16_tcgen05": {
         "mlr_gemm_bf16_tcgen05": [c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong,
                                   c_int, c_int, c_int, c_int, c_longlong, c_int, c_void_p, c_void_p],

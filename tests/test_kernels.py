@@ -143,49 +143,6 @@ def test_gemm_f32_is_true_float32_and_independent_of_batching(M, N, K):
     assert torch.equal(out2, out)
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (8, 4096, 4096), (3, 100, 96), (16, 515, 1056), (9, 6144, 4096), (5, 48, 12288)])
-@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-def test_gemv_bf16(M, N, K, out_dtype):
-    x = (torch.randn(M, K, generator=gen(0)) * 0.5).to(torch.bfloat16)
-    w = (torch.randn(N, K, generator=gen(1)) * 0.1).to(torch.bfloat16)
-    want = x.double() @ w.double().T
-    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
-    st = status()
-    F().gemv_bf16(x.to(DEV), w.to(DEV), out, st)
-    assert st.item() == 0
-    tol = 2e-2 if out_dtype is torch.bfloat16 else 1e-3      # bf16 rounding of the result; float32 sums of bf16 products
-    assert torch.allclose(out.double().cpu(), want, atol=tol * (1 + want.abs().max().item()), rtol=tol)
-    # x as a view with a wider row stride.
-    wide = torch.zeros(M, K + 64, dtype=torch.bfloat16, device=DEV)
-    wide[:, :K] = x.to(DEV)
-    out2 = torch.empty_like(out)
-    F().gemv_bf16(wide[:, :K], w.to(DEV), out2, st)
-    assert torch.equal(out2, out)
-
-
-@pytest.mark.parametrize("M,I,K", [(1, 8, 32), (8, 12288, 4096), (7, 100, 160), (16, 176, 96)])
-def test_gemv_bf16_fused_gate(M, I, K):
-    x = (torch.randn(M, K, generator=gen(0)) * 0.5).to(torch.bfloat16)
-    w = (torch.randn(2 * I, K, generator=gen(1)) * 0.1).to(torch.bfloat16)
-    g, u = x.double() @ w[:I].double().T, x.double() @ w[I:].double().T
-    want = g / (1 + torch.exp(-g)) * u
-    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
-    st = status()
-    F().gemv_bf16(x.to(DEV), w.to(DEV), out, st, swiglu=True)
-    assert st.item() == 0
-    assert torch.allclose(out.double().cpu(), want, atol=2e-2 * (1 + want.abs().max().item()), rtol=2e-2)
-
-
-def test_gemv_refuses_what_it_cannot_do():
-    from mini_llm_runtime_b200.ops.native import KernelError
-    x = torch.zeros(17, 64, dtype=torch.bfloat16, device=DEV)
-    w = torch.zeros(32, 64, dtype=torch.bfloat16, device=DEV)
-    with pytest.raises(KernelError, match="not one the kernel takes"):
-        F().gemv_bf16(x, w, torch.zeros(17, 32, dtype=torch.bfloat16, device=DEV), status())
-    with pytest.raises(KernelError, match="not one the kernel takes"):
-        F().gemv_bf16(x[:4, :48], w[:, :48].contiguous(), torch.zeros(4, 32, dtype=torch.bfloat16, device=DEV), status())
-
-
 @pytest.mark.parametrize("M,N,K", [(1, 64, 64), (8, 4096, 4096), (3, 100, 96), (16, 515, 1056), (64, 300, 200), (65, 256, 64),
                                    (128, 256, 4096), (200, 515, 136), (2048, 6144, 4096), (300, 48, 12288), (129, 24, 72)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
