@@ -624,8 +624,12 @@ __global__ void __launch_bounds__(kThreads) combine_kernel(
 // within the segment}.  Warp 4 copies the key tiles (copy_warp); compute warp w owns rows
 // 16w .. 16w+15 of the query tile and walks the keys up to the diagonal with a running
 // softmax.  No block-wide barrier in the loop; waits are bounded.
+// Registers: an SM's register file is split over four schedulers of 16384 registers each, and
+// a block's five warps spread over them, so two blocks per SM need three warps to fit one
+// scheduler: at most 168 registers per thread (5376 per warp).  Above that only one block
+// runs per SM and the kernel loses about a third of its speed.
 template <int DMAX, bool BLOCKS>
-__global__ void __launch_bounds__(kDecodeThreads) prefill_kernel(
+__global__ void __launch_bounds__(kDecodeThreads) __maxnreg__(DMAX <= 128 ? 168 : 255) prefill_kernel(
     const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat16* __restrict__ out, int ldo,
     const __nv_bfloat16* __restrict__ cache, int num_pages, const int* __restrict__ tiles,
     const int* __restrict__ segment_info, const int* __restrict__ block_table, int table_stride,

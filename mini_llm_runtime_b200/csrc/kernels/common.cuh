@@ -104,6 +104,22 @@ __device__ __forceinline__ float mlr_load(const __nv_bfloat16* p, size_t i) { re
 __device__ __forceinline__ void mlr_store(float* p, size_t i, float v) { p[i] = v; }
 __device__ __forceinline__ void mlr_store(__nv_bfloat16* p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
 
+// ---- 2 consecutive elements (the address must be aligned to the pair) ----
+__device__ __forceinline__ void mlr_load2(const float* p, float& a, float& b) {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    a = v.x;
+    b = v.y;
+}
+__device__ __forceinline__ void mlr_load2(const __nv_bfloat16* p, float& a, float& b) {
+    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(p);
+    a = __low2float(v);
+    b = __high2float(v);
+}
+__device__ __forceinline__ void mlr_store2(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void mlr_store2(__nv_bfloat16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
 // ---- 4 and 8 consecutive elements with 8- or 16-byte accesses (the address must be aligned to the access) ----
 __device__ __forceinline__ void mlr_load4(const float* p, float (&v)[4]) {
     const float4 q = *reinterpret_cast<const float4*>(p);

@@ -174,7 +174,7 @@ constexpr int kMaxPairsPerLane = 4;  // D/2 <= 128
 // With `partials`, the input is not qkv itself but `slices` float32 partial sums of it
 // ([slices][rows][ld_partial]); they are added in order as they are read, and qkv only
 // receives the results.
-template <typename T, typename W>
+template <typename T, typename W, bool VEC2>
 __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ partials, int slices,
                                           size_t slice_stride, int ld_partial, int rows, int q_heads, int kv_heads,
                                           int head_dim, const W* __restrict__ q_weight,
@@ -219,21 +219,56 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, int ld, const flo
               static_cast<size_t>(position % page_size) * head_dim;
     }
     const bool swizzled = mlr_cache_swizzled(sizeof(T) == 2, head_dim);
+    // Two adjacent elements per access where the head size allows it (a multiple of 4, so that
+    // both halves of a head start on a pair): wider loads and stores, same arithmetic.
+    auto input2 = [&](int i, float& a, float& b) {
+        if (xp) {
+            float2 v = *reinterpret_cast<const float2*>(xp + i);
+            for (int s = 1; s < slices; ++s) {
+                const float2 e = *reinterpret_cast<const float2*>(xp + s * slice_stride + i);
+                v.x += e.x;
+                v.y += e.y;
+            }
+            a = v.x;
+            b = v.y;
+        } else {
+            mlr_load2(x + i, a, b);
+        }
+    };
     if (is_value) {
-        for (int i = lane; i < head_dim; i += 32) mlr_store(dst, mlr_cache_col(i, position, swizzled), input(i));
+        if (VEC2) {
+            for (int i = 2 * lane; i < head_dim; i += 64) {
+                float a, b;
+                input2(i, a, b);
+                mlr_store2(dst + mlr_cache_col(i, position, swizzled), a, b);
+            }
+        } else {
+            for (int i = lane; i < head_dim; i += 32) mlr_store(dst, mlr_cache_col(i, position, swizzled), input(i));
+        }
         return;
     }
-    float lo[kMaxPairsPerLane], hi[kMaxPairsPerLane];
+    constexpr int kSlots = VEC2 ? 2 : kMaxPairsPerLane;     // VEC2: 2 x (2 + 2) elements per lane cover a head of 256
+    constexpr int kWidth = VEC2 ? 2 : 1;
+    float lo[kSlots][kWidth], hi[kSlots][kWidth];
     float sum = 0.0f;
 #pragma unroll
-    for (int k = 0; k < kMaxPairsPerLane; ++k) {
-        const int j = lane + 32 * k;
-        lo[k] = hi[k] = 0.0f;
+    for (int k = 0; k < kSlots; ++k) {
+        const int j = kWidth * (lane + 32 * k);
+#pragma unroll
+        for (int e = 0; e < kWidth; ++e) lo[k][e] = hi[k][e] = 0.0f;
         if (j < half) {
-            lo[k] = input(j);
-            hi[k] = input(j + half);
-            sum = fmaf(lo[k], lo[k], sum);
-            sum = fmaf(hi[k], hi[k], sum);
+            if (VEC2) {
+                input2(j, lo[k][0], lo[k][kWidth - 1]);
+                input2(j + half, hi[k][0], hi[k][kWidth - 1]);
+            } else {
+                lo[k][0] = input(j);
+                hi[k][0] = input(j + half);
+            }
+#pragma unroll
+            for (int e = 0; e < kWidth; ++e) {
+                sum = fmaf(lo[k][e], lo[k][e], sum);
+                sum = fmaf(hi[k][e], hi[k][e], sum);
+            }
         }
     }
     const W* weight = is_query ? q_weight : k_weight;
@@ -249,26 +284,40 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, int ld, const flo
     }
     const float* cs = rotate ? cos_sin + static_cast<size_t>(position) * head_dim : nullptr;
 #pragma unroll
-    for (int k = 0; k < kMaxPairsPerLane; ++k) {
-        const int j = lane + 32 * k;
+    for (int k = 0; k < kSlots; ++k) {
+        const int j = kWidth * (lane + 32 * k);
         if (j < half) {
-            float a = lo[k], b = hi[k];
-            if (weight) {
-                a = (a * scale) * mlr_load(weight, j);
-                b = (b * scale) * mlr_load(weight, j + half);
+            float a[kWidth], b[kWidth];
+#pragma unroll
+            for (int e = 0; e < kWidth; ++e) {
+                a[e] = lo[k][e];
+                b[e] = hi[k][e];
+                if (weight) {
+                    a[e] = (a[e] * scale) * mlr_load(weight, j + e);
+                    b[e] = (b[e] * scale) * mlr_load(weight, j + e + half);
+                }
+                if (rotate) {
+                    const float c = cs[j + e], sn = cs[j + e + half];
+                    const float ra = __fsub_rn(__fmul_rn(a[e], c), __fmul_rn(b[e], sn));
+                    const float rb = __fadd_rn(__fmul_rn(a[e], sn), __fmul_rn(b[e], c));
+                    a[e] = ra;
+                    b[e] = rb;
+                }
             }
-            if (rotate) {
-                const float c = cs[j], s = cs[j + half];
-                const float ra = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
-                const float rb = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
-                a = ra;
-                b = rb;
-            }
-            mlr_store(x, j, a);
-            mlr_store(x, j + half, b);
-            if (dst) {
-                mlr_store(dst, mlr_cache_col(j, position, swizzled), a);
-                mlr_store(dst, mlr_cache_col(j + half, position, swizzled), b);
+            if (VEC2) {
+                mlr_store2(x + j, a[0], a[kWidth - 1]);
+                mlr_store2(x + j + half, b[0], b[kWidth - 1]);
+                if (dst) {
+                    mlr_store2(dst + mlr_cache_col(j, position, swizzled), a[0], a[kWidth - 1]);
+                    mlr_store2(dst + mlr_cache_col(j + half, position, swizzled), b[0], b[kWidth - 1]);
+                }
+            } else {
+                mlr_store(x, j, a[0]);
+                mlr_store(x, j + half, b[0]);
+                if (dst) {
+                    mlr_store(dst, mlr_cache_col(j, position, swizzled), a[0]);
+                    mlr_store(dst, mlr_cache_col(j + half, position, swizzled), b[0]);
+                }
             }
         }
     }
@@ -411,12 +460,24 @@ MLR_API int mlr_qk_norm_rope_cache(void* qkv, int act_bf16, int ld, const float*
     if (rows == 0) return 0;
     const int warps = 4;
     const dim3 grid(rows, (q_heads + 2 * kv_heads + warps - 1) / warps);
+    const bool vec2 = head_dim % 4 == 0 && ld % 2 == 0 && reinterpret_cast<uintptr_t>(qkv) % 8 == 0 &&
+                      (!cache || reinterpret_cast<uintptr_t>(cache) % 8 == 0) &&
+                      (!partials || (reinterpret_cast<uintptr_t>(partials) % 8 == 0 && ld_partial % 2 == 0 && slice_stride % 2 == 0));
 #define MLR_LAUNCH(T, W)                                                                                       \
-    mlr_launch((qk_norm_rope_cache_kernel<T, W>), dim3(grid), dim3(warps * 32), 0, stream,                                           \
+    do {                                                                                                       \
+    if (vec2)                                                                                                  \
+    mlr_launch((qk_norm_rope_cache_kernel<T, W, true>), dim3(grid), dim3(warps * 32), 0, stream,             \
         static_cast<T*>(qkv), ld, partials, slices, static_cast<size_t>(slice_stride), ld_partial, rows, q_heads,  \
         kv_heads, head_dim, static_cast<const W*>(q_weight),                                                   \
         static_cast<const W*>(k_weight), eps, cos_sin, table_positions, positions, segment_of_row, block_table, \
-        table_stride, page_size, static_cast<T*>(cache), num_pages, write_cache, status)
+        table_stride, page_size, static_cast<T*>(cache), num_pages, write_cache, status);                      \
+    else                                                                                                       \
+    mlr_launch((qk_norm_rope_cache_kernel<T, W, false>), dim3(grid), dim3(warps * 32), 0, stream,                                           \
+        static_cast<T*>(qkv), ld, partials, slices, static_cast<size_t>(slice_stride), ld_partial, rows, q_heads,  \
+        kv_heads, head_dim, static_cast<const W*>(q_weight),                                                   \
+        static_cast<const W*>(k_weight), eps, cos_sin, table_positions, positions, segment_of_row, block_table, \
+        table_stride, page_size, static_cast<T*>(cache), num_pages, write_cache, status);                      \
+    } while (0)
     if (act_bf16 && w_bf16) MLR_LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else if (act_bf16) MLR_LAUNCH(__nv_bfloat16, float);
     else if (w_bf16) MLR_LAUNCH(float, __nv_bfloat16);
