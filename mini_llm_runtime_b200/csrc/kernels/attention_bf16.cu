@@ -5,7 +5,7 @@
 //                    <= 16: a decoded token, or a portion of two or three tokens).  One
 //                    block per (request, kv head, split of the keys); its four compute warps
 //                    walk disjoint keys of each 64-key tile with their own running softmax
-//                    and are merged at the end; splits are merged by `combine`.  The bytes
+//                    and are merged at the end; the block that finishes last merges the splits.  The bytes
 //                    of the cache are what it is bound by.
 //   prefill          for prompt portions.  One block per (64 query rows, query head); its
 //                    four compute warps own 16 rows each and walk the keys up to the
@@ -416,7 +416,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
     const __nv_bfloat16* __restrict__ cache, int num_pages, const int* __restrict__ items,
     const int* __restrict__ segment_info, const int* __restrict__ block_table, int table_stride,
     int page_size, int q_heads, int kv_heads, int head_dim, int window, float scale, int chunk,
-    int max_splits, float* __restrict__ partial, int* status) {
+    int max_splits, float* __restrict__ partial, int* __restrict__ counters, int* status) {
     mlr_grid_dependents_may_start();
     mlr_grid_wait();
     // BLOCKS: the cache rows are stored swizzled (head size 64, 128 or 256 = DMAX), so whole
@@ -507,6 +507,11 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
             // Give copies that may still be in flight time to land before the block's shared
             // memory is handed to another block.
             for (int i = 0; i < 100; ++i) __nanosleep(1000);
+            // Still count this block, so that the counter goes back to zero.
+            if (threadIdx.x == 0 && plan.splits > 1) {
+                int* counter = counters + item * kv_heads + kv_head;
+                if (atomicAdd(counter, 1) == plan.splits - 1) *counter = 0;
+            }
             return;
         }
     }
@@ -568,30 +573,31 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
             }
         }
     }
-}
+    if (direct) return;
 
-// grid = (items, kv_heads).  Adds up the splits of an item in split order.  The weights
-// exp2(m_split - m) / l are worked out once per (split, row) in shared memory; the sums
-// over splits then have no dependent loads.
-__global__ void __launch_bounds__(kThreads) combine_kernel(
-    __nv_bfloat16* __restrict__ out, int ldo, const int* __restrict__ items, const int* __restrict__ segment_info,
-    int q_heads, int kv_heads, int head_dim, int window, int chunk, int max_splits, const float* __restrict__ partial) {
-    mlr_grid_dependents_may_start();
-    mlr_grid_wait();
-    extern __shared__ float factor[];   // [splits][16]
-    const int item = blockIdx.x, kv_head = blockIdx.y;
-    const int segment = items ? items[item] : item;
-    const int first_row = segment_info[segment * 4 + 0], count = segment_info[segment * 4 + 1];
-    const int start = segment_info[segment * 4 + 2];
-    const SplitPlan plan = plan_splits(start, count, window, chunk);
-    if (plan.splits <= 1) return;
-    const int group = q_heads / kv_heads;
-    const int rows = count * group;
+    // The block that finishes last among the splits of this (request, kv head) adds them up,
+    // in split order, so the sum does not depend on which block that is.  The counter is left
+    // at zero for the next launch.
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* counter = counters + item * kv_heads + kv_head;
+        is_last = atomicAdd(counter, 1) == plan.splits - 1;
+        if (is_last) *counter = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // The weights exp2(m_split - m) / l are worked out once per (split, row) in shared memory;
+    // the sums over splits then have no dependent loads.  Other SMs wrote the partial
+    // results: they are read from L2, past this SM's L1.
+    float* factor = merge_ml + 4 * 16 * 2;      // [splits][16]
     const int stride = head_dim + 2;
     const float* base = partial + (static_cast<size_t>(item) * kv_heads + kv_head) * max_splits * 16 * stride;
-    for (int i = threadIdx.x; i < plan.splits * 16; i += kThreads) {
+    for (int i = threadIdx.x; i < plan.splits * 16; i += kDecodeThreads) {
         const int row = i & 15;
-        factor[i] = row < rows ? base[i * stride + head_dim] : -INFINITY;   // the split's maximum, for now
+        factor[i] = row < rows ? __ldcg(base + i * stride + head_dim) : -INFINITY;
     }
     __syncthreads();
     if (threadIdx.x < rows) {
@@ -602,20 +608,22 @@ __global__ void __launch_bounds__(kThreads) combine_kernel(
         for (int s = 0; s < plan.splits; ++s) {
             const float ms = factor[s * 16 + row];
             const float f = ms == -INFINITY ? 0.0f : exp2f(ms - m);
-            l += base[(s * 16 + row) * stride + head_dim + 1] * f;
+            l += __ldcg(base + (s * 16 + row) * stride + head_dim + 1) * f;
             factor[s * 16 + row] = f;
         }
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
         for (int s = 0; s < plan.splits; ++s) factor[s * 16 + row] *= inv;
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < rows * head_dim; idx += kThreads) {
+    for (int idx = threadIdx.x; idx < rows * head_dim; idx += kDecodeThreads) {
         const int row = idx / head_dim, d = idx - row * head_dim;
         float acc = 0.0f;
 #pragma unroll 4
-        for (int s = 0; s < plan.splits; ++s) acc = fmaf(base[(s * 16 + row) * stride + d], factor[s * 16 + row], acc);
+        for (int s = 0; s < plan.splits; ++s)
+            acc = fmaf(__ldcg(base + (s * 16 + row) * stride + d), factor[s * 16 + row], acc);
         const int token = row / group, head = kv_head * group + row % group;
-        out[static_cast<size_t>(first_row + token) * ldo + static_cast<size_t>(head) * head_dim + d] = __float2bfloat16_rn(acc);
+        out[static_cast<size_t>(first_row + token) * ldo + static_cast<size_t>(head) * head_dim + d] =
+            __float2bfloat16_rn(acc);
     }
 }
 
@@ -786,23 +794,23 @@ MLR_API long long mlr_attention_decode_scratch_floats(int items, int kv_heads, i
 // items: segment indices (null = segments 0..n_items-1).  Every item must have
 // count * (q_heads / kv_heads) <= 16 rows.  chunk: keys per split, a multiple of 64.
 // max_splits: the most splits any item needs (the grid's x extent).  partial: scratch of
-// mlr_attention_decode_scratch_floats floats (may be null when max_splits == 1).
+// mlr_attention_decode_scratch_floats floats, and counters: n_items * kv_heads ints that are
+// zero on entry and are left zero (both may be null when max_splits == 1).
 MLR_API int mlr_attention_decode_bf16(const void* q, int ldq, void* out, int ldo, const void* cache, int num_pages,
                                       const int* items, int n_items, const int* segment_info,
                                       const int* block_table, int table_stride, int page_size, int q_heads,
                                       int kv_heads, int head_dim, int window, float scale, int chunk,
-                                      int max_splits, float* partial, int* status, cudaStream_t stream) {
+                                      int max_splits, float* partial, int* counters, int* status, cudaStream_t stream) {
     if (int e = check_common("attention_decode_bf16", q_heads, kv_heads, head_dim, page_size, num_pages, window, ldq, ldo, scale)) return e;
     MLR_REQUIRE(q_heads / kv_heads <= 16, "attention_decode_bf16: %d query heads per kv head exceed the 16 rows of a block", q_heads / kv_heads);
     MLR_REQUIRE(chunk > 0 && chunk % kTileKeys == 0, "attention_decode_bf16: chunk %d is not a positive multiple of %d", chunk, kTileKeys);
-    MLR_REQUIRE(max_splits >= 1 && max_splits <= 512 && (max_splits == 1 || partial), "attention_decode_bf16: the split count must be in [1, 512], with scratch when above 1");
+    MLR_REQUIRE(max_splits >= 1 && max_splits <= 512 && (max_splits == 1 || (partial && counters)), "attention_decode_bf16: the split count must be in [1, 512], with scratch and counters when above 1");
     MLR_REQUIRE(n_items >= 0 && n_items <= 65535, "attention_decode_bf16: more than 65535 requests in one launch");
     if (n_items == 0) return 0;
     const dim3 grid(max_splits, kv_heads, n_items);
-    const dim3 combine_grid(n_items, kv_heads);
 #define MLR_LAUNCH(DMAX, BLOCKS)                                                                                   \
     do {                                                                                                           \
-        const size_t merge = sizeof(float) * (4 * 16 * DMAX + 4 * 16 * 2);                                         \
+        const size_t merge = sizeof(float) * (4 * 16 * DMAX + 4 * 16 * 2 + 16 * max_splits);                       \
         const size_t tile = BLOCKS ? Tile<DMAX>::kBytes : PaddedTile<DMAX>::kBytes;                                \
         const size_t stages = static_cast<size_t>(kDecodeStages) * 2 * tile;                                       \
         const size_t bytes = stages > merge ? stages : merge;                                                      \
@@ -810,7 +818,7 @@ MLR_API int mlr_attention_decode_bf16(const void* q, int ldq, void* out, int ldo
         mlr_launch((decode_splitkv_kernel<DMAX, BLOCKS>), dim3(grid), dim3(kDecodeThreads), bytes, stream,                               \
             static_cast<const __nv_bfloat16*>(q), ldq, static_cast<__nv_bfloat16*>(out), ldo,                      \
             static_cast<const __nv_bfloat16*>(cache), num_pages, items, segment_info, block_table, table_stride,   \
-            page_size, q_heads, kv_heads, head_dim, window, scale, chunk, max_splits, partial, status);            \
+            page_size, q_heads, kv_heads, head_dim, window, scale, chunk, max_splits, partial, counters, status);  \
     } while (0)
     if (head_dim == 64) MLR_LAUNCH(64, true);
     else if (head_dim == 128) MLR_LAUNCH(128, true);
@@ -819,13 +827,7 @@ MLR_API int mlr_attention_decode_bf16(const void* q, int ldq, void* out, int ldo
     else if (head_dim < 128) MLR_LAUNCH(128, false);
     else MLR_LAUNCH(256, false);
 #undef MLR_LAUNCH
-    if (int e = mlr_launched("attention_decode_bf16")) return e;
-    if (max_splits > 1) {
-        mlr_launch((combine_kernel), dim3(combine_grid), dim3(kThreads), sizeof(float) * 16 * max_splits, stream, static_cast<__nv_bfloat16*>(out), ldo, items, segment_info,
-                                                             q_heads, kv_heads, head_dim, window, chunk, max_splits, partial);
-        return mlr_launched("attention_decode_bf16 combine");
-    }
-    return 0;
+    return mlr_launched("attention_decode_bf16");
 }
 
 // ---------------------------------------------------------------- the entry point that allocates nothing
@@ -833,6 +835,9 @@ MLR_API int mlr_attention_decode_bf16(const void* q, int ldq, void* out, int ldo
 // this name is only a handle for the runtime: the device address comes from
 // cudaGetSymbolAddress.
 static __device__ __align__(256) float mlr_static_scratch[MLR_ATTENTION_STATIC_SCRATCH_FLOATS];
+// One counter per (request, kv head) of a call: zero when the library is loaded, and every
+// call leaves them zero again.
+static __device__ __align__(256) int mlr_static_counters[MLR_ATTENTION_STATIC_COUNTERS];
 
 MLR_API int mlr_attention_decode_bf16_no_alloc(const void* q, int ldq, void* out, int ldo, const void* cache,
                                                int num_pages, const int* items, int n_items,
@@ -848,9 +853,13 @@ MLR_API int mlr_attention_decode_bf16_no_alloc(const void* q, int ldq, void* out
                 "attention_decode_bf16_no_alloc: the call needs %lld floats of scratch, the built-in array holds %d; "
                 "use fewer requests per call, fewer splits, or mlr_attention_decode_bf16 with a buffer of your own",
                 need, MLR_ATTENTION_STATIC_SCRATCH_FLOATS);
-    // Device address of the array, looked up once per device with that device current.
+    MLR_REQUIRE(static_cast<long long>(n_items) * kv_heads <= MLR_ATTENTION_STATIC_COUNTERS,
+                "attention_decode_bf16_no_alloc: %d requests x %d kv heads exceed the %d built-in counters", n_items, kv_heads,
+                MLR_ATTENTION_STATIC_COUNTERS);
+    // Device addresses of the arrays, looked up once per device with that device current.
     constexpr int kMaxDevices = 64;
     static float* address[kMaxDevices] = {};
+    static int* counter_address[kMaxDevices] = {};
     int device = -1;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return mlr_fail("attention_decode_bf16_no_alloc: cudaGetDevice: %s", cudaGetErrorString(e));
@@ -860,11 +869,16 @@ MLR_API int mlr_attention_decode_bf16_no_alloc(const void* q, int ldq, void* out
         e = cudaGetSymbolAddress(&found, mlr_static_scratch);
         if (e != cudaSuccess || found == nullptr)
             return mlr_fail("attention_decode_bf16_no_alloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        void* found_counters = nullptr;
+        e = cudaGetSymbolAddress(&found_counters, mlr_static_counters);
+        if (e != cudaSuccess || found_counters == nullptr)
+            return mlr_fail("attention_decode_bf16_no_alloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        counter_address[device] = static_cast<int*>(found_counters);
         address[device] = static_cast<float*>(found);
     }
     return mlr_attention_decode_bf16(q, ldq, out, ldo, cache, num_pages, items, n_items, segment_info, block_table,
                                      table_stride, page_size, q_heads, kv_heads, head_dim, window, scale, chunk,
-                                     max_splits, address[device], status, stream);
+                                     max_splits, address[device], counter_address[device], status, stream);
 }
 
 // tiles: n_tiles pairs {segment, first token of a 64-row tile of that segment}.

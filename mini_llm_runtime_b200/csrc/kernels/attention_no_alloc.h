@@ -27,8 +27,11 @@
 //    streams, other host threads) would overwrite each other's partial results: run
 //    them one after the other on one stream.
 //  * The array keeps what the last call left in it.  That is harmless here: every
-//    element a merge reads was written by the same call's split kernel before, so
-//    nothing has to start at zero and nothing is cleared.
+//    element a merge reads was written by the same call's split blocks before, so
+//    nothing of it has to start at zero and nothing is cleared.  A small counter array
+//    beside it (one int per request and kv head, MLR_ATTENTION_STATIC_COUNTERS of
+//    them; a call with more is refused) does have to be zero: it is when the library
+//    is loaded, and the block that merges the splits sets its counter back to zero.
 //  * Inputs and outputs are still the caller's: q, out, the cache, the block table and
 //    the segment table are passed exactly as to mlr_attention_decode_bf16.
 //
@@ -38,6 +41,7 @@
 #include <cuda_runtime.h>
 
 #define MLR_ATTENTION_STATIC_SCRATCH_FLOATS (1 << 20)
+#define MLR_ATTENTION_STATIC_COUNTERS 4096      // requests x kv heads of one call
 
 extern "C" int mlr_attention_decode_bf16_no_alloc(const void* q, int ldq, void* out, int ldo, const void* cache,
                                                   int num_pages, const int* items, int n_items,

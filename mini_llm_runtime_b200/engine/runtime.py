@@ -42,6 +42,7 @@ class Runtime:
         self.decode_rows = 64         # up to this many rows a product streams the weights (swapped operands, split K)
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self._splits = {}
+        self._counters = None
         self.status = None        # the model's device status word (set at bind time)
         self._shared = {}
 
@@ -70,6 +71,16 @@ class Runtime:
     # ---- buffers
     def empty(self, *shape, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
+
+    def split_counters(self, count: int) -> torch.Tensor:
+        """Zeroed int32 counters for kernels that merge their own split results and leave the
+        counters zero again.  One long-lived tensor, made outside any graph capture, so a
+        captured step keeps pointing at it."""
+        if self._counters is None or count > self._counters.numel():
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("the split counters must be sized before a step is captured")
+            self._counters = torch.zeros(max(2 * count, 1 << 14), dtype=torch.int32, device=self.device)
+        return self._counters
 
     # ---- y = x @ w.T
     def _own_gemm(self, x: torch.Tensor, w: torch.Tensor) -> bool:

@@ -111,7 +111,7 @@ def paged_attention(qkv, out, cache, table, step, q_heads, kv_heads, head_dim, w
                 step.scratch[("attention_partial", count)] = partial
         F.attention_decode_bf16(qkv, out, cache, plan.items, plan.n_items, step.segment_info, table, step.page_size,
                                 q_heads, kv_heads, head_dim, window, scale, plan.chunk, plan.max_splits, partial,
-                                step.status)
+                                step.status, counters=step.rt.split_counters(plan.n_items * kv_heads))
     if plan.tiles is not None:
         F.attention_prefill_bf16(qkv, out, cache, plan.tiles, step.segment_info, table, step.page_size, q_heads,
                                  kv_heads, head_dim, window, scale, step.status)

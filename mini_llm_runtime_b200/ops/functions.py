@@ -148,12 +148,20 @@ def sample(logits: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
 def attention_decode_bf16(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, items: Optional[torch.Tensor],
                           n_items: int, segment_info: torch.Tensor, block_table: torch.Tensor, page_size: int,
                           q_heads: int, kv_heads: int, head_dim: int, window: int, scale: float, chunk: int,
-                          max_splits: int, partial: Optional[torch.Tensor], status: torch.Tensor) -> None:
+                          max_splits: int, partial: Optional[torch.Tensor], status: torch.Tensor,
+                          counters: Optional[torch.Tensor] = None) -> None:
     """Split-KV attention for requests that bring at most 16 rows per kv head (tokens
     times query heads per kv head).  `items` lists the segments to run (None: all of
     them, in order); `partial` is float32 scratch of `attention_decode_scratch_floats`
-    elements (needed when max_splits > 1)."""
-    on_gpu(q, out, cache, items, segment_info, block_table, partial, status)
+    elements and `counters` int32 zeros, one per item and kv head, which the kernel leaves
+    zero again (both needed when max_splits > 1; without `counters` a zeroed tensor is made)."""
+    on_gpu(q, out, cache, items, segment_info, block_table, partial, status, counters)
+    if max_splits > 1 and counters is None:
+        counters = torch.zeros(n_items * kv_heads, dtype=torch.int32, device=q.device)
+    if counters is not None:
+        expect(counters, torch.int32, "the split counters")
+        if counters.numel() < n_items * kv_heads:
+            raise KernelError("attention_decode_bf16: too few split counters")
     for t in (q, out, cache):
         if t.dtype is not torch.bfloat16:
             raise KernelError("attention_decode_bf16 takes bfloat16 tensors")
@@ -166,7 +174,7 @@ def attention_decode_bf16(q: torch.Tensor, out: torch.Tensor, cache: torch.Tenso
     call("attention_bf16", "mlr_attention_decode_bf16", ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(cache),
          cache.shape[0], ptr(items), n_items, ptr(segment_info), ptr(block_table), block_table.stride(0), page_size,
          q_heads, kv_heads, head_dim, int(window), float(scale), int(chunk), int(max_splits), ptr(partial),
-         ptr(status), stream())
+         ptr(counters), ptr(status), stream())
 
 
 def attention_decode_scratch_floats(n_items: int, kv_heads: int, head_dim: int, max_splits: int) -> int:

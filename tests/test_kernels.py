@@ -308,6 +308,8 @@ def test_attention_generic(case, dtype):
 
 
 def tensor_core_kernels(chunk=None):
+    shared = {}     # one set of split counters for all calls: each call leaves them zero
+
     def kernel(qkv, out, cache, table, positions, seg_of_row, info, segs, page, Hq, Hkv, D, window, scale, st):
         group = Hq // Hkv
         small = [i for i, (_, c) in enumerate(segs) if group <= 16 and c * group <= 16]
@@ -321,10 +323,12 @@ def tensor_core_kernels(chunk=None):
             ck = chunk or 128
             splits = max(-(-s // ck) for s in spans)
             items = torch.tensor(small, dtype=torch.int32, device=DEV)
+            counters = shared.setdefault("counters", torch.zeros(256, dtype=torch.int32, device=DEV))
             partial = torch.full((F().attention_decode_scratch_floats(len(small), Hkv, D, splits),), float("nan"),
                                  device=DEV)
             F().attention_decode_bf16(qkv, out, cache, items, len(small), info, table, page, Hq, Hkv, D, window, scale,
-                                      ck, splits, partial, st)
+                                      ck, splits, partial, st, counters=counters)
+            assert int(counters.abs().sum()) == 0, "the split counters were not left at zero"
         if large:
             tiles = torch.tensor([(i, t) for i in large for t in range(0, segs[i][1], 64)], dtype=torch.int32, device=DEV)
             F().attention_prefill_bf16(qkv, out, cache, tiles, info, table, page, Hq, Hkv, D, window, scale, st)
