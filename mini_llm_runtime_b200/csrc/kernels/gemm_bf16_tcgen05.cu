@@ -23,87 +23,16 @@
 //
 // The reference has no kernel of this kind: it calls cublasGemmEx for every product
 // (src/minillm/cuda/matrix.cpp:30-36).
-#include "common.cuh"
-
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 namespace {
+
+using namespace mlr_tc;
 
 constexpr int kThreads = 192;
 constexpr int kTileP = 128;     // rows of Pm per tile (the M of the instruction)
 constexpr int kTileK = 64;      // 64 bf16 = 128 bytes = one swizzle row
 constexpr int kTilePBytes = kTileP * kTileK * 2;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return done != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long start = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - start > 4000000000LL) return false;
-    }
-    return true;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::
-                     "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
-                 : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tmem_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tmem_load16(uint32_t addr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(addr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-}
-
-// Shared-memory descriptor of a K-major tile stored as rows of 128 bytes with the 128-byte
-// swizzle (what TMA writes): start address / 16 in bits 0-13, leading offset (unused for
-// swizzled K-major, set to 1) in bits 16-29, stride between groups of 8 rows = 1024 bytes
-// (/16 = 64) in bits 32-45, descriptor version 1 in bits 46-47, layout 2 (128-byte
-// swizzle) in bits 61-63.
-__device__ __forceinline__ uint64_t smem_descriptor(uint32_t addr) {
-    const uint64_t lo = ((addr >> 4) & 0x3FFFu) | (1u << 16);
-    const uint64_t hi = 64u | (1u << 14) | (2u << 29);
-    return lo | (hi << 32);
-}
-
-// Instruction descriptor: float32 accumulator (bits 4-5 = 1), bfloat16 A and B (bits 7-9 and
-// 10-12 = 1), both K-major (bits 15, 16 = 0), N / 8 in bits 17-22, M / 16 in bits 24-28.
-__host__ __device__ constexpr uint32_t instruction_descriptor(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kTileP >> 4) << 24);
-}
 
 template <int BN>
 struct Shape {
@@ -146,14 +75,9 @@ __global__ void __launch_bounds__(kThreads) gemm_tcgen05_kernel(const __grid_con
             mbar_init(acc_full_bar(a), 1);
             mbar_init(acc_empty_bar(a), 4);
         }
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        mbar_init_done();
     }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_slot)),
-                     "r"(S::kTmemColumns));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
-    }
+    if (warp == 1) tmem_alloc(&tmem_base_slot, S::kTmemColumns);
     tmem_fence_before();
     __syncthreads();
     tmem_fence_after();
@@ -310,28 +234,12 @@ __global__ void __launch_bounds__(kThreads) gemm_tcgen05_kernel(const __grid_con
             // Give work that may still be in flight time to finish before the memory goes back.
             for (int i = 0; i < 100; ++i) __nanosleep(1000);
         }
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(S::kTmemColumns));
+        tmem_free(tmem_base, S::kTmemColumns);
     }
     if (fault && threadIdx.x == 0 && status) atomicOr(status, MLR_STATUS_TIMEOUT);
 }
 
 // ---------------------------------------------------------------- host side
-using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_tiled() {
-    static EncodeTiled fn = nullptr;
-    if (fn == nullptr) {
-        void* found = nullptr;
-        cudaDriverEntryPointQueryResult result;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &found, cudaEnableDefault, &result) == cudaSuccess &&
-            result == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiled>(found);
-    }
-    return fn;
-}
-
 // A map over a row-major bf16 matrix [rows, cols] (row stride ld elements) that loads boxes
 // of `box_rows` x 64 with the 128-byte swizzle; what lies outside the matrix reads as zero.
 int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {

@@ -39,6 +39,7 @@ class Runtime:
         torch.backends.cudnn.allow_tf32 = False
         self.use_tcgen05 = True       # bf16 products on the package's tcgen05/TMA kernel
         self.tcgen05_prefill = False  # ... also for prompt portions (else the vendor library takes those)
+        self.tcgen05_attention = True  # prompt portions of 65 rows and more on the tcgen05 attention kernel
         self.decode_rows = 64         # up to this many rows a product streams the weights (swapped operands, split K)
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self._splits = {}

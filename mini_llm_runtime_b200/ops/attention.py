@@ -3,8 +3,11 @@
 float32: the generic kernel (one block per row and head; any head size up to 256).
 bfloat16, head size a multiple of 16: the tensor-core kernels.  Segments that bring
 at most 16 rows per kv head (a decoded token, a portion of two or three tokens) go
-to the split-KV kernel, the rest are cut into 64-row tiles for the flash kernel; a
-mixed step launches both.  Other head sizes in bfloat16 use the generic kernel.
+to the split-KV kernel; the rest are prompt portions and go to the flash kernels: with
+head size 64 or 128 (and a page size the kernel takes) in 128-row tiles to the tcgen05
+kernel, a remainder of up to 64 rows and everything else in 64-row tiles to the mma.sync
+kernel.  A mixed step launches all of them.  Other head sizes in bfloat16 use the generic
+kernel.
 
 The plan (which segments go where, how the keys are split) depends only on the
 step's segments and on the head grouping, so it is made once per step and reused by
@@ -19,6 +22,7 @@ import torch
 from . import functions as F
 
 _TILE = 64
+_WIDE_TILE = 128
 _MIN_CHUNK = 128
 
 
@@ -28,7 +32,7 @@ def tensor_core_ok(head_dim: int) -> bool:
 
 def modules_for(dtype: torch.dtype, head_dim: int) -> List[str]:
     if dtype is torch.bfloat16 and tensor_core_ok(head_dim):
-        return ["attention_bf16"]
+        return ["attention_bf16", "attention_tcgen05"] if head_dim in (64, 128) else ["attention_bf16"]
     return ["attention_generic"]
 
 
@@ -61,8 +65,8 @@ class _Plan:
     pass
 
 
-def _plan(step, group: int, kv_heads: int, window: int) -> _Plan:
-    key = ("attention_plan", group, kv_heads, window)
+def _plan(step, group: int, kv_heads: int, window: int, wide: bool) -> _Plan:
+    key = ("attention_plan", group, kv_heads, window, wide)
     plan = step.scratch.get(key)
     if plan is not None:
         return plan
@@ -73,6 +77,7 @@ def _plan(step, group: int, kv_heads: int, window: int) -> _Plan:
     plan.n_items = len(small)
     plan.items = None
     plan.tiles = None
+    plan.wide_tiles = None
     if small:
         if len(small) != len(step.segments):
             plan.items = torch.tensor(small, dtype=torch.int32).to(device)
@@ -86,9 +91,20 @@ def _plan(step, group: int, kv_heads: int, window: int) -> _Plan:
                 spans.append(min(step.context_bound, window + s.count + _TILE) if window else step.context_bound)
         plan.chunk, plan.max_splits = split_plan(spans, len(small) * kv_heads)
     if large:
-        tiles = [(i, t) for i in large for t in range(0, step.segments[i].count, _TILE)]
-        tiles.sort(key=lambda it: -(step.segments[it[0]].start + it[1]))      # longest key walks first
-        plan.tiles = torch.tensor(tiles, dtype=torch.int32).to(device)
+        tiles, wide_tiles = [], []
+        for i in large:
+            count = step.segments[i].count
+            # 128-row tiles while more than 64 rows are left, then one 64-row tile for the rest.
+            cut = 0
+            while wide and count - cut > _TILE:
+                wide_tiles.append((i, cut))
+                cut += _WIDE_TILE
+            tiles.extend((i, t) for t in range(cut, count, _TILE))
+        longest_first = lambda it: -(step.segments[it[0]].start + it[1])      # longest key walks first
+        if tiles:
+            plan.tiles = torch.tensor(sorted(tiles, key=longest_first), dtype=torch.int32).to(device)
+        if wide_tiles:
+            plan.wide_tiles = torch.tensor(sorted(wide_tiles, key=longest_first), dtype=torch.int32).to(device)
     step.scratch[key] = plan
     return plan
 
@@ -100,7 +116,8 @@ def paged_attention(qkv, out, cache, table, step, q_heads, kv_heads, head_dim, w
         F.attention_generic(qkv, out, cache, step.positions, step.segment_of_row, table, step.page_size,
                             q_heads, kv_heads, head_dim, window, scale, step.status)
         return
-    plan = _plan(step, q_heads // kv_heads, kv_heads, window)
+    wide = getattr(step.rt, "tcgen05_attention", True) and F.attention_prefill_tcgen05_applies(qkv, out, head_dim, step.page_size)
+    plan = _plan(step, q_heads // kv_heads, kv_heads, window, wide)
     if plan.n_items:
         partial = None
         if plan.max_splits > 1:
@@ -112,6 +129,9 @@ def paged_attention(qkv, out, cache, table, step, q_heads, kv_heads, head_dim, w
         F.attention_decode_bf16(qkv, out, cache, plan.items, plan.n_items, step.segment_info, table, step.page_size,
                                 q_heads, kv_heads, head_dim, window, scale, plan.chunk, plan.max_splits, partial,
                                 step.status, counters=step.rt.split_counters(plan.n_items * kv_heads))
+    if plan.wide_tiles is not None:
+        F.attention_prefill_tcgen05(qkv, out, cache, plan.wide_tiles, step.segment_info, table, step.page_size, q_heads,
+                                    kv_heads, head_dim, window, scale, step.status)
     if plan.tiles is not None:
         F.attention_prefill_bf16(qkv, out, cache, plan.tiles, step.segment_info, table, step.page_size, q_heads,
                                  kv_heads, head_dim, window, scale, step.status)

@@ -198,6 +198,32 @@ def attention_prefill_bf16(q: torch.Tensor, out: torch.Tensor, cache: torch.Tens
          page_size, q_heads, kv_heads, head_dim, int(window), float(scale), ptr(status), stream())
 
 
+def attention_prefill_tcgen05_applies(q: torch.Tensor, out: torch.Tensor, head_dim: int, page_size: int) -> bool:
+    """Whether the tcgen05 prompt-attention kernel takes these tensors (head size 64 or 128,
+    a page size that divides 64 or is a multiple of it, 16-byte aligned rows)."""
+    return (head_dim in (64, 128) and page_size % 8 == 0 and 8 <= page_size <= 256
+            and (64 % page_size == 0 or page_size % 64 == 0)
+            and q.dtype is torch.bfloat16 and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0
+            and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
+
+
+def attention_prefill_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, tiles: torch.Tensor,
+                              segment_info: torch.Tensor, block_table: torch.Tensor, page_size: int, q_heads: int,
+                              kv_heads: int, head_dim: int, window: int, scale: float, status: torch.Tensor) -> None:
+    """Flash attention for prompt portions on the tcgen05 tensor cores.  `tiles` is int32
+    [n, 2]: segment index and first token of each 128-row tile."""
+    on_gpu(q, out, cache, tiles, segment_info, block_table, status)
+    for t in (q, out, cache):
+        if t.dtype is not torch.bfloat16:
+            raise KernelError("attention_prefill_tcgen05 takes bfloat16 tensors")
+    if q.stride(1) != 1 or out.stride(1) != 1 or not cache.is_contiguous():
+        raise KernelError("attention: inner strides must be 1 and the cache contiguous")
+    expect(tiles, torch.int32, "the tile list")
+    call("attention_tcgen05", "mlr_attention_prefill_tcgen05", ptr(q), q.stride(0), q.shape[0], ptr(out), out.stride(0),
+         ptr(cache), cache.shape[0], ptr(tiles), tiles.shape[0], ptr(segment_info), ptr(block_table),
+         block_table.stride(0), page_size, q_heads, kv_heads, head_dim, int(window), float(scale), ptr(status), stream())
+
+
 def gemm_tcgen05_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
     return (x.dtype is torch.bfloat16 and w.dtype is torch.bfloat16 and x.shape[1] % 8 == 0 and x.shape[1] >= 8
             and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0

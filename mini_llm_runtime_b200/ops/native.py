@@ -49,6 +49,12 @@ _SIGNATURES = {
         "mlr_attention_prefill_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
                                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     },
+    "attention_tcgen05": {
+        "mlr_attention_prefill_tcgen05": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
+                                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                          c_void_p, c_void_p],
+        "mlr_attention_prefill_tcgen05_supports": [c_int, c_int],
+    },
     "gemm_bf16_tcgen05": {
         "mlr_gemm_bf16_tcgen05": [c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong,
                                   c_int, c_int, c_int, c_int, c_longlong, c_int, c_void_p, c_void_p],

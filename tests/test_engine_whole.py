@@ -8,7 +8,7 @@ from helpers import assert_close, engine_model, random_tokens, run_portions, run
 
 pytestmark = pytest.mark.gpu
 
-CASES = [("tiny_a", 0, 100), ("tiny_b", 1, 150), ("tiny_c", 2, 200)]
+CASES = [("tiny_a", 0, 100), ("tiny_b", 1, 150), ("tiny_c", 2, 200), ("tiny_d", 3, 333)]
 
 
 @pytest.fixture(scope="module", params=CASES, ids=[c[0] for c in CASES])

@@ -307,7 +307,7 @@ def test_attention_generic(case, dtype):
     run_attention_case(dtype, generic_kernel, case, seed=10)
 
 
-def tensor_core_kernels(chunk=None):
+def tensor_core_kernels(chunk=None, tcgen05=False):
     shared = {}     # one set of split counters for all calls: each call leaves them zero
 
     def kernel(qkv, out, cache, table, positions, seg_of_row, info, segs, page, Hq, Hkv, D, window, scale, st):
@@ -329,7 +329,11 @@ def tensor_core_kernels(chunk=None):
             F().attention_decode_bf16(qkv, out, cache, items, len(small), info, table, page, Hq, Hkv, D, window, scale,
                                       ck, splits, partial, st, counters=counters)
             assert int(counters.abs().sum()) == 0, "the split counters were not left at zero"
-        if large:
+        if large and tcgen05:
+            assert F().attention_prefill_tcgen05_applies(qkv, out, D, page)
+            tiles = torch.tensor([(i, t) for i in large for t in range(0, segs[i][1], 128)], dtype=torch.int32, device=DEV)
+            F().attention_prefill_tcgen05(qkv, out, cache, tiles, info, table, page, Hq, Hkv, D, window, scale, st)
+        elif large:
             tiles = torch.tensor([(i, t) for i in large for t in range(0, segs[i][1], 64)], dtype=torch.int32, device=DEV)
             F().attention_prefill_bf16(qkv, out, cache, tiles, info, table, page, Hq, Hkv, D, window, scale, st)
     return kernel
@@ -341,6 +345,25 @@ def test_attention_tensor_core_kernels(case, chunk):
     if case[2] % 16:
         pytest.skip("head size is no multiple of 16")
     run_attention_case(torch.bfloat16, tensor_core_kernels(chunk), case, seed=20)
+
+
+TCGEN05_CASES = [
+    # Hq, Hkv, D, page, [(context before, new tokens)], window
+    (32, 8, 128, 16, [(0, 129), (1536, 64), (63, 2)], 0),
+    (16, 8, 128, 64, [(300, 200), (5, 1)], 128),
+    (4, 4, 128, 16, [(0, 128)], 0),
+    (4, 2, 128, 16, [(0, 64)], 0),
+    (6, 2, 64, 8, [(0, 300), (77, 131), (1000, 17)], 0),
+    (3, 1, 64, 32, [(130, 270), (0, 5)], 90),
+    (8, 2, 128, 128, [(250, 390)], 0),
+    (2, 1, 128, 256, [(1000, 700)], 300),
+    (10, 5, 64, 16, [(0, 1), (31, 33), (640, 128)], 64),
+]
+
+
+@pytest.mark.parametrize("case", TCGEN05_CASES, ids=[f"case{i}" for i in range(len(TCGEN05_CASES))])
+def test_attention_prefill_tcgen05(case):
+    run_attention_case(torch.bfloat16, tensor_core_kernels(128, tcgen05=True), case, seed=30)
 
 
 def test_tensor_core_kernels_refuse_what_they_cannot_do():
@@ -412,6 +435,49 @@ def test_window_edge_is_exact(dtype, kernel):
         kernel(qkv, out, cache, table, positions, seg_of_row, info, [(before, 1)], page, Hq, Hkv, D, window, 1.0, status())
         tol = 1e-4 if dtype is torch.float32 else 3e-2
         assert torch.allclose(out.float().cpu().reshape(1, Hq, D).double(), want, atol=tol, rtol=tol), before
+
+
+@pytest.mark.parametrize("page,window", [(16, 0), (64, 0), (8, 1500), (128, 2100)])
+def test_prefill_tcgen05_far_keys_and_window_edges(page, window):
+    """A portion of 200 tokens after 3000 others.  Some rows look for one far key each (the
+    output must be that key's value: a skipped or repeated tile would show); with a window,
+    other rows have a key just outside it that would dominate if it were read."""
+    Hq, Hkv, D, before, count = 4, 2, 128, 3000, 200
+    T = before + count
+    dtype = torch.bfloat16
+    k = torch.randn(T, Hkv, D, generator=gen(0)) * 0.1
+    v = torch.randn(T, Hkv, D, generator=gen(1))
+    q = torch.randn(count, Hq, D, generator=gen(2)) * 0.01
+    basis = torch.linalg.qr(torch.randn(D, D, generator=gen(3)))[0]
+    lowest = before - window + 1 if window else 0           # first key row 0 may read
+    targets = {0: lowest, 77: lowest + 77 + 63, 130: before + 64, 199: before + 199, 128: 2048 + 15}
+    for n, (row, key) in enumerate(targets.items()):
+        k[key] = basis[n] * 40
+        q[row] = basis[n] * 40
+    hidden = {}
+    if window:
+        for n, row in enumerate((5, 64, 127, 190)):
+            key = before + row - window                     # just outside this row's window
+            k[key] = basis[10 + n] * 40
+            v[key] = 1000.0
+            q[row] = basis[10 + n] * 40
+            hidden[row] = key
+    want = fast_plain_attention(q, k, v, before, window, 1.0)
+    for row, key in targets.items():
+        assert torch.allclose(want[row].float(), v[key].repeat_interleave(Hq // Hkv, 0), atol=1e-3)
+    assert want.abs().max() < 100
+    cache, table = make_cache([(k, v)], page, dtype, seed=page)
+    positions, seg_of_row, info = segments_meta([(before, count)])
+    qkv = torch.zeros(count, (Hq + 2 * Hkv) * D, dtype=dtype, device=DEV)
+    qkv[:, :Hq * D] = q.reshape(count, -1).to(dtype).to(DEV)
+    out = torch.zeros(count, Hq * D, dtype=dtype, device=DEV)
+    st = status()
+    tensor_core_kernels(128, tcgen05=True)(qkv, out, cache, table, positions, seg_of_row, info, [(before, count)], page,
+                                           Hq, Hkv, D, window, 1.0, st)
+    assert int(st.item()) == 0
+    got = out.float().cpu().reshape(count, Hq, D)
+    assert torch.isfinite(got).all()
+    assert torch.allclose(got.double(), want, atol=3e-2, rtol=3e-2), f"max diff {(got.double() - want).abs().max():.3e}"
 
 
 # ------------------------------------------------------------------ q/k norm, rotation, cache write

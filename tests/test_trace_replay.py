@@ -12,7 +12,8 @@ from helpers import assert_close, random_tokens, tiny_folder
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"tiny_a": [100, 37, 128, 65, 80, 51], "tiny_b": [150, 33, 97, 256, 64, 70], "tiny_c": [200, 41, 130, 75, 300, 66]}
+LENGTHS = {"tiny_a": [100, 37, 128, 65, 80, 51], "tiny_b": [150, 33, 97, 256, 64, 70], "tiny_c": [200, 41, 130, 75, 300, 66],
+           "tiny_d": [330, 70, 200, 129, 262, 90]}
 MODES = {"whole": T.whole, "last32": T.last_32_one_by_one, "portions": T.portions,
          "mixed": lambda r: T.mixed(r, seed=11)}
 

@@ -74,7 +74,31 @@ TINY_C = {
     "torch_dtype": "bfloat16",
 }
 
-ALL = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C}
+# Head size 64, which in bfloat16 takes prompt portions through the tcgen05 attention
+# kernel: three query heads per kv head, a window on the second layer only.
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "model_type": "qwen3",
+    "hidden_size": 112,
+    "num_hidden_layers": 2,
+    "num_attention_heads": 6,
+    "num_key_value_heads": 2,
+    "head_dim": 64,
+    "intermediate_size": 144,
+    "vocab_size": 300,
+    "max_position_embeddings": 2048,
+    "rms_norm_eps": 2e-6,
+    "rope_theta": 20000.0,
+    "tie_word_embeddings": True,
+    "use_sliding_window": True,
+    "sliding_window": 150,
+    "max_window_layers": 1,
+    "hidden_act": "silu",
+    "attention_bias": False,
+    "torch_dtype": "bfloat16",
+}
+
+ALL = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_d": TINY_D}
 
 
 def get(name: str) -> dict:
