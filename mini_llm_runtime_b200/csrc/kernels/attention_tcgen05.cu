@@ -59,6 +59,28 @@ __device__ __forceinline__ float exp2_raw(float x) {
     return y;
 }
 
+// Two float32 operations in one instruction (sm_100a), and the maximum of three.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;\n"
+        : "=l"(d)
+        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)),
+          "l"(*reinterpret_cast<unsigned long long*>(&c)));
+    return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;\n"
+        : "=l"(d)
+        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+    return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 template <int D>
 __global__ void __launch_bounds__(kThreads, 2) prefill_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
@@ -243,7 +265,8 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tcgen05_kernel(
             }
             float part_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four short chains, not one long
 #pragma unroll
-            for (int c = 0; c < 64; ++c) part_max[c & 3] = fmaxf(part_max[c & 3], __uint_as_float(raw[c]));
+            for (int c = 0; c < 64; c += 2)
+                part_max[(c >> 1) & 3] = max3(part_max[(c >> 1) & 3], __uint_as_float(raw[c]), __uint_as_float(raw[c + 1]));
             const float tile_max = fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3]));
             const float m_tile = tile_max * scale_log2;      // scale_log2 > 0
             const bool grow = m_tile > m_ref + kRescaleStep || (m_ref == -INFINITY && m_tile > -INFINITY);
@@ -270,15 +293,17 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tcgen05_kernel(
             }
             const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
             uint32_t p[32];
-            float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            float2 sum[4] = {{0.0f, 0.0f}, {0.0f, 0.0f}, {0.0f, 0.0f}, {0.0f, 0.0f}};
+            const float2 scale2 = make_float2(scale_log2, scale_log2), shift2 = make_float2(-m_use, -m_use);
 #pragma unroll
             for (int c = 0; c < 64; c += 2) {
-                const float e0 = exp2_raw(fmaf(__uint_as_float(raw[c]), scale_log2, -m_use));
-                const float e1 = exp2_raw(fmaf(__uint_as_float(raw[c + 1]), scale_log2, -m_use));
-                sum[(c >> 1) & 3] += e0 + e1;
-                p[c >> 1] = pack_bf16(e0, e1);
+                const float2 x = fma2(make_float2(__uint_as_float(raw[c]), __uint_as_float(raw[c + 1])), scale2, shift2);
+                const float2 e = make_float2(exp2_raw(x.x), exp2_raw(x.y));
+                sum[(c >> 1) & 3] = add2(sum[(c >> 1) & 3], e);
+                p[c >> 1] = pack_bf16(e.x, e.y);
             }
-            l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+            const float2 total = add2(add2(sum[0], sum[1]), add2(sum[2], sum[3]));
+            l += total.x + total.y;
             tmem_store32(tmem_s(b) + lane_base, p);
             // Rows of V that hold no key this block may read become zero.
             const int tile_end = key0 + kKeys;
@@ -300,6 +325,10 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tcgen05_kernel(
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(kPFull, b));
         }
+        // A wait by parity can tell a phase only from the one before it.  The scores of the last
+        // tile were issued after P V of tile n-3, so that one is done; P V of tile n-2 may not
+        // be (its V tile may have come late), so its phase is waited for first.
+        if (ok && n_tiles >= 2) ok = __all_sync(0xffffffffu, wait(bar(kODone), (n_tiles - 2) & 1));
         if (ok) ok = __all_sync(0xffffffffu, wait(bar(kODone), (n_tiles - 1) & 1));
         if (ok) {
             tmem_fence_after();

@@ -332,6 +332,8 @@ def tensor_core_kernels(chunk=None, tcgen05=False):
         if large and tcgen05:
             assert F().attention_prefill_tcgen05_applies(qkv, out, D, page)
             tiles = torch.tensor([(i, t) for i in large for t in range(0, segs[i][1], 128)], dtype=torch.int32, device=DEV)
+            # Cold caches: the tiles then arrive late and in another order, which a missing wait would show.
+            torch.empty(64 << 20, dtype=torch.int32, device=DEV).zero_()
             F().attention_prefill_tcgen05(qkv, out, cache, tiles, info, table, page, Hq, Hkv, D, window, scale, st)
         elif large:
             tiles = torch.tensor([(i, t) for i in large for t in range(0, segs[i][1], 64)], dtype=torch.int32, device=DEV)
