@@ -149,45 +149,58 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tcgen05_kernel(
             for (int h = 0; h < kHalves; ++h)
                 tma_load_2d(q_tile + h * kQHalfBytes, &map_q, head * D + h * 64, first_row + tile_token, bar(kQFull));
         }
+        // Page sizes are powers of two here (the host checks it).  Lane c copies rows
+        // [sub * rows_per_copy, ..) of half c % kHalves of a tile, if any key of those rows is
+        // one this block may read.
+        const int page_shift = 31 - __clz(page_size);
         const int rows_per_copy = min(page_size, kKeys);
         const int copies = (kKeys / rows_per_copy) * kHalves;
+        const int sub = lane / kHalves, half = lane % kHalves;
         const int* table = block_table + static_cast<size_t>(segment) * table_stride;
-        // The K (value = 0) or V (value = 1) tile `j`: lane c copies rows [sub * rows_per_copy, ..)
-        // of half c % kHalves, if any key of those rows is one this block may read.
-        auto issue = [&](int j, int value) {
-            const int stage = j & 1;
+        constexpr int kNotMine = -2;
+        // The page this lane copies from in tile j.  Looked up two tiles ahead, so that the
+        // table read is off the path between a stage becoming free and its next copy.
+        auto lookup = [&](int j) {
             const int tile_start = key_begin + j * kKeys;
             const int from = max(tile_start, first_key), to = min(tile_start + kKeys, key_end);
-            const int sub = lane / kHalves, half = lane % kHalves;
             const int row0 = tile_start + sub * rows_per_copy;
-            const bool mine = lane < copies && row0 < to && row0 + rows_per_copy > from;
+            if (j >= n_tiles || lane >= copies || row0 >= to || row0 + rows_per_copy <= from) return kNotMine;
+            return __ldg(table + (row0 >> page_shift));
+        };
+        // The K (value = 0) or V (value = 1) tile j.
+        auto issue = [&](int j, int value, int page) {
+            const int stage = j & 1;
+            const bool mine = page != kNotMine;
             const unsigned mask = __ballot_sync(0xffffffffu, mine);
             const uint32_t full = bar(value ? kVFull : kKFull, stage);
             if (lane == 0) mbar_expect_tx(full, __popc(mask) * rows_per_copy * kHalfBytesPerRow);
             __syncwarp();
             if (mine) {
-                const int block = row0 / page_size, in_page = row0 - block * page_size;
-                int page = __ldg(table + block);
                 if (page < 0 || page >= num_pages) {
                     bad_page = 1;
                     page = 0;      // still copy something so that the tile's byte count is met
                 }
+                const int in_page = (key_begin + j * kKeys + sub * rows_per_copy) & (page_size - 1);
                 const uint32_t dst = (value ? v_tile(stage) : k_tile(stage)) + half * kKvHalfBytes +
                                      sub * rows_per_copy * kHalfBytesPerRow;
                 tma_load_3d(dst, &map_kv, half * 64, in_page, (page * 2 + value) * kv_heads + kv_head, full);
             }
         };
+        int page_now = lookup(0), page_next = lookup(1);
         bool ok = true;
-        issue(0, 0);
+        issue(0, 0, page_now);
         for (int j = 0; j < n_tiles && ok; ++j) {
             if (j + 1 < n_tiles) {
                 if (j + 1 >= 2) ok = wait(bar(kKEmpty, (j + 1) & 1), (((j + 1) >> 1) - 1) & 1);
                 if (!ok) break;
-                issue(j + 1, 0);
+                issue(j + 1, 0, page_next);
             }
+            const int page_after = lookup(j + 2);
             if (j >= 2) ok = wait(bar(kVEmpty, j & 1), ((j >> 1) - 1) & 1);
             if (!ok) break;
-            issue(j, 1);
+            issue(j, 1, page_now);
+            page_now = page_next;
+            page_next = page_after;
         }
     } else if (warp == 5) {
         // ---------------- tensor-core instructions
@@ -270,6 +283,10 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tcgen05_kernel(
             const float tile_max = fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3]));
             const float m_tile = tile_max * scale_log2;      // scale_log2 > 0
             const bool grow = m_tile > m_ref + kRescaleStep || (m_ref == -INFINITY && m_tile > -INFINITY);
+            // P V of tile j-1 is waited for once per tile, in order: a wait by parity can tell a
+            // phase only from the one before it.  Here if O must be rescaled, else before the
+            // probabilities are handed over, when it has long been done.
+            bool o_seen = j == 0;
             if (__any_sync(0xffffffffu, grow)) {
                 const float m_new = grow ? m_tile : m_ref;
                 const float alpha = grow ? exp2_raw(m_ref - m_new) : 1.0f;       // 0 for a row's first keys
@@ -279,6 +296,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tcgen05_kernel(
                     // O holds the sums up to tile j-1 once that tile's P V is done.
                     ok = __all_sync(0xffffffffu, wait(bar(kODone), (j - 1) & 1));
                     if (!ok) break;
+                    o_seen = true;
                     tmem_fence_after();
 #pragma unroll
                     for (int c = 0; c < D; c += 32) {
@@ -320,15 +338,15 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tcgen05_kernel(
                 }
                 fence_async_proxy();
             }
+            if (!o_seen) {
+                ok = __all_sync(0xffffffffu, wait(bar(kODone), (j - 1) & 1));
+                if (!ok) break;
+            }
             tmem_store_wait();
             tmem_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(kPFull, b));
         }
-        // A wait by parity can tell a phase only from the one before it.  The scores of the last
-        // tile were issued after P V of tile n-3, so that one is done; P V of tile n-2 may not
-        // be (its V tile may have come late), so its phase is waited for first.
-        if (ok && n_tiles >= 2) ok = __all_sync(0xffffffffu, wait(bar(kODone), (n_tiles - 2) & 1));
         if (ok) ok = __all_sync(0xffffffffu, wait(bar(kODone), (n_tiles - 1) & 1));
         if (ok) {
             tmem_fence_after();
@@ -391,8 +409,7 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, void* out, int l
 
 // Whether mlr_attention_prefill_tcgen05 takes this head size and page size.
 MLR_API int mlr_attention_prefill_tcgen05_supports(int head_dim, int page_size) {
-    return (head_dim == 64 || head_dim == 128) && page_size >= 8 && page_size % 8 == 0 &&
-           (kKeys % page_size == 0 || page_size % kKeys == 0) && page_size <= 256;
+    return (head_dim == 64 || head_dim == 128) && page_size >= 8 && page_size <= 256 && (page_size & (page_size - 1)) == 0;
 }
 
 // q: [q_rows, ldq] bfloat16 with the query heads in the first q_heads * head_dim columns;
@@ -405,7 +422,7 @@ MLR_API int mlr_attention_prefill_tcgen05(const void* q, int ldq, int q_rows, vo
                                           float scale, int* status, cudaStream_t stream) {
     MLR_REQUIRE(mlr_attention_prefill_tcgen05_supports(head_dim, page_size),
                 "attention_prefill_tcgen05: head size %d with pages of %d tokens is not supported (head size 64 or 128; "
-                "a page size that divides 64 or is a multiple of it, at most 256)", head_dim, page_size);
+                "a page size that is a power of two from 8 to 256)", head_dim, page_size);
     MLR_REQUIRE(q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0, "attention_prefill_tcgen05: %d query heads over %d kv heads",
                 q_heads, kv_heads);
     MLR_REQUIRE(num_pages > 0 && window >= 0 && scale > 0.0f && q_rows > 0, "attention_prefill_tcgen05: bad sizes");

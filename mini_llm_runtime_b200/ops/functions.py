@@ -200,9 +200,8 @@ def attention_prefill_bf16(q: torch.Tensor, out: torch.Tensor, cache: torch.Tens
 
 def attention_prefill_tcgen05_applies(q: torch.Tensor, out: torch.Tensor, head_dim: int, page_size: int) -> bool:
     """Whether the tcgen05 prompt-attention kernel takes these tensors (head size 64 or 128,
-    a page size that divides 64 or is a multiple of it, 16-byte aligned rows)."""
-    return (head_dim in (64, 128) and page_size % 8 == 0 and 8 <= page_size <= 256
-            and (64 % page_size == 0 or page_size % 64 == 0)
+    a page size that is a power of two from 8 to 256, 16-byte aligned rows)."""
+    return (head_dim in (64, 128) and 8 <= page_size <= 256 and page_size & (page_size - 1) == 0
             and q.dtype is torch.bfloat16 and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0
             and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
 
