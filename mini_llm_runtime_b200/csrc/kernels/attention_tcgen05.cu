@@ -208,19 +208,25 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tcgen05_kernel(
             constexpr uint32_t idesc_s = instruction_descriptor(kKeys);
             constexpr uint32_t idesc_o = instruction_descriptor(D, true);
             bool ok = wait(bar(kQFull), 0);
+            // Descriptors of the tiles, made once: an instruction adds a constant to them.
             const uint64_t desc_q = smem_descriptor(q_tile);
+            const uint64_t desc_k[2] = {smem_descriptor(k_tile(0)), smem_descriptor(k_tile(1))};
+            const uint64_t desc_v[2] = {smem_descriptor(v_tile(0), kKvHalfBytes, 1024), smem_descriptor(v_tile(1), kKvHalfBytes, 1024)};
             // S_j = Q K_j^T: per half of the head four steps of 16 along it (32 bytes = 2 units).
             auto issue_s = [&](int j) {
                 const int stage = j & 1;
                 if (!wait(bar(kKFull, stage), (j >> 1) & 1)) return false;
                 tmem_fence_after();
-                const uint64_t desc_k = smem_descriptor(k_tile(stage));
+                const uint32_t tmem_d = tmem_s(stage);
+                const uint64_t dk = desc_k[stage];
 #pragma unroll
                 for (int h = 0; h < kHalves; ++h)
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        umma_bf16(tmem_s(stage), desc_q + h * (kQHalfBytes >> 4) + 2 * k, desc_k + h * (kKvHalfBytes >> 4) + 2 * k,
-                                  idesc_s, h > 0 || k > 0);
+                    for (int k = 0; k < 4; ++k) {
+                        const uint64_t da = desc_q + (h * (kQHalfBytes >> 4) + 2 * k), db = dk + (h * (kKvHalfBytes >> 4) + 2 * k);
+                        if (h == 0 && k == 0) umma_bf16(tmem_d, da, db, idesc_s, 0u);
+                        else umma_bf16(tmem_d, da, db, idesc_s, 1u);
+                    }
                 umma_commit(bar(kKEmpty, stage));
                 umma_commit(bar(kSFull, stage));
                 return true;
@@ -235,15 +241,16 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tcgen05_kernel(
                 tmem_fence_after();
                 // O += P_j V_j: four steps of 16 keys (16 rows of 128 bytes further into V); P holds
                 // two probabilities per column, so a step is 8 columns.
+                const uint32_t tmem_p = tmem_s(stage);
+                const uint64_t dv = desc_v[stage];
+                umma_bf16_tmem_a(tmem_o, tmem_p, dv, idesc_o, j > 0);
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    umma_bf16_tmem_a(tmem_o, tmem_s(stage) + 8 * k,
-                                     smem_descriptor(v_tile(stage) + k * 16 * kHalfBytesPerRow, kKvHalfBytes, 1024), idesc_o,
-                                     j > 0 || k > 0);
+                for (int k = 1; k < 4; ++k)
+                    umma_bf16_tmem_a(tmem_o, tmem_p + 8 * k, dv + k * ((16 * kHalfBytesPerRow) >> 4), idesc_o, 1u);
                 umma_commit(bar(kVEmpty, stage));
                 umma_commit(bar(kODone));
             }
-            }
+        }
     } else {
         // ---------------- softmax: thread = query row
         const int row = warp * 32 + lane;
