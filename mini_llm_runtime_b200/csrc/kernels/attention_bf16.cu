@@ -287,7 +287,9 @@ __device__ __forceinline__ SplitPlan plan_splits(int start, int count, int windo
 // of V per page block the tile touches, byte for byte into an unpadded tile; rows of V
 // outside [first_valid, key_end) are zeroed (their scores are masked, but 0 * garbage must
 // stay 0).  Otherwise: one copy per key row into a padded tile; a key outside the range
-// copies the nearest key inside it.  Returns false if a wait ran out.
+// copies the nearest key inside it.  The block table and the keys below `fresh_from` must
+// not be written by any kernel in flight: they are read before the wait for the preceding
+// kernel (programmatic dependent launch).  Returns false if a wait ran out.
 struct StageRing {
     uint32_t smem_base, bar_base;
     unsigned char* smem;
@@ -301,7 +303,7 @@ struct StageRing {
 template <int DMAX, bool BLOCKS>
 __device__ __forceinline__ bool copy_warp(const StageRing& ring, const __nv_bfloat16* __restrict__ cache, const int* __restrict__ table,
                                           int num_pages, int page_size, int kv_heads, int head_dim, int kv_head, int key_begin,
-                                          int key_end, int first_valid, int tiles, int* fault) {
+                                          int key_end, int first_valid, int tiles, int fresh_from, int* fault) {
     using L = typename std::conditional<BLOCKS, Tile<DMAX>, PaddedTile<DMAX>>::type;
     const int lane = threadIdx.x & 31;
     const int page_shift = log2_or_minus1(page_size);
@@ -319,11 +321,19 @@ __device__ __forceinline__ bool copy_warp(const StageRing& ring, const __nv_bflo
         return (it_ < tiles && block_ <= last_block_) ? __ldg(table + block_) : -1;
     };
     int ahead = BLOCKS ? tile_page(0) : -1;
+    // Keys below `fresh_from` were written by earlier steps; the kernel before this one may
+    // still be writing the others.  So the tiles of old keys are fetched at once, and the
+    // wait for that kernel comes before the first tile that reaches a fresh key.
+    bool waited = false;
     for (int it = 0; it < tiles && ok; ++it) {
         const int stage = it % kDecodeStages;
         if (it >= kDecodeStages) ok = mbar_wait(ring.empty_bar(stage), ((it / kDecodeStages) - 1) & 1);
         if (!ok) break;
         const int tile_start = key_begin + it * kTileKeys;
+        if (!waited && min(tile_start + kTileKeys, key_end) > fresh_from) {
+            mlr_grid_wait();
+            waited = true;
+        }
         const int my_page = ahead;
         if (BLOCKS) ahead = tile_page(it + 1);
         if (BLOCKS) {
@@ -418,7 +428,9 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
     int page_size, int q_heads, int kv_heads, int head_dim, int window, float scale, int chunk,
     int max_splits, float* __restrict__ partial, int* __restrict__ counters, int* status) {
     mlr_grid_dependents_may_start();
-    mlr_grid_wait();
+    // The segment table and the block table were uploaded before the step's first kernel;
+    // what the preceding kernel writes (queries, the new keys and values) is read after
+    // mlr_grid_wait() below.
     // BLOCKS: the cache rows are stored swizzled (head size 64, 128 or 256 = DMAX), so whole
     // page blocks are copied byte for byte into unpadded tiles.  Otherwise rows are stored
     // plainly and are copied one by one into padded tiles.
@@ -459,10 +471,11 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
 
     if (warp == 4) {
         if (!copy_warp<DMAX, BLOCKS>(ring, cache, block_table + static_cast<size_t>(segment) * table_stride, num_pages,
-                                     page_size, kv_heads, head_dim, kv_head, key_begin, key_end, first_valid, tiles, &fault))
+                                     page_size, kv_heads, head_dim, kv_head, key_begin, key_end, first_valid, tiles, start, &fault))
             fault = 2;
     } else {
         // ---------------- compute warps
+        mlr_grid_wait();
         const int g = lane >> 2;
         int lo[2], hi[2];
         const __nv_bfloat16* qptr[2];
@@ -547,7 +560,11 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
     __syncthreads();
     const int rows = count * group;
     const bool direct = plan.splits == 1;
-    float* part = partial + ((static_cast<size_t>(item) * kv_heads + kv_head) * max_splits + split) * 16 * (head_dim + 2);
+    // Scratch: for every (request, kv head, split) 16 rows of head_dim sums, and after all of
+    // those 16 (maximum, sum of weights) pairs each.
+    const size_t unit = (static_cast<size_t>(item) * kv_heads + kv_head) * max_splits;
+    float* part = partial + (unit + split) * 16 * head_dim;
+    float* part_ml = partial + static_cast<size_t>(gridDim.z) * kv_heads * max_splits * 16 * head_dim + (unit + split) * 32;
     for (int idx = threadIdx.x; idx < rows * head_dim; idx += kDecodeThreads) {
         const int row = idx / head_dim, d = idx - row * head_dim;
         float m = -INFINITY;
@@ -566,10 +583,10 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
             out[static_cast<size_t>(first_row + token) * ldo + static_cast<size_t>(head) * head_dim + d] =
                 __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
         } else {
-            part[row * (head_dim + 2) + d] = acc;
+            part[row * head_dim + d] = acc;
             if (d == 0) {
-                part[row * (head_dim + 2) + head_dim] = m;
-                part[row * (head_dim + 2) + head_dim + 1] = l;
+                part_ml[row * 2] = m;
+                part_ml[row * 2 + 1] = l;
             }
         }
     }
@@ -589,15 +606,18 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    // The weights exp2(m_split - m) / l are worked out once per (split, row) in shared memory;
-    // the sums over splits then have no dependent loads.  Other SMs wrote the partial
-    // results: they are read from L2, past this SM's L1.
-    float* factor = merge_ml + 4 * 16 * 2;      // [splits][16]
-    const int stride = head_dim + 2;
-    const float* base = partial + (static_cast<size_t>(item) * kv_heads + kv_head) * max_splits * 16 * stride;
+    // The weights exp2(m_split - m) / l are worked out once per (split, row) in shared memory
+    // from maxima and sums that all threads fetch together; the sums over splits then have
+    // no dependent loads and are fetched four values and eight splits at a time.  Other SMs
+    // wrote the partial results: they are read from L2, past this SM's L1.
+    float* factor = merge_ml + 4 * 16 * 2;      // [splits][16]: maxima, then weights
+    float* weight_sum = factor + 16 * max_splits;
+    const float* base = partial + unit * 16 * head_dim;
+    const float* base_ml = part_ml - split * 32;
     for (int i = threadIdx.x; i < plan.splits * 16; i += kDecodeThreads) {
-        const int row = i & 15;
-        factor[i] = row < rows ? __ldcg(base + i * stride + head_dim) : -INFINITY;
+        const float2 ml = (i & 15) < rows ? __ldcg(reinterpret_cast<const float2*>(base_ml) + i) : make_float2(-INFINITY, 0.0f);
+        factor[i] = ml.x;
+        weight_sum[i] = ml.y;
     }
     __syncthreads();
     if (threadIdx.x < rows) {
@@ -608,22 +628,45 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
         for (int s = 0; s < plan.splits; ++s) {
             const float ms = factor[s * 16 + row];
             const float f = ms == -INFINITY ? 0.0f : exp2f(ms - m);
-            l += __ldcg(base + (s * 16 + row) * stride + head_dim + 1) * f;
+            l += weight_sum[s * 16 + row] * f;
             factor[s * 16 + row] = f;
         }
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
         for (int s = 0; s < plan.splits; ++s) factor[s * 16 + row] *= inv;
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < rows * head_dim; idx += kDecodeThreads) {
-        const int row = idx / head_dim, d = idx - row * head_dim;
-        float acc = 0.0f;
-#pragma unroll 4
-        for (int s = 0; s < plan.splits; ++s)
-            acc = fmaf(__ldcg(base + (s * 16 + row) * stride + d), factor[s * 16 + row], acc);
+    const int quads = head_dim >> 2;        // head_dim is a multiple of 16
+    for (int idx = threadIdx.x; idx < rows * quads; idx += kDecodeThreads) {
+        const int row = idx / quads, d = (idx - row * quads) * 4;
+        const float4* src = reinterpret_cast<const float4*>(base + row * head_dim + d);
+        const int split_stride = 4 * head_dim;      // float4 units between splits: 16 rows of head_dim floats
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        int s = 0;
+        for (; s + 8 <= plan.splits; s += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = __ldcg(src + (s + u) * split_stride);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {       // in split order, whatever the batch size
+                const float f = factor[(s + u) * 16 + row];
+                acc.x = fmaf(v[u].x, f, acc.x);
+                acc.y = fmaf(v[u].y, f, acc.y);
+                acc.z = fmaf(v[u].z, f, acc.z);
+                acc.w = fmaf(v[u].w, f, acc.w);
+            }
+        }
+        for (; s < plan.splits; ++s) {
+            const float4 v = __ldcg(src + s * split_stride);
+            const float f = factor[s * 16 + row];
+            acc.x = fmaf(v.x, f, acc.x);
+            acc.y = fmaf(v.y, f, acc.y);
+            acc.z = fmaf(v.z, f, acc.z);
+            acc.w = fmaf(v.w, f, acc.w);
+        }
         const int token = row / group, head = kv_head * group + row % group;
-        out[static_cast<size_t>(first_row + token) * ldo + static_cast<size_t>(head) * head_dim + d] =
-            __float2bfloat16_rn(acc);
+        __nv_bfloat16* dst = out + static_cast<size_t>(first_row + token) * ldo + static_cast<size_t>(head) * head_dim + d;
+        reinterpret_cast<uint32_t*>(dst)[0] = pack_bf16(acc.x, acc.y);      // row strides are even, not more
+        reinterpret_cast<uint32_t*>(dst)[1] = pack_bf16(acc.z, acc.w);
     }
 }
 
@@ -643,7 +686,6 @@ __global__ void __launch_bounds__(kDecodeThreads) __maxnreg__(DMAX <= 128 ? 168 
     const int* __restrict__ segment_info, const int* __restrict__ block_table, int table_stride,
     int page_size, int q_heads, int kv_heads, int head_dim, int window, float scale, int* status) {
     mlr_grid_dependents_may_start();
-    mlr_grid_wait();
     using L = typename std::conditional<BLOCKS, Tile<DMAX>, PaddedTile<DMAX>>::type;
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) unsigned long long barriers[2 * kDecodeStages];
@@ -672,9 +714,10 @@ __global__ void __launch_bounds__(kDecodeThreads) __maxnreg__(DMAX <= 128 ? 168 
     if (warp == 4) {
         if (!copy_warp<DMAX, BLOCKS>(ring, cache, block_table + static_cast<size_t>(segment) * table_stride, num_pages,
                                      page_size, kv_heads, head_dim, kv_head, key_begin, last_pos + 1, max(first_key, key_begin),
-                                     n_tiles, &fault))
+                                     n_tiles, start, &fault))
             fault = 2;
     } else {
+        mlr_grid_wait();
         const int g = lane >> 2, t = lane & 3;
         int lo[2], hi[2];
         const __nv_bfloat16* qptr[2];
@@ -805,12 +848,13 @@ MLR_API int mlr_attention_decode_bf16(const void* q, int ldq, void* out, int ldo
     MLR_REQUIRE(q_heads / kv_heads <= 16, "attention_decode_bf16: %d query heads per kv head exceed the 16 rows of a block", q_heads / kv_heads);
     MLR_REQUIRE(chunk > 0 && chunk % kTileKeys == 0, "attention_decode_bf16: chunk %d is not a positive multiple of %d", chunk, kTileKeys);
     MLR_REQUIRE(max_splits >= 1 && max_splits <= 512 && (max_splits == 1 || (partial && counters)), "attention_decode_bf16: the split count must be in [1, 512], with scratch and counters when above 1");
+    MLR_REQUIRE(reinterpret_cast<uintptr_t>(partial) % 16 == 0, "attention_decode_bf16: the scratch must be 16-byte aligned");
     MLR_REQUIRE(n_items >= 0 && n_items <= 65535, "attention_decode_bf16: more than 65535 requests in one launch");
     if (n_items == 0) return 0;
     const dim3 grid(max_splits, kv_heads, n_items);
 #define MLR_LAUNCH(DMAX, BLOCKS)                                                                                   \
     do {                                                                                                           \
-        const size_t merge = sizeof(float) * (4 * 16 * DMAX + 4 * 16 * 2 + 16 * max_splits);                       \
+        const size_t merge = sizeof(float) * (4 * 16 * DMAX + 4 * 16 * 2 + 32 * max_splits);                       \
         const size_t tile = BLOCKS ? Tile<DMAX>::kBytes : PaddedTile<DMAX>::kBytes;                                \
         const size_t stages = static_cast<size_t>(kDecodeStages) * 2 * tile;                                       \
         const size_t bytes = stages > merge ? stages : merge;                                                      \
