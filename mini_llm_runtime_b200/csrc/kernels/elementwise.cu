@@ -323,6 +323,106 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, int ld, const flo
     }
 }
 
+// The same for prompt portions in bfloat16 with head sizes 64, 128 and 256 and no partial
+// sums: a lane holds 8 elements of each half of a head (two 16-byte loads), D/16 lanes a
+// head, so a warp covers 32 / (D/16) heads of one row and enough bytes are in flight to
+// keep the memory busy.  Same arithmetic, element for element.
+template <typename W, int D>
+__global__ void __launch_bounds__(128) qk_norm_rope_cache_wide_kernel(
+    __nv_bfloat16* __restrict__ qkv, int ld, int rows, int q_heads, int kv_heads, const W* __restrict__ q_weight,
+    const W* __restrict__ k_weight, float eps, const float* __restrict__ cos_sin, int table_positions,
+    const int* __restrict__ positions, const int* __restrict__ segment_of_row, const int* __restrict__ block_table,
+    int table_stride, int page_size, __nv_bfloat16* __restrict__ cache, int num_pages, int write_cache, int* status) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
+    constexpr int kLanes = D / 16, kHeadsPerWarp = 32 / kLanes, kHalf = D / 2;
+    const int lane = threadIdx.x & 31, sub = lane % kLanes;
+    const int row = blockIdx.x;
+    const int head = (blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5)) * kHeadsPerWarp + lane / kLanes;
+    const int heads = q_heads + 2 * kv_heads;
+    const bool is_query = head < q_heads;
+    const bool is_key = !is_query && head < q_heads + kv_heads;
+    const bool is_value = !is_query && !is_key && head < heads;
+    bool active = head < heads && (is_query || write_cache);
+    const int position = positions[row];
+    __nv_bfloat16* x = qkv + static_cast<size_t>(row) * ld + static_cast<size_t>(head) * D;
+    float lo[8] = {}, hi[8] = {};
+    if (active) {
+        mlr_load8(x + 8 * sub, lo);
+        mlr_load8(x + kHalf + 8 * sub, hi);
+    }
+    __nv_bfloat16* dst = nullptr;
+    if (active && !is_query) {
+        const int kv_head = is_key ? head - q_heads : head - q_heads - kv_heads;
+        const int page = block_table[static_cast<size_t>(segment_of_row[row]) * table_stride + position / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (sub == 0 && status) atomicOr(status, MLR_STATUS_BAD_PAGE);
+            active = false;
+        } else {
+            dst = cache + (static_cast<size_t>(page) * 2 * kv_heads + (is_key ? 0 : kv_heads) + kv_head) * page_size * D +
+                  static_cast<size_t>(position % page_size) * D;
+        }
+    }
+    // Chunks of 8 elements: the lane's low chunk is `sub`, its high chunk sub + D/16; in the
+    // cache chunk c of the token at position p sits at c ^ (p & 7).
+    const int chunk_lo = (sub ^ (position & 7)) * 8, chunk_hi = ((sub + kLanes) ^ (position & 7)) * 8;
+    if (is_value) {
+        if (active) {
+            mlr_store8(dst + chunk_lo, lo);
+            mlr_store8(dst + chunk_hi, hi);
+        }
+        return;     // a head's lanes leave together; the shuffles below stay within a head
+    }
+    const W* weight = is_query ? q_weight : k_weight;
+    float scale = 1.0f;
+    if (weight) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            sum = fmaf(lo[e], lo[e], sum);
+            sum = fmaf(hi[e], hi[e], sum);
+        }
+#pragma unroll
+        for (int o = kLanes / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(__activemask(), sum, o);
+        scale = 1.0f / sqrtf(sum / static_cast<float>(D) + eps);
+    }
+    if (!active) return;
+    const bool rotate = cos_sin != nullptr;
+    if (rotate && (position < 0 || position >= table_positions)) {
+        if (sub == 0 && status) atomicOr(status, MLR_STATUS_BAD_INDEX);
+        return;
+    }
+    if (weight) {
+        float wl[8], wh[8];
+        mlr_load8(weight + 8 * sub, wl);
+        mlr_load8(weight + kHalf + 8 * sub, wh);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            lo[e] = (lo[e] * scale) * wl[e];
+            hi[e] = (hi[e] * scale) * wh[e];
+        }
+    }
+    if (rotate) {
+        const float* cs = cos_sin + static_cast<size_t>(position) * D + 8 * sub;
+        float c[8], sn[8];
+        mlr_load8(cs, c);
+        mlr_load8(cs + kHalf, sn);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float ra = __fsub_rn(__fmul_rn(lo[e], c[e]), __fmul_rn(hi[e], sn[e]));
+            const float rb = __fadd_rn(__fmul_rn(lo[e], sn[e]), __fmul_rn(hi[e], c[e]));
+            lo[e] = ra;
+            hi[e] = rb;
+        }
+    }
+    mlr_store8(x + 8 * sub, lo);
+    mlr_store8(x + kHalf + 8 * sub, hi);
+    if (dst) {
+        mlr_store8(dst + chunk_lo, lo);
+        mlr_store8(dst + chunk_hi, hi);
+    }
+}
+
 // ------------------------------------------------------------------ SiLU gate
 // gate_up is [rows, 2*inter]: the gate in the first `inter` columns, up in the rest.
 template <typename T>
@@ -459,6 +559,30 @@ MLR_API int mlr_qk_norm_rope_cache(void* qkv, int act_bf16, int ld, const float*
     MLR_REQUIRE(!write_cache || (cache && block_table && page_size > 0 && num_pages > 0), "qk_norm_rope_cache: cache write without a cache");
     if (rows == 0) return 0;
     const int warps = 4;
+    // Prompt portions in bfloat16 with a head size of 64, 128 or 256: the wide kernel.
+    if (act_bf16 && !partials && rows > 16 && (head_dim == 64 || head_dim == 128 || head_dim == 256) && ld % 8 == 0 &&
+        reinterpret_cast<uintptr_t>(qkv) % 16 == 0 && (!cache || reinterpret_cast<uintptr_t>(cache) % 16 == 0) &&
+        (!q_weight || (reinterpret_cast<uintptr_t>(q_weight) % 16 == 0 && reinterpret_cast<uintptr_t>(k_weight) % 16 == 0)) &&
+        (!cos_sin || reinterpret_cast<uintptr_t>(cos_sin) % 16 == 0)) {
+        const int heads_per_block = warps * 32 / (head_dim / 16);
+        const dim3 wide_grid(rows, (q_heads + 2 * kv_heads + heads_per_block - 1) / heads_per_block);
+#define MLR_WIDE(W, D)                                                                                         \
+        mlr_launch((qk_norm_rope_cache_wide_kernel<W, D>), dim3(wide_grid), dim3(warps * 32), 0, stream,        \
+                   static_cast<__nv_bfloat16*>(qkv), ld, rows, q_heads, kv_heads, static_cast<const W*>(q_weight), \
+                   static_cast<const W*>(k_weight), eps, cos_sin, table_positions, positions, segment_of_row,   \
+                   block_table, table_stride, page_size, static_cast<__nv_bfloat16*>(cache), num_pages, write_cache, status)
+        if (w_bf16) {
+            if (head_dim == 64) MLR_WIDE(__nv_bfloat16, 64);
+            else if (head_dim == 128) MLR_WIDE(__nv_bfloat16, 128);
+            else MLR_WIDE(__nv_bfloat16, 256);
+        } else {
+            if (head_dim == 64) MLR_WIDE(float, 64);
+            else if (head_dim == 128) MLR_WIDE(float, 128);
+            else MLR_WIDE(float, 256);
+        }
+#undef MLR_WIDE
+        return mlr_launched("qk_norm_rope_cache (wide)");
+    }
     const dim3 grid(rows, (q_heads + 2 * kv_heads + warps - 1) / warps);
     const bool vec2 = head_dim % 4 == 0 && ld % 2 == 0 && reinterpret_cast<uintptr_t>(qkv) % 8 == 0 &&
                       (!cache || reinterpret_cast<uintptr_t>(cache) % 8 == 0) &&

@@ -483,18 +483,22 @@ def test_prefill_tcgen05_far_keys_and_window_edges(page, window):
 
 
 # ------------------------------------------------------------------ q/k norm, rotation, cache write
-@pytest.mark.parametrize("Hq,Hkv,D,page", [(4, 2, 16, 4), (5, 1, 48, 16), (32, 8, 128, 16), (3, 3, 256, 8), (2, 1, 6, 2)])
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_qk_norm_rope_cache(Hq, Hkv, D, page, dtype):
+# Few rows take the kernel of one warp per head; many rows in bfloat16 with a head size of 64,
+# 128 or 256 take the wide one (several heads per warp), with norm weights of either precision.
+@pytest.mark.parametrize("segs", [[(5, 9), (0, 3), (30, 1)], [(5, 29), (0, 3), (30, 1), (60, 21)]], ids=["few-rows", "many-rows"])
+@pytest.mark.parametrize("Hq,Hkv,D,page", [(4, 2, 16, 4), (5, 1, 48, 16), (32, 8, 128, 16), (3, 3, 256, 8), (2, 1, 6, 2),
+                                           (7, 2, 64, 8), (5, 3, 128, 32)])
+@pytest.mark.parametrize("dtype,wdtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                          (torch.bfloat16, torch.float32)], ids=["f32", "bf16", "bf16-f32weights"])
+def test_qk_norm_rope_cache(Hq, Hkv, D, page, dtype, wdtype, segs):
     from mini_llm_runtime_b200.parts.rotary import rotation_table
-    segs = [(5, 9), (0, 3), (30, 1)]
     rows = sum(c for _, c in segs)
     theta, eps = 50000.0, 1e-5
     qkv = torch.randn(rows, (Hq + 2 * Hkv) * D, generator=gen(0)).to(dtype)
-    wq = (1 + 0.1 * torch.randn(D, generator=gen(1))).to(dtype)
-    wk = (1 + 0.1 * torch.randn(D, generator=gen(2))).to(dtype)
+    wq = (1 + 0.1 * torch.randn(D, generator=gen(1))).to(dtype).to(wdtype)
+    wk = (1 + 0.1 * torch.randn(D, generator=gen(2))).to(dtype).to(wdtype)
     positions, seg_of_row, info = segments_meta(segs)
-    table_cs = rotation_table(theta, D, 64)
+    table_cs = rotation_table(theta, D, 128)
     cos, sin = P.rope_table(positions.tolist(), D, theta, torch.float32)
     assert torch.allclose(table_cs[positions.long().cpu(), :D // 2], cos, atol=1e-6)
     x = qkv.float()

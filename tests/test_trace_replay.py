@@ -50,6 +50,18 @@ def test_replay_modes_match_the_plain_implementation(case, dtype, tmp_path):
                 assert torch.equal(row, results[mode][key]), f"{name} {mode} differs from whole at {key}"
 
 
+def test_replay_with_pages_of_64_tokens(case, tmp_path):
+    """The same mixed trace in a pool of 64-token pages (one copy per key tile in the
+    attention kernels instead of four)."""
+    name, folder, config, requests, want = case
+    if name != "tiny_d":
+        pytest.skip("one configuration is enough here")
+    trace = T.mixed(requests, seed=12)
+    logits = T.run_trace(folder, "bfloat16", trace, str(tmp_path / "p64"), config["vocab_size"], page_size=64)
+    for k, tokens in requests.items():
+        assert_close(T.stack(logits, k, len(tokens)), want[k], "bfloat16", f"{name} pages of 64, request {k}")
+
+
 def test_steps_without_wanted_logits_and_requests_left_out(case, tmp_path):
     name, folder, config, requests, want = case
     a, b = requests["r0"], requests["r1"]

@@ -93,12 +93,13 @@ def max_live_tokens(trace: List[dict]) -> int:
 
 
 def run_trace(model_dir: str, dtype: str, trace: List[dict], out_dir: str, vocab: int,
-              max_tokens: int = 0, env: dict = None, timeout: float = 600.0) -> Dict[Tuple[str, int], torch.Tensor]:
+              max_tokens: int = 0, env: dict = None, timeout: float = 600.0,
+              page_size: int = 0) -> Dict[Tuple[str, int], torch.Tensor]:
     """Feeds the trace to bin/trace_run, waiting for `done <step>` after each line."""
     max_tokens = max_tokens or max_live_tokens(trace)
     proc = subprocess.Popen([sys.executable, TRACE_RUN, "--model", model_dir, "--dtype", dtype, "--out", out_dir,
-                             "--max-tokens", str(max_tokens)], stdin=subprocess.PIPE, stdout=subprocess.PIPE,
-                            text=True, env=env)
+                             "--max-tokens", str(max_tokens)] + (["--page-size", str(page_size)] if page_size else []),
+                            stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, env=env)
     try:
         for step in trace:
             proc.stdin.write(json.dumps(step) + "\n")
