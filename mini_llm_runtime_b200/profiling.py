@@ -2,7 +2,7 @@
 Qwen3-8B layer sizes with few layers, bracketed by cudaProfilerStart/Stop.
 
     python -m mini_llm_runtime_b200.profiling decode  [--layers 2] [--batch 8] [--context 8192] [--steps 2]
-    python -m mini_llm_runtime_b200.profiling prefill [--layers 2] [--tokens 2048]
+    python -m mini_llm_runtime_b200.profiling prefill [--layers 2] [--tokens 2048] [--mma-sync-attention]
 
 Meant to run under `ncu --profile-from-start off ...`: with two layers it holds about
 4 GB on the device and launches a few dozen kernels inside the profiled region, so a
@@ -33,6 +33,9 @@ def main() -> int:
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--mma-sync-attention", action="store_true",
+                    help="prompt attention on the mma.sync kernel instead of the tcgen05 one")
     args = ap.parse_args()
 
     from .engine.loading import random_model
@@ -42,9 +45,10 @@ def main() -> int:
     cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
     length = args.context if args.mode == "decode" else args.tokens
     batch = args.batch if args.mode == "decode" else 1
-    model = random_model(cfg, 2, "bfloat16", CacheConfig(page_size=16, num_pages=batch * (length // 16 + 8),
+    model = random_model(cfg, 2, "bfloat16", CacheConfig(page_size=args.page_size, num_pages=batch * (length // args.page_size + 8),
                                                          max_requests=batch, max_model_len=length + 64, fill_nan=False))
     model.use_graphs = not args.no_graphs
+    model.rt.tcgen05_attention = not args.mma_sync_attention
     g = torch.Generator().manual_seed(0)
     tokens = lambda n: torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
