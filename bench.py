@@ -11,8 +11,10 @@ A step is one decode step of the whole batch.
   value      decoded tokens per second, timed on the device with CUDA events around K
              steps whose sampled tokens stay on the device
   e2e        the same through the public entry point (Engine.submit / Engine.step):
-             token ids go host -> device from pinned memory and sampled ids come
-             device -> host every step
+             every step its inputs (token slots, positions, block tables) go host ->
+             device from pinned memory and its sampled ids come device -> host; the
+             engine launches the next decode step before it reads the last one back,
+             feeding it the ids on the device, so its bookkeeping runs beside the GPU
   prefill    one request of 2048 tokens in one step: tokens/s, ms, and flops / time /
              bf16 peak
   roofline   bytes a decode step must read (every weight once plus the cache of the

@@ -20,9 +20,10 @@ class LLM:
     def __init__(self, model: Union[str, Model], dtype: str = "bfloat16", max_model_len: int = 0,
                  max_requests: int = 8, page_size: int = 16, num_pages: int = 0,
                  max_batch_tokens: int = 256, prefill_chunk: int = 128, policy: str = "mixed",
-                 device: str = "cuda:0"):
+                 device: str = "cuda:0", run_ahead: bool = True):
         """`model`: a folder with config.json and model.safetensors, or a built Model.
-        `num_pages` 0 sizes the pool for `max_requests` requests of `max_model_len`."""
+        `num_pages` 0 sizes the pool for `max_requests` requests of `max_model_len`.
+        `run_ahead`: launch a foreseeable decode step before the last one is read back."""
         if isinstance(model, Model):
             self.model = model
             if model.cache is None:
@@ -33,7 +34,7 @@ class LLM:
             pages = num_pages or max_requests * ((max_len + page_size - 1) // page_size)
             self.model.allocate_cache(CacheConfig(page_size=page_size, num_pages=pages, max_requests=max_requests,
                                                   max_model_len=max_len))
-        self.engine = Engine(self.model, max_batch_tokens, prefill_chunk, policy)
+        self.engine = Engine(self.model, max_batch_tokens, prefill_chunk, policy, run_ahead=run_ahead)
 
     def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 32, temperature: float = 0.0,
                  seed: int = 0, ignore_eos: bool = False,

@@ -27,18 +27,41 @@ class Finished:
     finish_reason: str     # "stop" (end-of-sequence id) or "length"
 
 
+@dataclass
+class _InFlight:
+    """A step that was launched and whose sampled ids have not been read back yet."""
+    sampled_for: List[Request]
+    ids: Optional[torch.Tensor]          # int32 on the device, one per request of `sampled_for`
+    host: Optional[torch.Tensor]         # pinned: the ids and the status word, once `ready` has happened
+    ready: Optional[torch.cuda.Event]
+    all_decode: bool                     # every entry was a single decoded token
+
+
 class Engine:
+    """`run_ahead`: when the step after the one in flight can be foreseen (the same requests
+    decode again: nothing waits for admission, nobody reaches its token limit), it is launched
+    BEFORE the ids of the step in flight are read back, fed on the device by those ids.  The
+    host's bookkeeping then runs beside the device's work instead of between two steps.  A
+    request that turns out to have met an end-of-sequence id has one row computed in vain;
+    its result is dropped.  Tokens, order and finish reasons are the same as without it."""
+
     def __init__(self, model: Model, max_batch_tokens: int = 256, prefill_chunk: int = 128,
-                 policy: str = "mixed", admission_reserve_steps: int = 16):
+                 policy: str = "mixed", admission_reserve_steps: int = 16, run_ahead: bool = True):
         if model.cache is None:
             raise ValueError("the model has no cache; call allocate_cache first")
         self.model = model
         self.scheduler = Scheduler(model.cache, max_batch_tokens, prefill_chunk, policy, admission_reserve_steps)
         self.sampler = Sampler(model.rt.device, model.status)
         self.eos = set(model.plan.eos_token_ids)
+        self.run_ahead = run_ahead
         self._next_id = 0
         self.steps = 0
+        self.steps_ahead = 0      # how many of them were launched before the step before was read back
         self.batch_log: List[Dict[str, int]] = []   # per step: prefill and decode tokens (a step trace)
+        self._in_flight: Optional[_InFlight] = None
+        # Two pinned buffers for the ids coming back: one being read while the next is filled.
+        self._readback = [torch.empty(model.cache.max_requests + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._readback_turn = 0
 
     def submit(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
         params = params or SamplingParams()
@@ -54,13 +77,27 @@ class Engine:
     def has_work(self) -> bool:
         return bool(self.scheduler.waiting or self.scheduler.active)
 
-    def step(self) -> List[Finished]:
-        """One iteration; returns the requests that finished in it."""
+    # ---- launching a step
+    def _sample_and_send_back(self, logits: torch.Tensor, sampled_for: List[Request], ahead: int, all_decode: bool) -> _InFlight:
+        """Samples one id per wanted row and starts their copy to the host.  `ahead` is how
+        many tokens of each request are still on their way (1 when launching ahead)."""
+        temps = [r.params.temperature for r in sampled_for]
+        uniforms = [uniform_for(r.params.seed, r.request_id, len(r.generated) + ahead) for r in sampled_for]
+        ids = self.sampler.sample(logits, temps, uniforms)
+        host = self._readback[self._readback_turn][:len(sampled_for) + 1]
+        self._readback_turn ^= 1
+        host.copy_(torch.cat([ids, self.model.status]), non_blocking=True)     # one copy: the tokens and the status word
+        ready = torch.cuda.Event()
+        ready.record()
+        return _InFlight(sampled_for, ids, host, ready, all_decode)
+
+    def _launch(self) -> Optional[_InFlight]:
+        """Admits, plans and launches one step from what the host knows."""
         sched = self.scheduler
         sched.admit(self.model.open_request)
         slices = sched.plan()
         if not slices:
-            return []
+            return None
         entries, sampled_for = [], []
         for s in slices:
             r = s.request
@@ -80,27 +117,69 @@ class Engine:
         for s in slices:
             if s.is_prefill:
                 s.request.processed += s.tokens
+        if not sampled_for:
+            return _InFlight([], None, None, None, False)
+        return self._sample_and_send_back(logits, sampled_for, 0, all(not s.is_prefill for s in slices))
+
+    def _launch_ahead(self, before: _InFlight) -> Optional[_InFlight]:
+        """The step after `before`, launched while the ids of `before` are still on the
+        device; None if that step cannot be foreseen."""
+        sched = self.scheduler
+        if not before.all_decode or sched.waiting or len(before.sampled_for) != len(sched.active):
+            return None
+        for r in before.sampled_for:
+            if r.finish_reason or len(r.generated) + 2 > r.params.max_tokens:      # ends with the token in flight
+                return None
+        # The plan does not look at token values: with every request past its prompt it is
+        # the same batch again.
+        slices = sched.plan()
+        if (len(slices) != len(before.sampled_for) or any(s.is_prefill for s in slices)
+                or any(s.request is not r for s, r in zip(slices, before.sampled_for))):
+            return None
+        entries = [StepEntry(r.slot, [0], [0]) for r in before.sampled_for]
+        logits = self.model.step(entries, device_tokens=before.ids)
+        self.steps += 1
+        self.steps_ahead += 1
+        self.batch_log.append({"prefill": 0, "decode": len(entries)})
+        return self._sample_and_send_back(logits, before.sampled_for, 1, True)
+
+    # ---- reading a step back
+    def _finish(self, step: _InFlight) -> List[Finished]:
         finished: List[Finished] = []
-        if sampled_for:
-            temps = [r.params.temperature for r in sampled_for]
-            uniforms = [uniform_for(r.params.seed, r.request_id, len(r.generated)) for r in sampled_for]
-            ids = self.sampler.sample(logits, temps, uniforms)
-            both = torch.cat([ids, self.model.status]).cpu()      # one read: the tokens and the status word
-            if int(both[-1]):
-                self.model.check_status()
-            for r, token in zip(sampled_for, both[:-1].tolist()):
-                if token < 0:
-                    raise RuntimeError(f"request {r.request_id}: the logits were not finite")
-                r.generated.append(token)
-                if token in self.eos and not r.params.ignore_eos:
-                    r.finish_reason = "stop"
-                elif len(r.generated) >= r.params.max_tokens:
-                    r.finish_reason = "length"
-                if r.finish_reason:
-                    self.model.close_request(r.slot)
-                    sched.release(r)
-                    finished.append(Finished(r.request_id, len(r.prompt), list(r.generated), r.finish_reason))
+        if not step.sampled_for:
+            return finished
+        step.ready.synchronize()
+        values = step.host.tolist()
+        if values[-1]:
+            self.model.check_status()
+        for r, token in zip(step.sampled_for, values[:-1]):
+            if r.finish_reason:
+                continue        # it ended with the step before; this row ran ahead in vain
+            if token < 0:
+                raise RuntimeError(f"request {r.request_id}: the logits were not finite")
+            r.generated.append(token)
+            if token in self.eos and not r.params.ignore_eos:
+                r.finish_reason = "stop"
+            elif len(r.generated) >= r.params.max_tokens:
+                r.finish_reason = "length"
+            if r.finish_reason:
+                self.model.close_request(r.slot)
+                self.scheduler.release(r)
+                finished.append(Finished(r.request_id, len(r.prompt), list(r.generated), r.finish_reason))
         return finished
+
+    def step(self) -> List[Finished]:
+        """One iteration; returns the requests that finished in it."""
+        current, self._in_flight = self._in_flight, None
+        if current is not None and all(r.finish_reason for r in current.sampled_for):
+            current = None      # every request of the step that ran ahead has ended meanwhile
+        if current is None:
+            current = self._launch()
+            if current is None:
+                return []
+        if self.run_ahead and current.sampled_for:
+            self._in_flight = self._launch_ahead(current)
+        return self._finish(current)
 
     def run(self) -> List[Finished]:
         """Runs until every submitted request has finished; results in submission order."""

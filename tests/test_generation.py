@@ -96,6 +96,38 @@ def test_end_of_sequence_stops_generation(case):
         assert ignored.finish_reason == "length" and ignored.token_ids == free_run
 
 
+def test_running_ahead_changes_nothing_but_the_timing(case):
+    """Several requests decode together and end at different times, some at an
+    end-of-sequence id (which the engine only learns after the next step is launched),
+    some at their token limit; greedy and with a temperature."""
+    from mini_llm_runtime_b200 import LLM, SamplingParams
+    folder, config, weights = case
+    prompts = [random_tokens(config, n, 90 + n) for n in (6, 11, 3, 20)]
+    free_runs = [plain_generate(config, weights, p, 14) for p in prompts]
+    eos = [free_runs[0][5], free_runs[1][9]]            # request 0 stops at its 6th token or earlier, request 1 at its 10th
+    cfg = dict(config, eos_token_id=eos)
+    import tempfile, shutil
+    with tempfile.TemporaryDirectory() as tmp:
+        shutil.copy(os.path.join(folder, "model.safetensors"), tmp)
+        json.dump(cfg, open(os.path.join(tmp, "config.json"), "w"))
+        outs = {}
+        for ahead in (False, True):
+            llm = LLM(tmp, dtype="float32", max_model_len=64, max_requests=4, num_pages=32, page_size=8,
+                      max_batch_tokens=64, prefill_chunk=32, run_ahead=ahead)
+            params = [SamplingParams(max_tokens=14), SamplingParams(max_tokens=14), SamplingParams(max_tokens=9),
+                      SamplingParams(max_tokens=14, temperature=0.8, seed=5)]
+            outs[ahead] = llm.generate(prompts, params=params)
+            assert (llm.engine.steps_ahead > 0) == ahead
+            assert llm.model.cache.free_pages(0) == 32 and llm.model.cache.free_slots() == 4
+            llm.model.check_status()
+        for a, b in zip(outs[False], outs[True]):
+            assert a.token_ids == b.token_ids and a.finish_reason == b.finish_reason
+        stops = [r.finish_reason for r in outs[True]]
+        assert stops[0] == "stop" and stops[2] == "length" and len(outs[True][2].token_ids) == 9
+        for run, result in zip(free_runs[:3], outs[True][:3]):
+            assert result.token_ids == run[:len(result.token_ids)]
+
+
 def test_small_pool_makes_requests_wait_and_pages_are_used_again(case):
     from mini_llm_runtime_b200 import LLM
     folder, config, weights = case
