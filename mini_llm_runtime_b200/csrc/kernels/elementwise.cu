@@ -443,21 +443,22 @@ template <typename T>
 __global__ void swiglu_vec8_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inter) {
     mlr_grid_dependents_may_start();
     mlr_grid_wait();
+    // grid = (column blocks, rows): 8 consecutive columns of one row per thread.
     const int per_row = inter >> 3;
-    const size_t total = static_cast<size_t>(rows) * per_row;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        const size_t r = i / per_row, c = (i - r * per_row) * 8;
-        float g[8], u[8];
-        mlr_load8(gate_up + r * 2 * inter + c, g);
-        mlr_load8(gate_up + r * 2 * inter + inter + c, u);
+    const int q = blockIdx.x * blockDim.x + threadIdx.x;
+    if (q >= per_row) return;
+    const size_t r = blockIdx.y, c = static_cast<size_t>(q) * 8;
+    float g[8], u[8];
+    mlr_load8(gate_up + r * 2 * inter + c, g);
+    mlr_load8(gate_up + r * 2 * inter + inter + c, u);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) g[k] = (g[k] / (1.0f + expf(-g[k]))) * u[k];
-        mlr_store8(out + r * inter + c, g);
+    for (int k = 0; k < 8; ++k) {
+        // A bfloat16 result keeps 8 bits: the fast exponential and division (2 ulp of float32) do.
+        if (sizeof(T) == 2) g[k] = __fdividef(g[k], 1.0f + __expf(-g[k])) * u[k];
+        else g[k] = (g[k] / (1.0f + expf(-g[k]))) * u[k];
     }
+    mlr_store8(out + r * inter + c, g);
 }
-
-// The same from `slices` float32 partial sums of gate_up ([slices][rows][2*inter]).
 template <typename T>
 __global__ void swiglu_sliced_kernel(const float* __restrict__ partials, int slices, size_t slice_stride,
                                      T* __restrict__ out, int rows, int inter) {
@@ -615,13 +616,12 @@ MLR_API int mlr_swiglu(const void* gate_up, void* out, int act_bf16, int rows, i
     if (rows == 0) return 0;
     const size_t total = static_cast<size_t>(rows) * inter;
     const bool vec = inter % 8 == 0 && reinterpret_cast<uintptr_t>(gate_up) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
-    if (vec) {
-        const size_t work = total / 8;
-        const int vblocks = static_cast<int>(work / 256 + 1 < 148 * 16 ? work / 256 + 1 : 148 * 16);
+    if (vec && rows <= 65535) {
+        const dim3 vgrid((inter / 8 + 255) / 256, rows);
         if (act_bf16)
-            mlr_launch((swiglu_vec8_kernel<__nv_bfloat16>), dim3(vblocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, inter);
+            mlr_launch((swiglu_vec8_kernel<__nv_bfloat16>), dim3(vgrid), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, inter);
         else
-            mlr_launch((swiglu_vec8_kernel<float>), dim3(vblocks), dim3(256), 0, stream, static_cast<const float*>(gate_up), static_cast<float*>(out), rows, inter);
+            mlr_launch((swiglu_vec8_kernel<float>), dim3(vgrid), dim3(256), 0, stream, static_cast<const float*>(gate_up), static_cast<float*>(out), rows, inter);
         return mlr_launched("swiglu");
     }
     const int blocks = static_cast<int>(total / 1024 + 1 < 148 * 16 ? total / 1024 + 1 : 148 * 16);

@@ -66,6 +66,24 @@ def test_rmsnorm_with_residual_add(rows, width, out_dtype, w_dtype):
     assert torch.allclose(out2[:1].double().cpu(), P.rms_norm(h[rows - 1:].double(), w.double(), eps), rtol=tol, atol=tol)
 
 
+@pytest.mark.parametrize("width", [4096, 2048, 1000, 8192])
+def test_rmsnorm_does_not_depend_on_how_many_rows_a_launch_has(width):
+    """A row's result is the same bits whether it is normed alone or among hundreds."""
+    h = torch.randn(200, width, generator=gen(3)) * 2
+    delta = torch.randn(200, width, generator=gen(4))
+    w = (1 + 0.1 * torch.randn(width, generator=gen(5)))
+    for out_dtype in (torch.float32, torch.bfloat16):
+        many, few = torch.empty(200, width, dtype=out_dtype, device=DEV), torch.empty(3, width, dtype=out_dtype, device=DEV)
+        hd = h.clone().to(DEV)
+        F().rmsnorm(hd, w.to(DEV), 1e-6, many, delta=delta.to(DEV))
+        hd2 = h[:3].clone().to(DEV)
+        F().rmsnorm(hd2, w.to(DEV), 1e-6, few, delta=delta[:3].contiguous().to(DEV))
+        assert torch.equal(many[:3], few) and torch.equal(hd[:3], hd2)
+        want = P.rms_norm((h + delta).double(), w.double(), 1e-6)
+        tol = 1e-5 if out_dtype is torch.float32 else 1e-2
+        assert torch.allclose(many.double().cpu(), want, rtol=tol, atol=tol)
+
+
 def test_consumers_add_up_partial_sums():
     """A product whose K was cut into ranges leaves float32 partial sums; the norm, the
     gate and the q/k kernel add them up (in order) as they read them."""
