@@ -109,9 +109,10 @@ class Model:
         self._bound = False
         self.last_h2d_bytes = 0
         # Decode steps are replayed from CUDA graphs unless a mixer keeps state that a
-        # repeated run would advance twice (capturing runs a step more than once).
+        # repeated run would advance twice (capturing runs a step more than once) or a part
+        # says that its forward cannot be captured.
         self.use_graphs = True
-        self._graphable = all(r.state_need is None for r in self.runs)
+        self._graphable = all(r.state_need is None for r in self.runs) and all(p.graph_safe for p in self._all_parts())
         self.graph_bucket_blocks = 64          # table width of a graph, in blocks
         self.max_graphs = 48
         self._graphs = {}

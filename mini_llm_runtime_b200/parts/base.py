@@ -89,6 +89,11 @@ class RunContext:
 # --------------------------------------------------------------------------- parts
 class Part:
     category = ""
+    # Whether `forward` may be captured in a CUDA graph and replayed: it launches the same
+    # kernels with the same shapes for every step of a given batch size, reads nothing back
+    # to the host and keeps no state that a repeated run would advance twice.  A model with
+    # a part that says False launches its decode steps kernel by kernel.
+    graph_safe = True
 
     def __init__(self, spec: PartSpec):
         self.spec = spec

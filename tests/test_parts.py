@@ -1,7 +1,8 @@
 """Each part alone against the plain implementation's function for it, the run order
 as data (a layer run twice, a run that reads another run's cache), and a toy mixer
 with state of its own that is defined here, registered, built and stepped without
-any change to the package."""
+any change to the package; likewise a toy feed-forward with routing and a toy position
+encoding.  The toy parts use torch operations: they show the interfaces, not kernels."""
 import dataclasses
 import math
 
@@ -268,3 +269,134 @@ def test_a_toy_mixer_with_state_is_added_from_outside(tmp_path_factory):
     sc = model.open_request()
     assert sc == sa
     assert_close(model.step([StepEntry(sc, b, list(range(len(b))))]).cpu(), want_b, "float32", "reused slot")
+
+
+def test_a_toy_feed_forward_with_routing_is_added_from_outside(tmp_path_factory):
+    """Two experts and a router that sends each token to one of them: a FeedForward
+    registered here and put into the second layer of an otherwise ordinary model."""
+    from mini_llm_runtime_b200.config.base import LayerSpec, PartSpec, Run
+    from mini_llm_runtime_b200.config.registry import config_from_dir, plan_for, register_part
+    from mini_llm_runtime_b200.engine.model import CacheConfig, Model
+    from mini_llm_runtime_b200.parts.base import FeedForward
+    from mini_llm_runtime_b200.weights.loader import WeightSpec
+    from helpers import run_portions, run_whole
+
+    def routed(x, router, up, down):
+        """x [M, W] float32 -> sum over the chosen expert only: p_e * down_e relu(up_e x)."""
+        probs = torch.softmax(x @ router.T, dim=-1)
+        choice = probs.argmax(-1)
+        out = torch.zeros_like(x)
+        for e in range(router.shape[0]):
+            rows = choice == e
+            hidden = torch.relu(x[rows] @ up[e].T)
+            out[rows] = probs[rows, e:e + 1] * (hidden @ down[e].T)
+        return out
+
+    class TopOneExperts(FeedForward):
+        graph_safe = False       # indexing by a mask reads the count of chosen rows back to the host
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.width, self.inter, self.experts = (spec.params[k] for k in ("width", "inter", "experts"))
+
+        def weight_specs(self):
+            w = self.spec.weights
+            return [WeightSpec(w["router"], (self.experts, self.width)),
+                    WeightSpec(w["up"], (self.experts * self.inter, self.width)),
+                    WeightSpec(w["down"], (self.experts * self.width, self.inter))]
+
+        def bind(self, tensors, rt):
+            w = self.spec.weights
+            on = lambda name: tensors[w[name]].to(rt.device).float()
+            self.router = on("router")
+            self.up = on("up").view(self.experts, self.inter, self.width)
+            self.down = on("down").view(self.experts, self.width, self.inter)
+
+        def forward(self, x, step):
+            return routed(x.float(), self.router, self.up, self.down)      # a float32 contribution to the stream
+
+    register_part("feed_forward", "test_top_one_experts", TopOneExperts)
+    folder, config, weights = tiny_folder(tmp_path_factory, "tiny_a", seed=12)
+    base = plan_for(config_from_dir(folder))
+    H, I, E = config["hidden_size"], 24, 2
+    toy = PartSpec("test_top_one_experts", {"width": H, "inter": I, "experts": E},
+                   {"router": "toy.router", "up": "toy.up", "down": "toy.down"})
+    plan = dataclasses.replace(base, layers=(base.layers[0], dataclasses.replace(base.layers[1], feed_forward=toy)))
+    g = torch.Generator().manual_seed(4)
+    toy_w = {"toy.router": torch.randn(E, H, generator=g), "toy.up": torch.randn(E * I, H, generator=g) * 0.1,
+             "toy.down": torch.randn(E * H, I, generator=g) * 0.1}
+    model = Model(plan, runtime(torch.float32))
+    expected = model.expected_weights()
+    assert "toy.router" in expected and "model.layers.1.mlp.gate_proj.weight" not in expected
+    assert "model.layers.0.mlp.gate_proj.weight" in expected and "model.layers.1.self_attn.q_proj.weight" in expected
+    model.bind({n: toy_w[n] if n in toy_w else weights[n] for n in expected})
+    model.allocate_cache(CacheConfig(page_size=4, num_pages=64, max_requests=2))
+    assert not model._graphable
+
+    def plain(tokens):
+        T = len(tokens)
+        h = P.embedding(weights["model.embed_tokens.weight"], tokens, torch.float32)
+        cos, sin = P.rope_table(range(T), config["head_dim"], config["rope_theta"], torch.float32)
+        h, _ = P.decoder_layer(h, weights, 0, config, cos, sin, None)
+        # Layer 1 with its own feed-forward silenced, then the toy one in its place.
+        silent = dict(weights)
+        silent["model.layers.1.mlp.down_proj.weight"] = torch.zeros_like(weights["model.layers.1.mlp.down_proj.weight"])
+        h, _ = P.decoder_layer(h, silent, 1, config, cos, sin, None)
+        n = P.rms_norm(h, weights["model.layers.1.post_attention_layernorm.weight"], config["rms_norm_eps"])
+        h = h + routed(n, toy_w["toy.router"], toy_w["toy.up"].view(E, I, H), toy_w["toy.down"].view(E, H, I))
+        return P.final_logits(h, weights, config)
+
+    tokens = random_tokens(config, 50, 6)
+    want = plain(tokens)
+    chosen = torch.softmax(P.rms_norm(torch.randn(50, H, generator=g), torch.ones(H), 1e-6) @ toy_w["toy.router"].T, -1).argmax(-1)
+    assert 0 < int(chosen.sum()) < 50                      # both experts are in use for inputs of this kind
+    assert_close(run_whole(model, tokens), want, "float32", "routed feed-forward, whole")
+    assert_close(run_portions(model, tokens, [19, 2, 1, 7]), want, "float32", "routed feed-forward, in portions")
+
+
+def test_a_toy_position_encoding_is_added_from_outside(tmp_path_factory):
+    """Learned absolute positions added to the embedded tokens, and attention that does not
+    rotate: a PositionEncoding registered here, named by the plan in place of the rotary one."""
+    from mini_llm_runtime_b200.config.base import PartSpec
+    from mini_llm_runtime_b200.config.registry import config_from_dir, plan_for, register_part
+    from mini_llm_runtime_b200.engine.model import CacheConfig, Model
+    from mini_llm_runtime_b200.parts.base import PositionEncoding
+    from mini_llm_runtime_b200.weights.loader import WeightSpec
+    from helpers import run_portions, run_whole
+
+    class LearnedPositions(PositionEncoding):
+        def weight_specs(self):
+            return [WeightSpec(self.spec.weights["table"], (self.spec.params["max_positions"], self.spec.params["width"]))]
+
+        def bind(self, tensors, rt):
+            self.table = tensors[self.spec.weights["table"]].to(rt.device).float()
+
+        def add_to_embedding(self, h, step):
+            h += self.table[step.positions.long()]
+
+    register_part("position", "test_learned_positions", LearnedPositions)
+    folder, config, weights = tiny_folder(tmp_path_factory, "tiny_b", seed=13)
+    base = plan_for(config_from_dir(folder))
+    H, positions = config["hidden_size"], 128
+    layers = tuple(dataclasses.replace(l, mixer=dataclasses.replace(l.mixer, params={**l.mixer.params, "position": None}))
+                   for l in base.layers)
+    plan = dataclasses.replace(base, layers=layers, positions={
+        "learned": PartSpec("test_learned_positions", {"max_positions": positions, "width": H}, {"table": "toy.positions"})})
+    table = torch.randn(positions, H, generator=torch.Generator().manual_seed(2)) * 0.5
+    for dtype in ("float32", "bfloat16"):
+        model = Model(plan, runtime(torch.float32 if dtype == "float32" else torch.bfloat16))
+        expected = model.expected_weights()
+        assert "toy.positions" in expected
+        model.bind({n: table if n == "toy.positions" else weights[n] for n in expected})
+        model.allocate_cache(CacheConfig(page_size=8, num_pages=32, max_requests=2))
+        assert all(b.mixer.position is None for b in model.blocks)
+
+        tokens = random_tokens(config, 70, 9)
+        T = len(tokens)
+        h = P.embedding(weights["model.embed_tokens.weight"], tokens, torch.float32) + table[:T]
+        no_turn = (torch.ones(T, config["head_dim"] // 2), torch.zeros(T, config["head_dim"] // 2))
+        for layer in range(config["num_hidden_layers"]):
+            h, _ = P.decoder_layer(h, weights, layer, config, *no_turn, None)
+        want = P.final_logits(h, weights, config)
+        assert_close(run_whole(model, tokens), want, dtype, "learned positions, whole")
+        assert_close(run_portions(model, tokens, [33, 1, 2, 20]), want, dtype, "learned positions, in portions")
