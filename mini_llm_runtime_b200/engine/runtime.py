@@ -119,11 +119,18 @@ class Runtime:
         F.gemm_bf16_tcgen05(x, w, out, self.status)
         return out
 
-    def linear_delta(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    def linear_delta(self, x: torch.Tensor, w: torch.Tensor, into: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """A float32 contribution to the residual stream: [M, N], or [S, M, N] partial sums
-        that the next norm adds up."""
+        that the next norm adds up.  With `into` (the stream itself, float32 [M, N]) a
+        library product of a prompt portion adds its result there in its epilogue
+        (into += x W^T, one rounding per element as the separate add had) and None is returned."""
         parts = self.linear_partials(x, w)
-        return parts if parts is not None else self.linear(x, w, out_dtype=torch.float32)
+        if parts is not None:
+            return parts
+        if into is not None and self.dtype is torch.bfloat16 and not self._own_gemm(x, w) and into.dtype is torch.float32:
+            torch.addmm(into, x, w.t(), out_dtype=torch.float32, out=into)
+            return None
+        return self.linear(x, w, out_dtype=torch.float32)
 
     def gated_linear(self, x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
         """silu(x Wgate^T) * (x Wup^T) for the stacked matrix [2 I, K]."""

@@ -82,7 +82,7 @@ class AttentionMixer(Mixer):
         out = rt.empty(x.shape[0], self.heads * D)
         A.paged_attention(qkv, out, run.cache, table, step, self.heads, self.kv_heads, D,
                           self.window or 0, self.scale, cache_group=run.group)
-        return rt.linear_delta(out, self.w_o)
+        return rt.linear_delta(out, self.w_o, into=step.residual)
 
 
 register_part("mixer", "attention", AttentionMixer)

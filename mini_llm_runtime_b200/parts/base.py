@@ -75,6 +75,10 @@ class StepContext:
                                           # must be planned for contexts up to this bound, not for the
                                           # lengths of the step at hand
     scratch: Dict[str, object] = field(default_factory=dict)   # per-step memo for kernels' plans
+    # The float32 residual stream while a block runs.  A mixer or feed-forward whose last
+    # product can add its result straight into it (h += x W^T in the product's epilogue)
+    # does so and returns None instead of a contribution for the next norm to add.
+    residual: Optional[torch.Tensor] = None
 
 
 @dataclass

@@ -1,10 +1,11 @@
 """Pre-norm residual block: `h += mixer(norm(h))`, then `h += feed_forward(norm(h))`
 (src/minillm/runtime.cpp:245-337; src/minillm/cuda/layer.cpp:42-70).
 
-Each residual add is folded into the norm that follows it: a sub-layer's output is
-handed on as `pending` and added to `h` by the next norm's kernel, so the residual
-stream is read and written once per sub-layer.  Norm slots: "pre_mixer",
-"pre_feed_forward".
+Each residual add is folded into a neighbouring kernel: either the sub-layer's last
+product adds its result into `h` itself (it finds `h` in `step.residual` and returns
+None), or its output is handed on as `pending` and added to `h` by the next norm's
+kernel.  Either way the residual stream is read and written once per sub-layer.  Norm
+slots: "pre_mixer", "pre_feed_forward".
 """
 from __future__ import annotations
 
@@ -14,6 +15,7 @@ from .base import Block
 
 class PreNormBlock(Block):
     def forward(self, h, pending, step, run):
+        step.residual = h
         x = self.norms["pre_mixer"].forward(h, pending, step)
         mixed = self.mixer.forward(x, step, run)
         x = self.norms["pre_feed_forward"].forward(h, mixed, step)

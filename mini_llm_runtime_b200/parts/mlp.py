@@ -42,7 +42,7 @@ class SwiGLU(FeedForward):
     def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
         rt = step.rt
         act = rt.gated_linear(x, self.w_gate_up)
-        return rt.linear_delta(act, self.w_down)
+        return rt.linear_delta(act, self.w_down, into=step.residual)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)
