@@ -86,7 +86,9 @@ def write_model(path: str, cfg: dict, weights: dict):
 
 
 def main():
-    reference = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_reference_golden.py <checkout of lilong555/mini-llm-runtime>")
+    reference = sys.argv[1]
     with tempfile.TemporaryDirectory() as tmp:
         binary = os.path.join(tmp, "anchor")
         command = ["g++", "-std=c++20", "-O1", "-pthread", "-I", os.path.join(reference, "include"),
