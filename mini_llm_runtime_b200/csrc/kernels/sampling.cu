@@ -7,8 +7,10 @@
 // (src/http_server.cpp:140-142); the temperature draw is this engine's own: with
 // z_i = logit_i / T, e_i = exp(z_i - max z) in float32 and sums in float64, the token is
 // the first id whose cumulative sum exceeds u * sum(e), u in [0,1) given per row by the
-// host.  One block per row; every thread owns one contiguous run of ids, so the sums are
-// taken in a fixed order.
+// host.  One block of 32 warps per row.  Each warp owns one contiguous range of ids and
+// walks it 128 ids at a time (a float4 per lane, so a warp's load is 512 consecutive bytes);
+// the sums are taken in a fixed order: per lane along the range, a fixed tree over the
+// lanes, the warps in order.
 #include "common.cuh"
 
 namespace {
@@ -25,6 +27,17 @@ __device__ __forceinline__ Best better(Best a, Best b) {
     return a;
 }
 
+// The four values at ids i .. i+3 of a row (those at or beyond `end` read as `fill`).
+__device__ __forceinline__ void load4(const float* x, int i, int end, bool vector, float fill, float (&v)[4]) {
+    if (vector && i + 3 < end) {
+        const float4 q = *reinterpret_cast<const float4*>(x + i);
+        v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+    } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = i + k < end ? x[i + k] : fill;
+    }
+}
+
 __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restrict__ logits, int ld, int vocab,
                                                           const float* __restrict__ temperature,
                                                           const double* __restrict__ uniform,
@@ -32,38 +45,28 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restric
     mlr_grid_dependents_may_start();
     mlr_grid_wait();
     __shared__ Best best_of_warp[32];
-    __shared__ double sums[kThreads];
+    __shared__ double sum_of_warp[33];
     __shared__ int nonfinite;
     __shared__ Best winner;
-    __shared__ double total;
     const int row = blockIdx.x;
     const float* x = logits + static_cast<size_t>(row) * ld;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int run = ((vocab + kThreads - 1) / kThreads + 3) & ~3;   // a multiple of 4: runs start on 16-byte boundaries
-    const int begin = min(vocab, static_cast<int>(threadIdx.x) * run), end = min(vocab, begin + run);
+    const int range = (((vocab + 31) >> 5) + 127) & ~127;          // ids per warp, a multiple of 128
+    const int begin = min(vocab, warp * range), end = min(vocab, begin + range);
     const bool vector = (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
     if (threadIdx.x == 0) nonfinite = 0;
     __syncthreads();
 
     Best best{-INFINITY, 0x7fffffff};
     bool bad = false;
-    int i = begin;
-    if (vector) {
-#pragma unroll 4
-        for (; i + 3 < end; i += 4) {
-            const float4 q = *reinterpret_cast<const float4*>(x + i);
-            const float v[4] = {q.x, q.y, q.z, q.w};
+    for (int i = begin + 4 * lane; i < end; i += 128) {
+        float v[4];
+        load4(x, i, end, vector, 0.0f, v);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                bad |= !isfinite(v[k]);
-                if (v[k] > best.value) best = Best{v[k], i + k};
-            }
+        for (int k = 0; k < 4; ++k) {
+            bad |= !isfinite(v[k]);
+            if (i + k < end && v[k] > best.value) best = Best{v[k], i + k};
         }
-    }
-    for (; i < end; ++i) {
-        const float v = x[i];
-        bad |= !isfinite(v);
-        if (v > best.value) best = Best{v, i};
     }
     if (bad) nonfinite = 1;
 #pragma unroll
@@ -97,37 +100,70 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restric
     }
     // z = logit / T; its maximum is at the greedy winner because T > 0.
     const float zmax = winner.value / t;
+    auto weights = [&](int i, double (&e)[4]) {        // exp(z - max z) of ids i .. i+3 (0 beyond the range)
+        float v[4];
+        load4(x, i, end, vector, -INFINITY, v);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) e[k] = i + k < end ? static_cast<double>(expf(v[k] / t - zmax)) : 0.0;
+    };
     double mine = 0.0;
-    for (int i = begin; i < end; ++i) mine += static_cast<double>(expf(x[i] / t - zmax));
-    sums[threadIdx.x] = mine;
+    for (int i = begin + 4 * lane; i < end; i += 128) {
+        double e[4];
+        weights(i, e);
+        mine += ((e[0] + e[1]) + e[2]) + e[3];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+    if (lane == 0) sum_of_warp[warp] = mine;
     __syncthreads();
     if (threadIdx.x == 0) {
         double running = 0.0;
-        for (int i = 0; i < kThreads; ++i) {
-            const double s = sums[i];
-            sums[i] = running;  // exclusive prefix
+        for (int w = 0; w < 32; ++w) {
+            const double s = sum_of_warp[w];
+            sum_of_warp[w] = running;       // the sum of all warps before w
             running += s;
         }
-        total = running;
+        sum_of_warp[32] = running;
+        out[row] = vocab - 1;               // if rounding leaves the target beyond the last sum
     }
     __syncthreads();
-    const double target = uniform[row] * total;
-    const double before = sums[threadIdx.x];
-    const double after = threadIdx.x + 1 < kThreads ? sums[threadIdx.x + 1] : total;
-    if (threadIdx.x == 0) out[row] = vocab - 1;  // if rounding leaves the target beyond the last sum
-    __syncthreads();
-    if (begin < end && target >= before && target < after) {
-        double running = before;
-        int chosen = end - 1;
-        for (int i = begin; i < end; ++i) {
-            running += static_cast<double>(expf(x[i] / t - zmax));
-            if (running > target) {
-                chosen = i;
-                break;
-            }
+    const double target = uniform[row] * sum_of_warp[32];
+    if (begin >= end || target < sum_of_warp[warp] || (warp < 31 && target >= sum_of_warp[warp + 1])) return;
+    // This warp's range holds the target: walk it again, 128 ids at a time, with a running
+    // sum over the lanes, until the sum passes the target.
+    double running = sum_of_warp[warp];
+    int chosen = end - 1;                   // if this pass's rounding differs from the first one's
+    for (int base = begin; base < end; base += 128) {
+        double e[4];
+        weights(base + 4 * lane, e);
+        const double own = ((e[0] + e[1]) + e[2]) + e[3];
+        double upto = own;                  // inclusive sum over lanes 0 .. lane
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const double other = __shfl_up_sync(0xffffffffu, upto, o);
+            if (lane >= o) upto += other;
         }
-        out[row] = chosen;
+        const unsigned passed = __ballot_sync(0xffffffffu, running + upto > target);
+        if (passed) {
+            const int first = __ffs(passed) - 1;
+            if (lane == first) {
+                double sum = running + upto - own;
+                chosen = min(base + 4 * lane + 3, end - 1);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    sum += e[k];
+                    if (sum > target) {
+                        chosen = base + 4 * lane + k;
+                        break;
+                    }
+                }
+                out[row] = min(chosen, end - 1);
+            }
+            return;
+        }
+        running += __shfl_sync(0xffffffffu, upto, 31);
     }
+    if (lane == 0) out[row] = chosen;
 }
 
 }  // namespace
