@@ -73,3 +73,18 @@ def test_device_tokens_feed_the_next_step(case):
         ids = torch.tensor([tokens[p]], dtype=torch.int32, device="cuda:0")
         logits = model.step([StepEntry(slot, [0], [0])], device_tokens=ids)
         assert_close(logits.float().cpu(), want[p:p + 1], "float32", f"position {p}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_prompt_whole_and_in_large_portions(tmp_path_factory, dtype):
+    """2000 tokens: many query tiles and key tiles, waves of attention blocks, over a
+    hundred pages, the window of the second layer far behind; in one step, in portions of
+    800 (remainders of every kind), and with pages of 64 tokens."""
+    folder, config, weights = tiny_folder(tmp_path_factory, "tiny_d", seed=21)
+    tokens = random_tokens(config, 2000, 77)
+    want = plain_qwen3.forward(config, weights, tokens)
+    model = engine_model(folder, dtype, num_pages=2 * 128, page_size=16, max_requests=2)
+    assert_close(run_whole(model, tokens), want, dtype, "long prompt, whole")
+    assert_close(run_portions(model, tokens, [800, 800, 337, 63]), want, dtype, "long prompt, in portions")
+    model64 = engine_model(folder, dtype, num_pages=2 * 32, page_size=64, max_requests=2)
+    assert_close(run_portions(model64, tokens, [1500, 1, 1, 498]), want, dtype, "long prompt, pages of 64")
