@@ -44,6 +44,7 @@ class Runtime:
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self._splits = {}
         self._counters = None
+        self._retired = []
         self.status = None        # the model's device status word (set at bind time)
         self._shared = {}
 
@@ -80,6 +81,8 @@ class Runtime:
         if self._counters is None or count > self._counters.numel():
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("the split counters must be sized before a step is captured")
+            if self._counters is not None:
+                self._retired.append(self._counters)     # graphs captured earlier still point at it
             self._counters = torch.zeros(max(2 * count, 1 << 14), dtype=torch.int32, device=self.device)
         return self._counters
 
