@@ -193,3 +193,17 @@ def test_random_weights_mode_writes_a_loadable_folder(tmp_path):
     # The plain implementation runs on what was written.
     logits = plain_qwen3.forward(raw, a, [1, 2, 3])
     assert logits.shape == (3, raw["vocab_size"]) and torch.isfinite(logits).all()
+
+
+def test_bench_refuses_several_gpus_and_has_no_reference_arm():
+    """The contract of bench.py that needs no GPU: one line and exit code 2 for N > 1; the
+    reference arm says in one JSON line why it cannot run and exits 0."""
+    import json
+    import subprocess
+    import sys
+    bench = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py")
+    many = subprocess.run([sys.executable, bench, "--gpus", "2"], capture_output=True, text=True)
+    assert many.returncode == 2 and len(many.stdout.strip().splitlines()) == 1
+    reference = subprocess.run([sys.executable, bench, "--impl", "reference"], capture_output=True, text=True)
+    line = json.loads(reference.stdout.strip())
+    assert reference.returncode == 0 and line["impl"] == "reference" and line["unavailable"]
