@@ -40,7 +40,12 @@ class Runtime:
         self.use_tcgen05 = True       # bf16 products on the package's tcgen05/TMA kernel
         self.tcgen05_prefill = False  # ... also for prompt portions (else the vendor library takes those)
         self.tcgen05_attention = True  # prompt portions of 65 rows and more on the tcgen05 attention kernel
-        self.decode_rows = 64         # up to this many rows a product streams the weights (swapped operands, split K)
+        # Up to this many rows a product runs on the own kernel (swapped operands, split K, partial
+        # sums added by the kernel that reads them).  Measured in the decode step of the 8B sizes:
+        # it wins by 5 % at 1 to 4 rows, ties at 8 and loses 3-4 % to the vendor library from 16
+        # rows on, where its float32 partial sums (rows x splits) become real traffic.  64 is the
+        # most the kernel's swapped form takes.
+        self.decode_rows = 8
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self._splits = {}
         self._counters = None
