@@ -113,7 +113,10 @@ class Model:
         # says that its forward cannot be captured.
         self.use_graphs = True
         self._graphable = all(r.state_need is None for r in self.runs) and all(p.graph_safe for p in self._all_parts())
-        self.graph_bucket_blocks = 64          # table width of a graph, in blocks
+        # Table width of a graph, in blocks: a graph serves the contexts of one bucket, and its
+        # attention launch is planned for the bucket's upper end.  Set to about 1024 tokens when
+        # the cache is allocated (a wider bucket plans key splits that short contexts leave idle).
+        self.graph_bucket_blocks = 64
         self.max_graphs = 48
         self._graphs = {}
         self._graph_pool = None
@@ -157,6 +160,7 @@ class Model:
         if len(pages) != len(self.group_windows) or any(p <= 0 for p in pages):
             raise ValueError(f"need a positive page count for each of {len(self.group_windows)} cache groups, got {pages}")
         self.cache_config = CacheConfig(config.page_size, config.num_pages, config.max_requests, max_len, pages, config.fill_nan)
+        self.graph_bucket_blocks = max(1, 1024 // config.page_size)
         self.cache = CacheManager([GroupSpec(w, p) for w, p in zip(self.group_windows, pages)],
                                   config.page_size, config.max_requests, max_len)
         for i, run in enumerate(self.runs):
