@@ -71,8 +71,8 @@ class AttentionMixer(Mixer):
     def forward(self, x: torch.Tensor, step: StepContext, run: RunContext) -> torch.Tensor:
         rt = step.rt
         D = self.head_dim
-        partials = rt.linear_partials(x, self.w_qkv)
-        qkv = rt.empty(x.shape[0], self.w_qkv.shape[0]) if partials is not None else rt.linear(x, self.w_qkv)
+        partials = rt.linear_partials(x, self.w_qkv, activation=True)
+        qkv = rt.empty(x.shape[0], self.w_qkv.shape[0]) if partials is not None else rt.linear(x, self.w_qkv, activation=True)
         table = step.tables[run.group]
         rotation = self.position.rotation_table() if self.position is not None else None
         F.qk_norm_rope_cache(qkv, self.heads, self.kv_heads, D, self.q_norm, self.k_norm,
