@@ -59,7 +59,25 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restric
 
     Best best{-INFINITY, 0x7fffffff};
     bool bad = false;
-    for (int i = begin + 4 * lane; i < end; i += 128) {
+    int i = begin + 4 * lane;
+    if (vector) {
+        // Eight loads in flight per lane while whole chunks of 128 ids remain.
+        for (; i + 7 * 128 + 3 < end; i += 8 * 128) {
+            float4 q[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) q[c] = *reinterpret_cast<const float4*>(x + i + c * 128);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const float v[4] = {q[c].x, q[c].y, q[c].z, q[c].w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    bad |= !isfinite(v[k]);
+                    if (v[k] > best.value) best = Best{v[k], i + c * 128 + k};
+                }
+            }
+        }
+    }
+    for (; i < end; i += 128) {
         float v[4];
         load4(x, i, end, vector, 0.0f, v);
 #pragma unroll
