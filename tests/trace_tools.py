@@ -69,7 +69,7 @@ def mixed(requests: Dict[str, List[int]], seed: int, live_limit: int = 4) -> Lis
         for k in chosen:
             t, pos = requests[k], live[k]
             prompt = len(t) * 2 // 3
-            n = min(rng.choice([2, 3, 5, 8, 16, 29]), prompt - pos) if pos < prompt else 1
+            n = min(rng.choice([2, 3, 5, 8, 16, 29, 70, 130]), prompt - pos) if pos < prompt else 1
             entries.append({"id": k, "tokens": t[pos:pos + n], "want": list(range(n))})
             live[k] = pos + n
             if live[k] == len(t):
