@@ -596,9 +596,11 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
     // in split order, so the sum does not depend on which block that is.  The counter is left
     // at zero for the next launch.
     __shared__ int is_last;
-    __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
+        // One fence after the block's barrier orders every thread's partial results before
+        // the count (fences are cumulative), as a grid-wide barrier does it.
+        __threadfence();
         int* counter = counters + item * kv_heads + kv_head;
         is_last = atomicAdd(counter, 1) == plan.splits - 1;
         if (is_last) *counter = 0;
