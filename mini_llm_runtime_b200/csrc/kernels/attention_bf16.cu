@@ -603,11 +603,13 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
         __threadfence();
         int* counter = counters + item * kv_heads + kv_head;
         is_last = atomicAdd(counter, 1) == plan.splits - 1;
-        if (is_last) *counter = 0;
+        if (is_last) {
+            *counter = 0;
+            __threadfence();       // the other blocks' partial results, for every thread after the barrier
+        }
     }
     __syncthreads();
     if (!is_last) return;
-    __threadfence();
     // The weights exp2(m_split - m) / l are worked out once per (split, row) in shared memory
     // from maxima and sums that all threads fetch together; the sums over splits then have
     // no dependent loads and are fetched four values and eight splits at a time.  Other SMs
