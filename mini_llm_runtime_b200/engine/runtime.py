@@ -7,14 +7,18 @@ the serving path: matrices, activations and the cache are bfloat16, products
 accumulate in float32.  In both, the residual stream, norms, softmax, rotation and
 logits are float32.
 
-bfloat16 products of a decode step (up to 64 rows) run on the package's tcgen05/TMA
-kernel (`csrc/kernels/gemm_bf16_tcgen05.cu`): the weight matrix takes the 128-row side
-of the instruction, K is cut into ranges so that a small matrix still occupies every
-SM, and the kernel that reads the result adds the ranges' partial sums.  Products of
-prompt portions go to the vendor library (cuBLAS through `torch.mm`), as the reference
-sends all of its products to cuBLAS (src/minillm/cuda/matrix.cpp:30-36); the package's
-kernel takes those too when `tcgen05_prefill` is set (it reaches about 85 % of the
-library's two-SM kernels there).
+Which kernel a bfloat16 product takes depends on its rows and on what its result is:
+with up to `decode_rows` rows, a product that ends a sub-layer (o_proj, down_proj) and the
+head run on the package's tcgen05/TMA kernel (`csrc/kernels/gemm_bf16_tcgen05.cu`): the
+weight matrix takes the 128-row side of the instruction, K is cut into ranges so that a
+small matrix still occupies every SM, and the kernel that reads the result adds the ranges'
+partial sums.  Every other product goes to the vendor library (cuBLAS through `torch.mm` /
+`torch.addmm`), as the reference sends all of its products to cuBLAS
+(src/minillm/cuda/matrix.cpp:30-36): the few-row products whose result is an activation
+(q/k/v, gate/up), which the library writes in bfloat16 at once, and everything with more
+rows; a library product that ends a sub-layer adds its result into the residual stream in
+its epilogue.  The package's kernel takes prompt portions too when `tcgen05_prefill` is set
+(it reaches about 85 % of the library's two-SM kernels there).
 """
 from __future__ import annotations
 
