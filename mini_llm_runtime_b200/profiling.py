@@ -3,6 +3,10 @@ Qwen3-8B layer sizes with few layers, bracketed by cudaProfilerStart/Stop.
 
     python -m mini_llm_runtime_b200.profiling decode  [--layers 2] [--batch 8] [--context 8192] [--steps 2]
     python -m mini_llm_runtime_b200.profiling prefill [--layers 2] [--tokens 2048] [--mma-sync-attention]
+    python -m mini_llm_runtime_b200.profiling attention [--page-size 64]
+
+`attention` times the two bfloat16 attention kernels alone (CUDA events, no model) over a
+range of prompt lengths, contexts, batch sizes and head sizes and prints two tables.
 
 Meant to run under `ncu --profile-from-start off ...`: with two layers it holds about
 4 GB on the device and launches a few dozen kernels inside the profiled region, so a
@@ -26,7 +30,7 @@ QWEN3_8B = {
 
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("mode", choices=["decode", "prefill"])
+    ap.add_argument("mode", choices=["decode", "prefill", "attention"])
     ap.add_argument("--layers", type=int, default=2)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
@@ -37,6 +41,9 @@ def main() -> int:
     ap.add_argument("--mma-sync-attention", action="store_true",
                     help="prompt attention on the mma.sync kernel instead of the tcgen05 one")
     args = ap.parse_args()
+
+    if args.mode == "attention":
+        return attention_tables(args.page_size if args.page_size != 16 else 64)
 
     from .engine.loading import random_model
     from .engine.model import CacheConfig, StepEntry
@@ -102,6 +109,76 @@ def main() -> int:
         torch.cuda.synchronize()
         torch.cuda.cudart().cudaProfilerStop()
     model.check_status()
+    return 0
+
+
+def attention_tables(page: int) -> int:
+    """The prompt kernel (tcgen05) and the decode kernel (split-KV) alone, random data, pages
+    in random order for decode; time per launch from CUDA events over 10 launches after 3."""
+    import math
+
+    from .ops import attention as A
+    from .ops import functions as F
+    dev = "cuda:0"
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(reps):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / reps
+
+    def prefill(tokens, heads, kv_heads, dim, window=0, before=0):
+        blocks = (before + tokens + page - 1) // page
+        cache = (torch.randn(blocks, 2, kv_heads, page, dim, device=dev) * 0.5).to(torch.bfloat16)
+        table = torch.arange(blocks, device=dev, dtype=torch.int32).view(1, blocks)
+        info = torch.tensor([[0, tokens, before, 0]], dtype=torch.int32, device=dev)
+        qkv = torch.randn(tokens, (heads + 2 * kv_heads) * dim, device=dev).to(torch.bfloat16)
+        out = torch.empty(tokens, heads * dim, device=dev, dtype=torch.bfloat16)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        tiles = sorted(((0, t) for t in range(0, tokens, 128)), key=lambda x: -x[1])
+        tiles = torch.tensor(tiles, dtype=torch.int32, device=dev)
+        ms = timed(lambda: F.attention_prefill_tcgen05(qkv, out, cache, tiles, info, table, page, heads, kv_heads, dim, window,
+                                                       1 / math.sqrt(dim), status))
+        pairs = sum(min(before + t + 1, window) if window else before + t + 1 for t in range(tokens))
+        print(f"| {tokens} | {before} | {heads}/{kv_heads} x {dim} | {window or '-'} | {ms * 1e3:.0f} | {4 * heads * dim * pairs / ms / 1e9:.0f} |")
+        assert status.item() == 0
+
+    def decode(batch, context, heads, kv_heads, dim):
+        blocks = (context + page - 1) // page
+        cache = (torch.randn(batch * blocks, 2, kv_heads, page, dim, device=dev) * 0.5).to(torch.bfloat16)
+        table = torch.randperm(batch * blocks, device=dev).to(torch.int32).view(batch, blocks)
+        info = torch.tensor([[i, 1, context - 1, i] for i in range(batch)], dtype=torch.int32, device=dev)
+        qkv = torch.randn(batch, (heads + 2 * kv_heads) * dim, device=dev).to(torch.bfloat16)
+        out = torch.empty(batch, heads * dim, device=dev, dtype=torch.bfloat16)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        chunk, splits = A.split_plan([context] * batch, batch * kv_heads)
+        partial = torch.empty(max(1, F.attention_decode_scratch_floats(batch, kv_heads, dim, splits)), device=dev)
+        counters = torch.zeros(batch * kv_heads, dtype=torch.int32, device=dev)
+        ms = timed(lambda: F.attention_decode_bf16(qkv, out, cache, None, batch, info, table, page, heads, kv_heads, dim, 0,
+                                                   1 / math.sqrt(dim), chunk, splits, partial, status, counters=counters))
+        gb = batch * context * kv_heads * dim * 2 * 2 / 1e9
+        print(f"| {batch} | {context} | {heads}/{kv_heads} x {dim} | {splits} x {chunk} | {ms * 1e3:.1f} | {gb / ms:.2f} |")
+        assert status.item() == 0
+
+    print(f"pages of {page} tokens\n\n| prompt tokens | context before | heads x size | window | µs | TFLOP/s (causal) |\n| ---: | ---: | --- | ---: | ---: | ---: |")
+    for tokens in (512, 1024, 2048, 4096, 8192, 16384, 32768):
+        prefill(tokens, 32, 8, 128)
+    prefill(2048, 32, 8, 128, before=30720)
+    prefill(2048, 32, 8, 128, window=4096, before=30720)
+    for tokens in (2048, 8192):
+        prefill(tokens, 16, 4, 64)
+    print("\n| requests | context | heads x size | splits x keys | µs | TB/s of cache bytes |\n| ---: | ---: | --- | --- | ---: | ---: |")
+    for batch, context in ((1, 1024), (1, 8192), (1, 32768), (1, 131072), (8, 1024), (8, 4096), (8, 8192), (8, 32768), (64, 1024),
+                           (64, 4096), (64, 8192), (64, 32768), (256, 2048)):
+        decode(batch, context, 32, 8, 128)
+    for batch, context in ((8, 8192), (64, 8192)):
+        decode(batch, context, 16, 4, 64)
     return 0
 
 
