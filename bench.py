@@ -147,6 +147,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--quick", action="store_true", help="a small model, for checking this script")
     ap.add_argument("--no-points", action="store_true")
+    ap.add_argument("--own-products", action="store_true",
+                    help="every matrix product on the package's tcgen05 kernel, none on the vendor library (slower)")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (the baseline's configuration has 16; 64 is a little faster)")
     args = ap.parse_args()
     if args.gpus != 1:
@@ -180,6 +182,8 @@ def main() -> int:
     model = random_model(cfg, seed=2, dtype="bfloat16",
                          cache=CacheConfig(page_size=page, num_pages=pages, max_requests=max_batch,
                                            max_model_len=context + horizon + page, fill_nan=False))
+    if args.own_products:
+        model.rt.own_products_only()
     gen = torch.Generator().manual_seed(1234)
     prompt_of = lambda n: torch.randint(0, cfg["vocab_size"], (n,), generator=gen).tolist()
     layer_params, head_params = matmul_params(cfg, layers)
@@ -296,7 +300,7 @@ def main() -> int:
               "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
               "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": args.batch,
               "seq_len": context, "context_len": context, "page_size": page, "prefill_tokens": T,
-              "parallelism": "single_gpu", "l2": "inputs>L2 (15 GB of weights per step), no flush",
+              "parallelism": "single_gpu", "products": "own kernel only" if args.own_products else "own kernel and vendor library", "l2": "inputs>L2 (15 GB of weights per step), no flush",
               "weight_gb": round(weight_bytes / 1e9, 2), "kv_kb_per_token": kv_bytes_per_token / 1024}
     print(json.dumps({
         "metric": "decode tok/s (Qwen3-8B sizes, batch 8, context 8192, bf16)", "value": value, "unit": "tokens/s",

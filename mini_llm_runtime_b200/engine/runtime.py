@@ -63,6 +63,15 @@ class Runtime:
         self.status = None        # the model's device status word (set at bind time)
         self._shared = {}
 
+    def own_products_only(self) -> None:
+        """Every bfloat16 product on the package's tcgen05 kernel, none on the vendor library:
+        few rows in its swapped form with split K (up to 64 rows), more rows in its plain
+        form.  Slower than the default mix (the figures are in the design notes); it shows
+        that the package's kernels cover every product of the model."""
+        self.decode_rows = 64
+        self.own_activation_products = True
+        self.tcgen05_prefill = True
+
     @property
     def is_bf16(self) -> bool:
         return self.dtype is torch.bfloat16

@@ -88,3 +88,23 @@ def test_a_long_prompt_whole_and_in_large_portions(tmp_path_factory, dtype):
     assert_close(run_portions(model, tokens, [800, 800, 337, 63]), want, dtype, "long prompt, in portions")
     model64 = engine_model(folder, dtype, num_pages=2 * 32, page_size=64, max_requests=2)
     assert_close(run_portions(model64, tokens, [1500, 1, 1, 498]), want, dtype, "long prompt, pages of 64")
+
+
+def test_every_product_on_the_own_kernel(tmp_path_factory):
+    """The mode without the vendor library: prompt portions, decoded tokens and a batch of
+    more than 8 rows all go through the package's tcgen05 product."""
+    from mini_llm_runtime_b200.engine.model import StepEntry
+    folder, config, weights = tiny_folder(tmp_path_factory, "tiny_d", seed=31)
+    tokens = random_tokens(config, 300, 5)
+    want = plain_qwen3.forward(config, weights, tokens)
+    model = engine_model(folder, "bfloat16", num_pages=64, max_requests=16)
+    model.rt.own_products_only()
+    assert_close(run_whole(model, tokens), want, "bfloat16", "own products, whole")
+    assert_close(run_portions(model, tokens, [200, 70, 1]), want, "bfloat16", "own products, portions and single tokens")
+    # Twelve requests decode together (more rows than the default hands to the own kernel).
+    slots = [model.open_request() for _ in range(12)]
+    model.step([StepEntry(s, tokens[:20 + i], []) for i, s in enumerate(slots)])
+    logits = model.step([StepEntry(s, [tokens[20 + i]], [0]) for i, s in enumerate(slots)]).float().cpu()
+    model.check_status()
+    for i in range(12):
+        assert_close(logits[i:i + 1], want[20 + i:21 + i], "bfloat16", f"own products, request {i} of a batch of 12")
