@@ -75,6 +75,27 @@ static void mlr_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);   // an error shows in mlr_launched()
 }
 
+// The same for a kernel whose blocks form clusters of `cluster` consecutive blocks.
+template <typename... KArgs, typename... Args>
+static void mlr_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, unsigned cluster, size_t smem, cudaStream_t stream,
+                               Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[2];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = cluster;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = mlr_pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);   // an error shows in mlr_launched()
+}
+
 #define MLR_REQUIRE(condition, ...) \
     do {                            \
         if (!(condition)) return mlr_fail(__VA_ARGS__); \

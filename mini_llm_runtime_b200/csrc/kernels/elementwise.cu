@@ -424,33 +424,40 @@ __global__ void __launch_bounds__(128) qk_norm_rope_cache_wide_kernel(
 }
 
 // ------------------------------------------------------------------ SiLU gate
-// gate_up is [rows, 2*inter]: the gate in the first `inter` columns, up in the rest.
+// gate_up is [rows, 2*inter], in blocks of `block` gate columns followed by the `block` "up"
+// columns of the same outputs: output column c reads the gate at (c / block) * 2 * block +
+// c % block and "up" `block` columns further.  block == inter is the plain stacking (all gates,
+// then all ups); inter is a multiple of block.
+__device__ __forceinline__ size_t gate_column(size_t c, int block) { return (c / block) * 2 * block + c % block; }
+
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inter) {
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inter, int block) {
     mlr_grid_dependents_may_start();
     mlr_grid_wait();
     const size_t total = static_cast<size_t>(rows) * inter;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<size_t>(gridDim.x) * blockDim.x) {
         const size_t r = i / inter, c = i - r * inter;
-        const float g = mlr_load(gate_up, r * 2 * inter + c);
-        const float u = mlr_load(gate_up, r * 2 * inter + inter + c);
+        const size_t at = r * 2 * inter + gate_column(c, block);
+        const float g = mlr_load(gate_up, at);
+        const float u = mlr_load(gate_up, at + block);
         mlr_store(out, i, (g / (1.0f + expf(-g))) * u);
     }
 }
 
 template <typename T>
-__global__ void swiglu_vec8_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inter) {
+__global__ void swiglu_vec8_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inter, int block) {
     mlr_grid_dependents_may_start();
     mlr_grid_wait();
-    // grid = (column blocks, rows): 8 consecutive columns of one row per thread.
+    // grid = (column blocks, rows): 8 consecutive columns of one row per thread (block % 8 == 0).
     const int per_row = inter >> 3;
     const int q = blockIdx.x * blockDim.x + threadIdx.x;
     if (q >= per_row) return;
     const size_t r = blockIdx.y, c = static_cast<size_t>(q) * 8;
+    const size_t at = r * 2 * inter + gate_column(c, block);
     float g[8], u[8];
-    mlr_load8(gate_up + r * 2 * inter + c, g);
-    mlr_load8(gate_up + r * 2 * inter + inter + c, u);
+    mlr_load8(gate_up + at, g);
+    mlr_load8(gate_up + at + block, u);
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
         // A bfloat16 result keeps 8 bits: the fast exponential and division (2 ulp of float32) do.
@@ -461,15 +468,16 @@ __global__ void swiglu_vec8_kernel(const T* __restrict__ gate_up, T* __restrict_
 }
 template <typename T>
 __global__ void swiglu_sliced_kernel(const float* __restrict__ partials, int slices, size_t slice_stride,
-                                     T* __restrict__ out, int rows, int inter) {
+                                     T* __restrict__ out, int rows, int inter, int block) {
     mlr_grid_dependents_may_start();
     mlr_grid_wait();
     const size_t total = static_cast<size_t>(rows) * inter;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<size_t>(gridDim.x) * blockDim.x) {
         const size_t r = i / inter, c = i - r * inter;
-        const float g = sliced(partials + r * 2 * inter + c, slices, slice_stride);
-        const float u = sliced(partials + r * 2 * inter + inter + c, slices, slice_stride);
+        const size_t at = r * 2 * inter + gate_column(c, block);
+        const float g = sliced(partials + at, slices, slice_stride);
+        const float u = sliced(partials + at + block, slices, slice_stride);
         mlr_store(out, i, (g / (1.0f + expf(-g))) * u);
     }
 }
@@ -611,40 +619,44 @@ MLR_API int mlr_qk_norm_rope_cache(void* qkv, int act_bf16, int ld, const float*
     return mlr_launched("qk_norm_rope_cache");
 }
 
-MLR_API int mlr_swiglu(const void* gate_up, void* out, int act_bf16, int rows, int inter, cudaStream_t stream) {
+// out[rows, inter] = silu(gate) * up for gate_up [rows, 2 * inter] laid out in blocks of
+// `block` gate columns and their `block` "up" columns (block == inter: all gates, then all ups).
+MLR_API int mlr_swiglu(const void* gate_up, void* out, int act_bf16, int rows, int inter, int block, cudaStream_t stream) {
     MLR_REQUIRE(rows >= 0 && inter > 0, "swiglu: bad sizes rows=%d inter=%d", rows, inter);
+    MLR_REQUIRE(block >= 1 && inter % block == 0, "swiglu: the width %d is no multiple of the gate block %d", inter, block);
     if (rows == 0) return 0;
     const size_t total = static_cast<size_t>(rows) * inter;
-    const bool vec = inter % 8 == 0 && reinterpret_cast<uintptr_t>(gate_up) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+    const bool vec = inter % 8 == 0 && block % 8 == 0 && reinterpret_cast<uintptr_t>(gate_up) % 16 == 0 &&
+                     reinterpret_cast<uintptr_t>(out) % 16 == 0;
     if (vec && rows <= 65535) {
         const dim3 vgrid((inter / 8 + 255) / 256, rows);
         if (act_bf16)
-            mlr_launch((swiglu_vec8_kernel<__nv_bfloat16>), dim3(vgrid), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, inter);
+            mlr_launch((swiglu_vec8_kernel<__nv_bfloat16>), dim3(vgrid), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, inter, block);
         else
-            mlr_launch((swiglu_vec8_kernel<float>), dim3(vgrid), dim3(256), 0, stream, static_cast<const float*>(gate_up), static_cast<float*>(out), rows, inter);
+            mlr_launch((swiglu_vec8_kernel<float>), dim3(vgrid), dim3(256), 0, stream, static_cast<const float*>(gate_up), static_cast<float*>(out), rows, inter, block);
         return mlr_launched("swiglu");
     }
     const int blocks = static_cast<int>(total / 1024 + 1 < 148 * 16 ? total / 1024 + 1 : 148 * 16);
     if (act_bf16)
-        mlr_launch((swiglu_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, inter);
+        mlr_launch((swiglu_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, inter, block);
     else
-        mlr_launch((swiglu_kernel<float>), dim3(blocks), dim3(256), 0, stream, static_cast<const float*>(gate_up), static_cast<float*>(out), rows, inter);
+        mlr_launch((swiglu_kernel<float>), dim3(blocks), dim3(256), 0, stream, static_cast<const float*>(gate_up), static_cast<float*>(out), rows, inter, block);
     return mlr_launched("swiglu");
 }
 
-// out[rows, inter] = silu(gate) * up from `slices` float32 partial sums of the stacked
-// product [slices][rows][2 * inter].
+// The same from `slices` float32 partial sums of the stacked product [slices][rows][2 * inter].
 MLR_API int mlr_swiglu_sliced(const float* partials, int slices, long long slice_stride, void* out, int act_bf16, int rows,
-                              int inter, cudaStream_t stream) {
+                              int inter, int block, cudaStream_t stream) {
     MLR_REQUIRE(rows >= 0 && inter > 0 && slices >= 1, "swiglu_sliced: bad sizes rows=%d inter=%d slices=%d", rows, inter, slices);
+    MLR_REQUIRE(block >= 1 && inter % block == 0, "swiglu_sliced: the width %d is no multiple of the gate block %d", inter, block);
     if (rows == 0) return 0;
     const size_t total = static_cast<size_t>(rows) * inter;
     const int blocks = static_cast<int>(total / 256 + 1 < 148 * 16 ? total / 256 + 1 : 148 * 16);
     if (act_bf16)
         mlr_launch((swiglu_sliced_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream, partials, slices, static_cast<size_t>(slice_stride),
-                                                         static_cast<__nv_bfloat16*>(out), rows, inter);
+                                                         static_cast<__nv_bfloat16*>(out), rows, inter, block);
     else
         mlr_launch((swiglu_sliced_kernel<float>), dim3(blocks), dim3(256), 0, stream, partials, slices, static_cast<size_t>(slice_stride),
-                                                         static_cast<float*>(out), rows, inter);
+                                                         static_cast<float*>(out), rows, inter, block);
     return mlr_launched("swiglu_sliced");
 }

@@ -158,6 +158,64 @@ __host__ __device__ constexpr uint32_t instruction_descriptor(int n, bool b_mn_m
            (static_cast<uint32_t>(128 >> 4) << 24);
 }
 
+// ---------------------------------------------------------------- two blocks of a cluster as one
+// A cluster of two blocks on neighbouring SMs can issue one matrix instruction over both SMs'
+// tensor cores (cta_group::2): block 0 (the leader) issues it, each block holds half of the
+// rows of A, half of the rows of B and half of the accumulator's rows, at the same
+// shared-memory and tensor-memory offsets in both.  A kernel uses one group width throughout.
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+// All threads of all blocks of the cluster; orders shared-memory and barrier state between them.
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// The cluster-wide address of the shared-memory location `addr` in the block of rank `rank`.
+__device__ __forceinline__ uint32_t in_block_of_rank(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_bar) : "memory");
+}
+// A tile load into this block's shared memory whose completion is counted on a barrier that
+// may live in the other block of the pair (a cluster-wide address).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::
+                     "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(cluster_bar)
+                 : "memory");
+}
+// D[tmem of both] (+)= A B^T with M = 256 (128 rows of A and of D per block) and N columns
+// (N / 2 rows of B per block).
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// One arrival on the barrier at this offset in each block named in `block_mask`, once all
+// tensor-core instructions this thread issued before are done.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t block_mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n" ::"r"(bar),
+                 "h"(block_mask)
+                 : "memory");
+}
+// One warp of each block of the pair calls these.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* slot, int columns) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(slot)), "r"(columns));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::);
+}
+__device__ __forceinline__ void tmem_free_pair(uint32_t base, int columns) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(base), "r"(columns));
+}
+__host__ __device__ constexpr uint32_t instruction_descriptor_m256(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
+}
+
 // ---------------------------------------------------------------- host side
 using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,

@@ -7,18 +7,20 @@ the serving path: matrices, activations and the cache are bfloat16, products
 accumulate in float32.  In both, the residual stream, norms, softmax, rotation and
 logits are float32.
 
-Which kernel a bfloat16 product takes depends on its rows and on what its result is:
-with up to `decode_rows` rows, a product that ends a sub-layer (o_proj, down_proj) and the
-head run on the package's tcgen05/TMA kernel (`csrc/kernels/gemm_bf16_tcgen05.cu`): the
-weight matrix takes the 128-row side of the instruction, K is cut into ranges so that a
-small matrix still occupies every SM, and the kernel that reads the result adds the ranges'
-partial sums.  Every other product goes to the vendor library (cuBLAS through `torch.mm` /
-`torch.addmm`), as the reference sends all of its products to cuBLAS
-(src/minillm/cuda/matrix.cpp:30-36): the few-row products whose result is an activation
-(q/k/v, gate/up), which the library writes in bfloat16 at once, and everything with more
-rows; a library product that ends a sub-layer adds its result into the residual stream in
-its epilogue.  The package's kernel takes prompt portions too when `tcgen05_prefill` is set
-(it reaches about 85 % of the library's two-SM kernels there).
+Which kernel a bfloat16 product takes depends on its rows and on what its result is.
+From `pair_rows` rows on (prompt portions) every product runs on the package's two-SM
+tcgen05 kernel (`csrc/kernels/gemm_bf16_tcgen05_pair.cu`), whose epilogue also does what
+would otherwise be a kernel of its own: a product that ends a sub-layer (o_proj, down_proj)
+adds into the float32 residual stream, and the gate/up product applies the SiLU gate (the
+feed-forward keeps its two matrices interleaved in blocks of 128 rows for that).  With up to
+`decode_rows` rows, a product that ends a sub-layer and the head run on the one-block
+tcgen05 kernel (`csrc/kernels/gemm_bf16_tcgen05.cu`): the weight matrix takes the 128-row
+side of the instruction, K is cut into ranges so that a small matrix still occupies every
+SM, and the kernel that reads the result adds the ranges' partial sums.  What is left goes
+to the vendor library (cuBLAS through `torch.mm` / `torch.addmm`), as the reference sends
+all of its products to cuBLAS (src/minillm/cuda/matrix.cpp:30-36): the few-row products whose
+result is an activation (q/k/v, gate/up), which the library writes in bfloat16 at once, and
+steps between the two row counts.  `own_products_only()` takes the library out altogether.
 """
 from __future__ import annotations
 
@@ -42,7 +44,10 @@ class Runtime:
         torch.backends.cuda.matmul.allow_tf32 = False
         torch.backends.cudnn.allow_tf32 = False
         self.use_tcgen05 = True       # bf16 products on the package's tcgen05/TMA kernel
-        self.tcgen05_prefill = False  # ... also for prompt portions (else the vendor library takes those)
+        self.tcgen05_prefill = False  # the one-block kernel also for the row counts the vendor library takes by default
+        # From this many rows on a product runs on the two-SM kernel (256 x 256 tiles; its fused
+        # epilogues make up for the rows a smaller portion leaves empty in a tile).
+        self.pair_rows = 256
         self.tcgen05_attention = True  # prompt portions of 65 rows and more on the tcgen05 attention kernel
         # Up to this many rows a product runs on the own kernel (swapped operands, split K, partial
         # sums added by the kernel that reads them).  Measured in the decode step of the 8B sizes:
@@ -64,10 +69,11 @@ class Runtime:
         self._shared = {}
 
     def own_products_only(self) -> None:
-        """Every bfloat16 product on the package's tcgen05 kernel, none on the vendor library:
-        few rows in its swapped form with split K (up to 64 rows), more rows in its plain
-        form.  Slower than the default mix (the figures are in the design notes); it shows
-        that the package's kernels cover every product of the model."""
+        """Every bfloat16 product on the package's tcgen05 kernels, none on the vendor library:
+        few rows on the one-block kernel in its swapped form with split K (up to 64 rows) and
+        in its plain form (up to `pair_rows`), more rows on the two-SM kernel as always.
+        Slower than the default mix in decode steps (the figures are in the design notes); it
+        shows that the package's kernels cover every product of the model."""
         self.decode_rows = 64
         self.own_activation_products = True
         self.tcgen05_prefill = True
@@ -111,12 +117,17 @@ class Runtime:
         return self._counters
 
     # ---- y = x @ w.T
+    def _tcgen05_ok(self, x: torch.Tensor, w: torch.Tensor) -> bool:
+        return self.use_tcgen05 and self.status is not None and F.gemm_tcgen05_applies(x, w)
+
+    def _pair(self, x: torch.Tensor, w: torch.Tensor) -> bool:
+        """Whether this bf16 product runs on the two-SM kernel."""
+        return x.shape[0] >= self.pair_rows and self._tcgen05_ok(x, w)
+
     def _own_gemm(self, x: torch.Tensor, w: torch.Tensor) -> bool:
-        """Whether this bf16 product runs on the package's tcgen05 kernel: always for the few
-        rows of a decode step; for prompt portions only when `tcgen05_prefill` is set (the
-        vendor library's two-SM kernels are still faster there)."""
-        return (self.use_tcgen05 and self.status is not None and F.gemm_tcgen05_applies(x, w)
-                and (x.shape[0] <= self.decode_rows or self.tcgen05_prefill))
+        """Whether this bf16 product runs on the one-block tcgen05 kernel: always for the few
+        rows of a decode step; beyond those only when `tcgen05_prefill` is set."""
+        return self._tcgen05_ok(x, w) and (x.shape[0] <= self.decode_rows or self.tcgen05_prefill)
 
     def linear(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                activation: bool = False) -> torch.Tensor:
@@ -126,6 +137,10 @@ class Runtime:
         if self.dtype is torch.float32:
             out = torch.empty((x.shape[0], w.shape[0]), dtype=torch.float32, device=self.device)
             F.gemm_f32(x, w, out)
+            return out
+        if self._pair(x, w):
+            out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=self.device)
+            F.gemm_bf16_tcgen05_pair(x, w, out, self.status, "bf16" if out_dtype is torch.bfloat16 else "f32")
             return out
         if self._own_gemm(x, w) and (not activation or self.own_activation_products or self.tcgen05_prefill):
             out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=self.device)
@@ -153,21 +168,42 @@ class Runtime:
 
     def linear_delta(self, x: torch.Tensor, w: torch.Tensor, into: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """A float32 contribution to the residual stream: [M, N], or [S, M, N] partial sums
-        that the next norm adds up.  With `into` (the stream itself, float32 [M, N]) a
-        library product of a prompt portion adds its result there in its epilogue
-        (into += x W^T, one rounding per element as the separate add had) and None is returned."""
+        that the next norm adds up.  With `into` (the stream itself, float32 [M, N]) the
+        product of a prompt portion adds its result there in its epilogue (into += x W^T,
+        one rounding per element as the separate add had) and None is returned."""
         parts = self.linear_partials(x, w)
         if parts is not None:
             return parts
-        if into is not None and self.dtype is torch.bfloat16 and not self._own_gemm(x, w) and into.dtype is torch.float32:
-            torch.addmm(into, x, w.t(), out_dtype=torch.float32, out=into)
-            return None
+        if into is not None and self.dtype is torch.bfloat16 and into.dtype is torch.float32 and into.is_contiguous():
+            if self._pair(x, w):
+                F.gemm_bf16_tcgen05_pair(x, w, into, self.status, "add_f32")
+                return None
+            if not self._own_gemm(x, w):
+                torch.addmm(into, x, w.t(), out_dtype=torch.float32, out=into)
+                return None
         return self.linear(x, w, out_dtype=torch.float32)
 
+    # ---- the gated pair of matrices of a feed-forward
+    def stack_gate_up(self, w_gate: torch.Tensor, w_up: torch.Tensor):
+        """The two [I, K] matrices as the one operand `gated_linear` takes, and the width I' of
+        its result.  In bfloat16 the rows alternate in blocks of 128 (gate rows of 128 outputs,
+        then their "up" rows), padded with zero rows to whole blocks, so that the gate can be
+        applied in the epilogue of the product: I' = I rounded up to 128, and the extra
+        outputs are zero.  In float32 all gate rows come first and I' = I."""
+        w_gate, w_up = self.matrix(w_gate), self.matrix(w_up)
+        if self.dtype is torch.bfloat16:
+            stacked = F.interleave_gate_up(w_gate, w_up)
+            return stacked, stacked.shape[0] // 2
+        return torch.cat([w_gate, w_up], dim=0).contiguous(), w_gate.shape[0]
+
     def gated_linear(self, x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
-        """silu(x Wgate^T) * (x Wup^T) for the stacked matrix [2 I, K]."""
+        """silu(x Wgate^T) * (x Wup^T) for the operand `stack_gate_up` made."""
         inter = w_gate_up.shape[0] // 2
+        block = F.GATE_BLOCK if self.dtype is torch.bfloat16 else inter
         out = torch.empty((x.shape[0], inter), dtype=self.dtype, device=self.device)
+        if self.dtype is torch.bfloat16 and self._pair(x, w_gate_up):
+            F.gemm_bf16_tcgen05_pair(x, w_gate_up, out, self.status, "silu_gate")
+            return out
         parts = self.linear_partials(x, w_gate_up, activation=True)
-        F.swiglu(parts if parts is not None else self.linear(x, w_gate_up, activation=True), out)
+        F.swiglu(parts if parts is not None else self.linear(x, w_gate_up, activation=True), out, block)
         return out

@@ -86,20 +86,27 @@ def qk_norm_rope_cache(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim:
          cache.shape[0] if cache is not None else 0, int(write_cache), ptr(status), stream())
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out = silu(gate_up[:, :I]) * gate_up[:, I:].  gate_up may also be float32
-    [S, M, 2 I]: S partial sums that are added in order first."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
+    """out[M, I] = silu(gate) * up for gate_up [M, 2 I] laid out in blocks of `block` gate
+    columns followed by the `block` "up" columns of the same outputs; block = 0 means I
+    (all gates, then all ups).  gate_up may also be float32 [S, M, 2 I]: S partial sums
+    that are added in order first."""
     on_gpu(gate_up, out)
+    block = block or out.shape[1]
+    if out.shape[1] % block:
+        raise KernelError(f"swiglu: the width {out.shape[1]} is no multiple of the gate block {block}")
     if gate_up.dim() == 3:
         expect(gate_up, torch.float32, "the partial sums")
         if not out.is_contiguous() or gate_up.shape[2] != 2 * out.shape[1] or gate_up.shape[1] != out.shape[0]:
             raise KernelError("swiglu: partial sums [S, M, 2 I] do not fit the output [M, I]")
         call("elementwise", "mlr_swiglu_sliced", ptr(gate_up), gate_up.shape[0], gate_up.stride(0), ptr(out), is_bf16(out),
-             out.shape[0], out.shape[1], stream())
+             out.shape[0], out.shape[1], block, stream())
         return
     if not gate_up.is_contiguous() or not out.is_contiguous() or gate_up.dtype is not out.dtype:
         raise KernelError("swiglu wants contiguous tensors of one dtype")
-    call("elementwise", "mlr_swiglu", ptr(gate_up), ptr(out), is_bf16(out), out.shape[0], out.shape[1], stream())
+    if gate_up.shape != (out.shape[0], 2 * out.shape[1]):
+        raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)} does not fit the output {tuple(out.shape)}")
+    call("elementwise", "mlr_swiglu", ptr(gate_up), ptr(out), is_bf16(out), out.shape[0], out.shape[1], block, stream())
 
 
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -223,6 +230,11 @@ def attention_prefill_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: torch.T
          block_table.stride(0), page_size, q_heads, kv_heads, head_dim, int(window), float(scale), ptr(status), stream())
 
 
+def product_modules(dtype) -> list:
+    """The kernel modules the matrix products of a precision may call."""
+    return ["gemm_f32"] if dtype is torch.float32 else ["gemm_bf16_tcgen05", "gemm_bf16_tcgen05_pair"]
+
+
 def gemm_tcgen05_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
     return (x.dtype is torch.bfloat16 and w.dtype is torch.bfloat16 and x.shape[1] % 8 == 0 and x.shape[1] >= 8
             and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
@@ -262,6 +274,44 @@ def gemm_bf16_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, statu
     else:
         call("gemm_bf16_tcgen05", "mlr_gemm_bf16_tcgen05", ptr(x), x.stride(0), M, ptr(w), w.stride(0), N, K, ptr(out),
              ldo, f32, 0, tile_q, splits, split_stride, 2, ptr(status), stream())
+
+
+PAIR_EPILOGUES = {"bf16": 0, "f32": 1, "add_f32": 2, "silu_gate": 3}
+
+
+def gemm_bf16_tcgen05_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor, epilogue: str) -> None:
+    """The product x[M, K] @ w[N, K]^T of a prompt portion on pairs of SMs (256 x 256 tiles,
+    tcgen05 instructions that span two thread blocks).  `epilogue`: "bf16" or "f32" store the
+    result in out[M, N]; "add_f32" adds it to the float32 out[M, N]; "silu_gate" takes w as
+    blocks of 128 gate rows, each followed by its 128 "up" rows (`interleave_gate_up`), and
+    stores silu(gate) * up in the bfloat16 out[M, N / 2]."""
+    on_gpu(x, w, out, status)
+    if not gemm_tcgen05_applies(x, w):
+        raise KernelError("gemm_bf16_tcgen05_pair: operands must be bfloat16, K-contiguous, 16-byte aligned, K % 8 == 0")
+    M, K = x.shape
+    N = w.shape[0]
+    columns = N // 2 if epilogue == "silu_gate" else N
+    want = torch.bfloat16 if epilogue in ("bf16", "silu_gate") else torch.float32
+    if w.shape[1] != K or tuple(out.shape) != (M, columns) or out.dtype is not want or out.stride(1) != 1:
+        raise KernelError(f"gemm_bf16_tcgen05_pair: {tuple(x.shape)} x {tuple(w.shape)}^T with epilogue {epilogue!r} "
+                          f"does not fit an output {tuple(out.shape)} of {out.dtype}")
+    call("gemm_bf16_tcgen05_pair", "mlr_gemm_bf16_tcgen05_pair", ptr(x), x.stride(0), M, ptr(w), w.stride(0), N, K, ptr(out),
+         out.stride(0), PAIR_EPILOGUES[epilogue], ptr(status), stream())
+
+
+GATE_BLOCK = 128     # rows of the gate that alternate with their "up" rows in the interleaved operand
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """The stacked matrix the gated epilogue of the pair product reads: 128 rows of the gate,
+    then the 128 rows of "up" for the same outputs, and so on; the last block is padded with
+    zero rows, so the result has 2 * ceil(I / 128) * 128 rows."""
+    inter, K = w_gate.shape
+    blocks = -(-inter // GATE_BLOCK)
+    padded = torch.zeros((2, blocks * GATE_BLOCK, K), dtype=w_gate.dtype, device=w_gate.device)
+    padded[0, :inter] = w_gate
+    padded[1, :inter] = w_up
+    return padded.view(2, blocks, GATE_BLOCK, K).transpose(0, 1).reshape(2 * blocks * GATE_BLOCK, K)
 
 
 def k_splits_for(rows: int, K: int, sms: int = 148) -> int:

@@ -27,13 +27,13 @@ _SIGNATURES = {
         "mlr_embed_gather": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
         "mlr_rmsnorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
                         c_float, c_int, c_void_p],
-        "mlr_swiglu_sliced": [c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
+        "mlr_swiglu_sliced": [c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "mlr_residual_add": [c_void_p, c_void_p, c_longlong, c_void_p],
         "mlr_qk_norm_rope_cache": [c_void_p, c_int, c_int, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int,
                                    c_void_p, c_void_p, c_int,
                                    c_float, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                    c_void_p, c_int, c_int, c_void_p, c_void_p],
-        "mlr_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "mlr_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
     "gemm_f32": {
         "mlr_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -58,6 +58,10 @@ _SIGNATURES = {
     "gemm_bf16_tcgen05": {
         "mlr_gemm_bf16_tcgen05": [c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong,
                                   c_int, c_int, c_int, c_int, c_longlong, c_int, c_void_p, c_void_p],
+    },
+    "gemm_bf16_tcgen05_pair": {
+        "mlr_gemm_bf16_tcgen05_pair": [c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong,
+                                       c_int, c_void_p, c_void_p],
     },
     "sampling": {
         "mlr_sample": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],

@@ -55,8 +55,7 @@ class AttentionMixer(Mixer):
         return specs
 
     def kernel_modules(self, dtype) -> List[str]:
-        return ["elementwise"] + A.modules_for(dtype, self.head_dim) + (
-            ["gemm_f32"] if dtype is torch.float32 else ["gemm_bf16_tcgen05"])
+        return ["elementwise"] + A.modules_for(dtype, self.head_dim) + F.product_modules(dtype)
 
     def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
         w = self.spec.weights

@@ -51,7 +51,7 @@ class LinearHead(Part):
         return [WeightSpec(self.spec.weights["weight"], (self.vocab, self.width))]
 
     def kernel_modules(self, dtype) -> List[str]:
-        return ["gemm_f32"] if dtype is torch.float32 else ["gemm_bf16_tcgen05"]
+        return F.product_modules(dtype)
 
     def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
         self.weight = rt.shared_matrix(self.spec.weights["weight"], tensors)

@@ -1,10 +1,12 @@
 """SiLU-gated feed-forward: `down(silu(gate(x)) * up(x))`, no bias
 (src/minillm/runtime.cpp:323-335; src/minillm/cuda/layer.cpp:65-70).
 
-The gate and up matrices are stacked into one [2 I, width] operand at bind time,
-so one product yields both; the kernel that applies the gate reads the two halves
-of each row.  Parameters: hidden_size, intermediate_size.  Weights: "gate", "up"
-[I, width], "down" [width, I].
+The gate and up matrices are stacked into one operand at bind time, so one product
+yields both, and the gate is applied by that product's epilogue or by the kernel that
+reads its result; how the rows are stacked is the runtime's business
+(`Runtime.stack_gate_up`), which may round the inner width up (the extra activations
+are zero, and "down" gets zero columns for them).  Parameters: hidden_size,
+intermediate_size.  Weights: "gate", "up" [I, width], "down" [width, I].
 """
 from __future__ import annotations
 
@@ -32,12 +34,16 @@ class SwiGLU(FeedForward):
                 WeightSpec(w["down"], (self.width, self.inter))]
 
     def kernel_modules(self, dtype) -> List[str]:
-        return ["elementwise"] + (["gemm_f32"] if dtype is torch.float32 else ["gemm_bf16_tcgen05"])
+        return ["elementwise"] + F.product_modules(dtype)
 
     def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
         w = self.spec.weights
-        self.w_gate_up = torch.cat([rt.matrix(tensors[w["gate"]]), rt.matrix(tensors[w["up"]])], dim=0).contiguous()
+        self.w_gate_up, inner = rt.stack_gate_up(tensors[w["gate"]], tensors[w["up"]])
         self.w_down = rt.matrix(tensors[w["down"]])
+        if inner != self.inter:
+            padded = torch.zeros((self.width, inner), dtype=self.w_down.dtype, device=self.w_down.device)
+            padded[:, :self.inter] = self.w_down
+            self.w_down = padded
 
     def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
         rt = step.rt

@@ -205,6 +205,84 @@ def test_gemm_bf16_tcgen05_every_tile_width():
         F().gemm_bf16_tcgen05(x[:, :100].contiguous(), w[:, :100].contiguous(), torch.empty(400, 700, device=DEV), status())
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (257, 512, 4096), (300, 700, 136), (1000, 1032, 520), (2048, 6144, 4096),
+                                   (130, 24, 72), (600, 256, 12288)])
+def test_gemm_bf16_tcgen05_pair_and_its_epilogues(M, N, K):
+    """The two-SM product: plain stores, the add into a float32 matrix, and the SiLU gate over
+    interleaved gate/up rows, beside float32 products of the same bfloat16 values."""
+    x = (torch.randn(M, K, generator=gen(0)) * 0.5).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=gen(1)) * 0.1).to(torch.bfloat16).to(DEV)
+    want = x.float() @ w.float().T
+    scale = 1 + want.abs().max().item()
+    st = status()
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    F().gemm_bf16_tcgen05_pair(x, w, out, st, "bf16")
+    assert st.item() == 0 and torch.allclose(out.float(), want, atol=2e-2 * scale, rtol=2e-2)
+    out32 = torch.full((M, N), float("nan"), device=DEV)
+    F().gemm_bf16_tcgen05_pair(x, w, out32, st, "f32")
+    assert st.item() == 0 and torch.allclose(out32, want, atol=1e-3 * scale, rtol=1e-3)
+    # Adding into a matrix: one float32 rounding on top of the plain result, and nothing outside.
+    wide = torch.randn(M + 1, N + 8, generator=gen(2)).to(DEV)
+    before = wide.clone()
+    F().gemm_bf16_tcgen05_pair(x, w, wide[:M, :N], st, "add_f32")
+    assert st.item() == 0 and torch.equal(wide[:M, :N], before[:M, :N] + out32)
+    assert torch.equal(wide[M:], before[M:]) and torch.equal(wide[:, N:], before[:, N:])
+    # Operands that are views with wider row strides.
+    padded = torch.zeros(M, K + 64, dtype=torch.bfloat16, device=DEV)
+    padded[:, :K] = x
+    again = torch.empty_like(out32)
+    F().gemm_bf16_tcgen05_pair(padded[:, :K], w, again, st, "f32")
+    assert torch.equal(again, out32)
+    # The gate: w as gate rows then up rows, interleaved in blocks of 128.
+    if N % 2 == 0:
+        inter = N // 2
+        stacked = F().interleave_gate_up(w[:inter], w[inter:])
+        inner = stacked.shape[0] // 2
+        assert inner % 128 == 0 and inner - inter < 128
+        act = torch.full((M, inner), float("nan"), dtype=torch.bfloat16, device=DEV)
+        F().gemm_bf16_tcgen05_pair(x, stacked, act, st, "silu_gate")
+        g, u = out[:, :inter].float(), out[:, inter:].float()        # the bfloat16 gate and up, as the unfused path has them
+        gated = g / (1 + torch.exp(-g)) * u
+        assert st.item() == 0 and torch.allclose(act[:, :inter].float(), gated, atol=1e-2 * (1 + gated.abs().max().item()), rtol=2e-2)
+        assert (act[:, inter:] == 0).all()
+        # The kernel that applies the gate to a stored product reads the same interleaving.
+        product = torch.empty(M, 2 * inner, dtype=torch.bfloat16, device=DEV)
+        F().gemm_bf16_tcgen05_pair(x, stacked, product, st, "bf16")
+        unfused = torch.empty(M, inner, dtype=torch.bfloat16, device=DEV)
+        F().swiglu(product, unfused, 128)
+        assert torch.allclose(unfused.float(), act.float(), atol=1e-2 * (1 + gated.abs().max().item()), rtol=2e-2)
+
+
+def test_gemm_bf16_tcgen05_pair_refuses_what_it_cannot_do():
+    from mini_llm_runtime_b200.ops.native import KernelError
+    x = torch.zeros(300, 100, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(512, 100, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(KernelError, match="K % 8"):
+        F().gemm_bf16_tcgen05_pair(x, w, torch.empty(300, 512, dtype=torch.bfloat16, device=DEV), status(), "bf16")
+    x, w = x[:, :96].contiguous(), w[:, :96].contiguous()
+    with pytest.raises(KernelError, match="does not fit"):
+        F().gemm_bf16_tcgen05_pair(x, w, torch.empty(300, 512, device=DEV), status(), "bf16")
+    with pytest.raises(KernelError, match="256"):
+        F().gemm_bf16_tcgen05_pair(x, w[:300], torch.empty(300, 150, dtype=torch.bfloat16, device=DEV), status(), "silu_gate")
+
+
+@pytest.mark.parametrize("rows,inter,block", [(3, 256, 128), (5, 384, 128), (2, 48, 16), (4, 21, 7)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_over_interleaved_blocks(rows, inter, block, dtype):
+    gu = (torch.randn(rows, 2 * inter, generator=gen(0)) * 3).to(dtype)
+    blocks = gu.view(rows, inter // block, 2, block).double()
+    g, u = blocks[:, :, 0].reshape(rows, inter), blocks[:, :, 1].reshape(rows, inter)
+    want = g / (1 + torch.exp(-g)) * u
+    tol = 1e-6 if dtype is torch.float32 else 1e-2
+    out = torch.empty(rows, inter, dtype=dtype, device=DEV)
+    F().swiglu(gu.to(DEV), out, block)
+    assert torch.allclose(out.double().cpu(), want, rtol=tol, atol=tol)
+    # From partial sums.
+    parts = torch.stack([gu.float() * 0.25, gu.float() * 0.75]).to(DEV)
+    F().swiglu(parts, out, block)
+    assert torch.allclose(out.double().cpu(), want, rtol=tol, atol=tol)
+
+
 # ------------------------------------------------------------------ paged cache helpers
 def stored_row(x, dtype):
     """Rows [T, Hkv, D] as the cache stores them: bfloat16 caches with a head size of 64,
