@@ -7,20 +7,25 @@ the serving path: matrices, activations and the cache are bfloat16, products
 accumulate in float32.  In both, the residual stream, norms, softmax, rotation and
 logits are float32.
 
-Which kernel a bfloat16 product takes depends on its rows and on what its result is.
-From `pair_rows` rows on (prompt portions) every product runs on the package's two-SM
-tcgen05 kernel (`csrc/kernels/gemm_bf16_tcgen05_pair.cu`), whose epilogue also does what
-would otherwise be a kernel of its own: a product that ends a sub-layer (o_proj, down_proj)
-adds into the float32 residual stream, and the gate/up product applies the SiLU gate (the
-feed-forward keeps its two matrices interleaved in blocks of 128 rows for that).  With up to
-`decode_rows` rows, a product that ends a sub-layer and the head run on the one-block
-tcgen05 kernel (`csrc/kernels/gemm_bf16_tcgen05.cu`): the weight matrix takes the 128-row
-side of the instruction, K is cut into ranges so that a small matrix still occupies every
-SM, and the kernel that reads the result adds the ranges' partial sums.  What is left goes
-to the vendor library (cuBLAS through `torch.mm` / `torch.addmm`), as the reference sends
-all of its products to cuBLAS (src/minillm/cuda/matrix.cpp:30-36): the few-row products whose
-result is an activation (q/k/v, gate/up), which the library writes in bfloat16 at once, and
-steps between the two row counts.  `own_products_only()` takes the library out altogether.
+Which kernel a bfloat16 product takes depends on its rows and on what its result is; each
+choice below is the faster one as measured in whole steps of the 8B sizes.
+  * The gate/up product of a prompt portion of `pair_rows` rows or more runs on the package's
+    two-SM tcgen05 kernel (`csrc/kernels/gemm_bf16_tcgen05_pair.cu`), which applies the SiLU
+    gate in its epilogue: the product never goes to memory (the feed-forward keeps its two
+    matrices interleaved in blocks of 128 rows for that).
+  * With up to `decode_rows` rows, a product that ends a sub-layer (o_proj, down_proj) and the
+    head run on the one-block tcgen05 kernel (`csrc/kernels/gemm_bf16_tcgen05.cu`): the
+    weight matrix takes the 128-row side of the instruction, K is cut into ranges so that a
+    small matrix still occupies every SM, and the kernel that reads the result adds the
+    ranges' partial sums.
+  * What is left goes to the vendor library (cuBLAS through `torch.mm` / `torch.addmm`), as the
+    reference sends all of its products to cuBLAS (src/minillm/cuda/matrix.cpp:30-36): the
+    few-row products whose result is an activation (q/k/v, gate/up), which the library writes
+    in bfloat16 at once, and the plain products of prompt portions; one that ends a sub-layer
+    adds its result into the residual stream in the library's epilogue.
+`own_products_only()` takes the library out altogether: the two-SM kernel then runs every
+product of 256 rows or more (adding into the residual stream in its own epilogue), the
+one-block kernel the rest.
 """
 from __future__ import annotations
 
@@ -45,9 +50,11 @@ class Runtime:
         torch.backends.cudnn.allow_tf32 = False
         self.use_tcgen05 = True       # bf16 products on the package's tcgen05/TMA kernel
         self.tcgen05_prefill = False  # the one-block kernel also for the row counts the vendor library takes by default
-        # From this many rows on a product runs on the two-SM kernel (256 x 256 tiles; its fused
-        # epilogues make up for the rows a smaller portion leaves empty in a tile).
-        self.pair_rows = 256
+        # From this many rows on the gate/up product runs on the two-SM kernel with the gate in its
+        # epilogue (against the library's product and a gate kernel it ties at 1024 rows and wins
+        # beyond; in a 2048-token step of the 8B sizes it saves 4 % of the step).
+        self.pair_rows = 1024
+        self.pair_everything = False  # every product of 256 rows or more on the two-SM kernel
         self.tcgen05_attention = True  # prompt portions of 65 rows and more on the tcgen05 attention kernel
         # Up to this many rows a product runs on the own kernel (swapped operands, split K, partial
         # sums added by the kernel that reads them).  Measured in the decode step of the 8B sizes:
@@ -77,6 +84,8 @@ class Runtime:
         self.decode_rows = 64
         self.own_activation_products = True
         self.tcgen05_prefill = True
+        self.pair_everything = True
+        self.pair_rows = 256
 
     @property
     def is_bf16(self) -> bool:
@@ -120,9 +129,9 @@ class Runtime:
     def _tcgen05_ok(self, x: torch.Tensor, w: torch.Tensor) -> bool:
         return self.use_tcgen05 and self.status is not None and F.gemm_tcgen05_applies(x, w)
 
-    def _pair(self, x: torch.Tensor, w: torch.Tensor) -> bool:
+    def _pair(self, x: torch.Tensor, w: torch.Tensor, gated: bool = False) -> bool:
         """Whether this bf16 product runs on the two-SM kernel."""
-        return x.shape[0] >= self.pair_rows and self._tcgen05_ok(x, w)
+        return (gated or self.pair_everything) and x.shape[0] >= self.pair_rows and self._tcgen05_ok(x, w)
 
     def _own_gemm(self, x: torch.Tensor, w: torch.Tensor) -> bool:
         """Whether this bf16 product runs on the one-block tcgen05 kernel: always for the few
@@ -201,7 +210,7 @@ class Runtime:
         inter = w_gate_up.shape[0] // 2
         block = F.GATE_BLOCK if self.dtype is torch.bfloat16 else inter
         out = torch.empty((x.shape[0], inter), dtype=self.dtype, device=self.device)
-        if self.dtype is torch.bfloat16 and self._pair(x, w_gate_up):
+        if self.dtype is torch.bfloat16 and self._pair(x, w_gate_up, gated=True):
             F.gemm_bf16_tcgen05_pair(x, w_gate_up, out, self.status, "silu_gate")
             return out
         parts = self.linear_partials(x, w_gate_up, activation=True)
