@@ -4,9 +4,14 @@ Qwen3-8B layer sizes with few layers, bracketed by cudaProfilerStart/Stop.
     python -m mini_llm_runtime_b200.profiling decode  [--layers 2] [--batch 8] [--context 8192] [--steps 2]
     python -m mini_llm_runtime_b200.profiling prefill [--layers 2] [--tokens 2048] [--mma-sync-attention]
     python -m mini_llm_runtime_b200.profiling attention [--page-size 64]
+    python -m mini_llm_runtime_b200.profiling products  [--tokens 2048]
 
 `attention` times the two bfloat16 attention kernels alone (CUDA events, no model) over a
 range of prompt lengths, contexts, batch sizes and head sizes and prints two tables.
+`products` does the same for the matrix products of a prompt portion (`--tokens` rows) at
+the 8B layer sizes: the two-SM tcgen05 kernel with each epilogue, the one-block kernel and
+the vendor library, each timed over a loop with the L2 flushed between launches; the profiled
+region holds three launches of the two-SM kernel with the gate epilogue.
 
 Meant to run under `ncu --profile-from-start off ...`: with two layers it holds about
 4 GB on the device and launches a few dozen kernels inside the profiled region, so a
@@ -30,7 +35,7 @@ QWEN3_8B = {
 
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("mode", choices=["decode", "prefill", "attention"])
+    ap.add_argument("mode", choices=["decode", "prefill", "attention", "products"])
     ap.add_argument("--layers", type=int, default=2)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
@@ -44,6 +49,9 @@ def main() -> int:
 
     if args.mode == "attention":
         return attention_tables(args.page_size if args.page_size != 16 else 64)
+
+    if args.mode == "products":
+        return product_table(args.tokens)
 
     from .engine.loading import random_model
     from .engine.model import CacheConfig, StepEntry
@@ -109,6 +117,72 @@ def main() -> int:
         torch.cuda.synchronize()
         torch.cuda.cudart().cudaProfilerStop()
     model.check_status()
+    return 0
+
+
+def product_table(rows: int) -> int:
+    """The products of one layer of the 8B sizes for `rows` tokens, each kernel alone: median
+    of 20 launches after 3, a 256 MB buffer written between launches so that operands come
+    from DRAM."""
+    from .ops import functions as F
+    dev = "cuda:0"
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn, reps=20):
+        for _ in range(3):
+            fn()
+        times = []
+        for _ in range(reps):
+            flush.zero_()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            fn()
+            end.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(end) * 1e3)
+        return sorted(times)[len(times) // 2]
+
+    H, I = QWEN3_8B["hidden_size"], QWEN3_8B["intermediate_size"]
+    qkv = (QWEN3_8B["num_attention_heads"] + 2 * QWEN3_8B["num_key_value_heads"]) * QWEN3_8B["head_dim"]
+    gen = torch.Generator(device=dev).manual_seed(0)
+    print(f"| product ({rows} rows) | library | one-block tcgen05 | two-SM tcgen05 | two-SM TFLOP/s |")
+    print("| --- | ---: | ---: | ---: | ---: |")
+    gated = None
+    for name, N, K in (("q/k/v", qkv, H), ("o_proj", H, QWEN3_8B["num_attention_heads"] * QWEN3_8B["head_dim"]),
+                       ("gate/up", 2 * I, H), ("down_proj", H, I)):
+        x = torch.randn(rows, K, device=dev, generator=gen).bfloat16()
+        w = (torch.randn(N, K, device=dev, generator=gen) * 0.02).bfloat16()
+        out = torch.empty(rows, N, dtype=torch.bfloat16, device=dev)
+        lib = timed(lambda: torch.mm(x, w.t(), out=out))
+        one = timed(lambda: F.gemm_bf16_tcgen05(x, w, out, status))
+        pair = timed(lambda: F.gemm_bf16_tcgen05_pair(x, w, out, status, "bf16"))
+        print(f"| {name} {N} x {K}, bfloat16 out | {lib:.1f} | {one:.1f} | {pair:.1f} | {2 * rows * N * K / pair / 1e6:.0f} |")
+        if name in ("o_proj", "down_proj"):
+            h = torch.zeros(rows, N, device=dev)
+            lib = timed(lambda: torch.addmm(h, x, w.t(), out_dtype=torch.float32, out=h))
+            pair = timed(lambda: F.gemm_bf16_tcgen05_pair(x, w, h, status, "add_f32"))
+            print(f"| {name}, added into the float32 stream | {lib:.1f} | | {pair:.1f} | {2 * rows * N * K / pair / 1e6:.0f} |")
+        if name == "gate/up":
+            stacked = F.interleave_gate_up(w[:I], w[I:])
+            act = torch.empty(rows, I, dtype=torch.bfloat16, device=dev)
+
+            def library_then_gate():
+                torch.mm(x, stacked.t(), out=out)
+                F.swiglu(out, act, F.GATE_BLOCK)
+
+            gated = lambda: F.gemm_bf16_tcgen05_pair(x, stacked, act, status, "silu_gate")
+            lib, pair = timed(library_then_gate), timed(gated)
+            print(f"| gate/up with the SiLU gate (library: product, then gate kernel) | {lib:.1f} | | {pair:.1f} | "
+                  f"{2 * rows * N * K / pair / 1e6:.0f} |")
+            torch.cuda.synchronize()
+            torch.cuda.cudart().cudaProfilerStart()
+            for _ in range(3):
+                gated()
+            torch.cuda.synchronize()
+            torch.cuda.cudart().cudaProfilerStop()
+    if status.item():
+        raise RuntimeError(f"a kernel reported status {status.item()}")
     return 0
 
 
