@@ -49,6 +49,12 @@ QWEN3_8B = {
     "tie_word_embeddings": False, "use_sliding_window": False, "hidden_act": "silu", "attention_bias": False,
     "torch_dtype": "bfloat16",
 }
+# The two other sizes the baseline names: (configuration, weights seed, context, batch of the headline, largest batch).
+QWEN3_06B = dict(QWEN3_8B, hidden_size=1024, num_hidden_layers=28, num_attention_heads=16, num_key_value_heads=8,
+                 intermediate_size=3072, tie_word_embeddings=True)
+QWEN3_32B = dict(QWEN3_8B, hidden_size=5120, num_hidden_layers=64, num_attention_heads=64, num_key_value_heads=8,
+                 intermediate_size=25600)
+MODELS = {"qwen3-8b": (QWEN3_8B, 2, 8192, 64), "qwen3-0.6b": (QWEN3_06B, 3, 4096, 64), "qwen3-32b": (QWEN3_32B, 4, 4096, 32)}
 QUICK = dict(QWEN3_8B, hidden_size=512, num_hidden_layers=4, num_attention_heads=8, num_key_value_heads=2,
              head_dim=64, intermediate_size=1024, vocab_size=4099, max_position_embeddings=4096)
 
@@ -136,6 +142,35 @@ def matmul_params(cfg, layers):
     return per_layer * layers, cfg["vocab_size"] * H
 
 
+def serving(args, cfg, model, prompt_of, gen) -> int:
+    """The baseline's mixed workload: 64 requests arrive at once, prompt lengths uniform in
+    [16, 2048], 256 generated tokens each, greedy, through the Python entry point (host token
+    ids in and out; admission, chunked prompts beside decoding requests, pages given back)."""
+    import torch
+    from mini_llm_runtime_b200.engine.api import LLM
+    requests, new_tokens = 64, 256
+    lengths = torch.randint(16, 2049, (requests,), generator=gen).tolist()
+    prompts = [prompt_of(n) for n in lengths]
+    llm = LLM(model, max_batch_tokens=4096, prefill_chunk=2048)
+    llm.generate(prompts[:4], max_tokens=8, ignore_eos=True)            # warm-up: kernels, graphs of small batches
+    torch.cuda.synchronize()
+    steps_before = llm.engine.steps
+    t0 = time.perf_counter()
+    results = llm.generate(prompts, max_tokens=new_tokens, ignore_eos=True)
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    assert all(len(r.token_ids) == new_tokens for r in results)
+    steps = llm.engine.steps - steps_before
+    print(json.dumps({
+        "metric": "generated tok/s, 64 requests at once, prompts U[16, 2048], 256 tokens each, through LLM.generate",
+        "value": requests * new_tokens / seconds, "unit": "tokens/s", "seconds": seconds, "steps": steps,
+        "ms_per_step": seconds * 1e3 / steps, "prompt_tokens": sum(lengths),
+        "all_tokens_per_s": (sum(lengths) + requests * new_tokens) / seconds,
+        "model": args.model, "layers": cfg["num_hidden_layers"], "dtype": "bf16", "data": "synthetic",
+        "max_requests": model.cache.max_requests, "page_size": args.page_size}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -143,10 +178,15 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--context", type=int, default=0, help="default: the context length the baseline names for the model")
+    ap.add_argument("--model", default="qwen3-8b", choices=sorted(MODELS),
+                    help="layer sizes; the default is the configuration the headline is quoted on")
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--quick", action="store_true", help="a small model, for checking this script")
     ap.add_argument("--no-points", action="store_true")
+    ap.add_argument("--serving", action="store_true",
+                    help="instead of the headline: the baseline's mixed workload through LLM.generate (64 requests, prompts of "
+                         "16 to 2048 random tokens, 256 generated tokens each); prints one JSON line of its own")
     ap.add_argument("--own-products", action="store_true",
                     help="every matrix product on the package's tcgen05 kernel, none on the vendor library (slower)")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (the baseline's configuration has 16; 64 is a little faster)")
@@ -166,26 +206,30 @@ def main() -> int:
     from mini_llm_runtime_b200.ops import native
     from mini_llm_runtime_b200.sampling.sampler import Sampler, SamplingParams
 
-    cfg = dict(QUICK if args.quick else QWEN3_8B)
+    model_cfg, weights_seed, model_context, largest_batch = MODELS[args.model]
+    cfg = dict(QUICK if args.quick else model_cfg)
+    args.context = args.context or model_context
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
     layers = cfg["num_hidden_layers"]
     context, page = args.context, args.page_size
     horizon = args.steps + args.warmup + 8
-    batches = [args.batch] if args.no_points else sorted({1, args.batch, 64})
+    batches = [args.batch] if args.no_points else sorted({1, args.batch, largest_batch})
     max_batch = max(batches)
     pages = max_batch * ((context + horizon + page - 1) // page + 1)
     pk = peaks()
 
     torch.manual_seed(0)
-    model = random_model(cfg, seed=2, dtype="bfloat16",
+    model = random_model(cfg, seed=weights_seed, dtype="bfloat16",
                          cache=CacheConfig(page_size=page, num_pages=pages, max_requests=max_batch,
                                            max_model_len=context + horizon + page, fill_nan=False))
     if args.own_products:
         model.rt.own_products_only()
     gen = torch.Generator().manual_seed(1234)
     prompt_of = lambda n: torch.randint(0, cfg["vocab_size"], (n,), generator=gen).tolist()
+    if args.serving:
+        return serving(args, cfg, model, prompt_of, gen)
     layer_params, head_params = matmul_params(cfg, layers)
     weight_bytes = 2 * (layer_params + head_params)
     kv_bytes_per_token = model.cache_bytes_per_token()
@@ -269,10 +313,10 @@ def main() -> int:
     points = {}
     if not args.no_points:
         short = max(4, args.steps // 4)
-        for b in (1, 64):
+        for b in (1, largest_batch):
             if b != args.batch:
                 points[f"decode_b{b}"] = decode_rate(b, context, short, 3)[0]
-        for b in (1, 8, 64):
+        for b in (1, 8, largest_batch):
             points[f"decode_b{b}_ctx2048"] = decode_rate(b, min(2048, context), short, 3)[0]
 
     # ---------------------------------------------------------------- end to end through the engine
@@ -295,15 +339,16 @@ def main() -> int:
     e2e = {"value": args.batch / e2e_ms * 1e3, "unit": "tokens/s", "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": model.last_h2d_bytes, "d2h_bytes_per_step": 4 * (args.batch + 1)}
 
-    config = {"model": "Qwen3-8B sizes, random weights (seed 2)" if not args.quick else "quick check model",
+    name = {"qwen3-8b": "Qwen3-8B", "qwen3-0.6b": "Qwen3-0.6B", "qwen3-32b": "Qwen3-32B"}[args.model]
+    config = {"model": f"{name} sizes, random weights (seed {weights_seed})" if not args.quick else "quick check model",
               "layers": layers, "layers_of_model": full_layers, "hidden": cfg["hidden_size"],
               "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
               "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": args.batch,
               "seq_len": context, "context_len": context, "page_size": page, "prefill_tokens": T,
-              "parallelism": "single_gpu", "products": "own kernel only" if args.own_products else "own kernel and vendor library", "l2": "inputs>L2 (15 GB of weights per step), no flush",
+              "parallelism": "single_gpu", "products": "own kernel only" if args.own_products else "own kernel and vendor library", "l2": f"inputs>L2 ({weight_bytes / 1e9:.1f} GB of weights per step), no flush",
               "weight_gb": round(weight_bytes / 1e9, 2), "kv_kb_per_token": kv_bytes_per_token / 1024}
     print(json.dumps({
-        "metric": "decode tok/s (Qwen3-8B sizes, batch 8, context 8192, bf16)", "value": value, "unit": "tokens/s",
+        "metric": f"decode tok/s ({name} sizes, batch {args.batch}, context {context}, bf16)", "value": value, "unit": "tokens/s",
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
         "config": config, "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "prefill": prefill,
