@@ -675,7 +675,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
 }
 
 // ---------------------------------------------------------------- prefill: flash attention
-// grid = (tiles, q_heads), 160 threads.  tiles[i] = {segment, first token of the 64-row tile
+// grid = (q_heads, tiles), 160 threads.  tiles[i] = {segment, first token of the 64-row tile
 // within the segment}.  Warp 4 copies the key tiles (copy_warp); compute warp w owns rows
 // 16w .. 16w+15 of the query tile and walks the keys up to the diagonal with a running
 // softmax.  No block-wide barrier in the loop; waits are bounded.
@@ -694,8 +694,10 @@ __global__ void __launch_bounds__(kDecodeThreads) __maxnreg__(DMAX <= 128 ? 168 
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) unsigned long long barriers[2 * kDecodeStages];
     __shared__ int fault;
-    const int head = blockIdx.y;
-    const int segment = tiles[blockIdx.x * 2], tile_token = tiles[blockIdx.x * 2 + 1];
+    // Blocks start in the order of their index, x fastest: all heads of the first tile (the one
+    // with the longest walk over the keys, as the caller sorts them), then all heads of the next.
+    const int head = blockIdx.x;
+    const int segment = tiles[blockIdx.y * 2], tile_token = tiles[blockIdx.y * 2 + 1];
     const int first_row = segment_info[segment * 4 + 0], count = segment_info[segment * 4 + 1];
     const int start = segment_info[segment * 4 + 2];
     const int kv_head = head / (q_heads / kv_heads);
@@ -938,7 +940,8 @@ MLR_API int mlr_attention_prefill_bf16(const void* q, int ldq, void* out, int ld
     if (int e = check_common("attention_prefill_bf16", q_heads, kv_heads, head_dim, page_size, num_pages, window, ldq, ldo, scale)) return e;
     MLR_REQUIRE(n_tiles >= 0, "attention_prefill_bf16: negative tile count");
     if (n_tiles == 0) return 0;
-    const dim3 grid(n_tiles, q_heads);
+    MLR_REQUIRE(n_tiles <= 65535, "attention_prefill_bf16: %d tiles in one launch, the most is 65535", n_tiles);
+    const dim3 grid(q_heads, n_tiles);
 #define MLR_LAUNCH(DMAX, BLOCKS)                                                                                   \
     do {                                                                                                           \
         const size_t tile = BLOCKS ? Tile<DMAX>::kBytes : PaddedTile<DMAX>::kBytes;                                \

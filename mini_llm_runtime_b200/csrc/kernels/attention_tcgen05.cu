@@ -108,8 +108,12 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tcgen05_kernel(
     const uint32_t bar_base = smem_u32(barriers);
     auto bar = [&](int which, int s = 0) { return bar_base + (which + s) * 8; };
 
-    const int head = blockIdx.y;
-    const int segment = tiles[blockIdx.x * 2], tile_token = tiles[blockIdx.x * 2 + 1];
+    // Blocks start in the order of their index, x fastest: all heads of the first tile (the one
+    // with the longest walk over the keys, as the caller sorts them), then all heads of the next.
+    // The long walks so begin first and the short ones fill the gaps at the end; the heads of a
+    // kv head run side by side and share its keys in L2.
+    const int head = blockIdx.x;
+    const int segment = tiles[blockIdx.y * 2], tile_token = tiles[blockIdx.y * 2 + 1];
     const int first_row = segment_info[segment * 4 + 0], count = segment_info[segment * 4 + 1];
     const int start = segment_info[segment * 4 + 2];
     const int kv_head = head / (q_heads / kv_heads);
@@ -406,7 +410,7 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, void* out, int l
             return mlr_fail("attention_prefill_tcgen05: cannot use %zu bytes of shared memory: %s", bytes, cudaGetErrorString(e));
         allowed_device = device;
     }
-    mlr_launch((prefill_tcgen05_kernel<D>), dim3(n_tiles, q_heads), dim3(kThreads), bytes, stream, map_q, map_kv,
+    mlr_launch((prefill_tcgen05_kernel<D>), dim3(q_heads, n_tiles), dim3(kThreads), bytes, stream, map_q, map_kv,
                static_cast<__nv_bfloat16*>(out), ldo, num_pages, tiles, segment_info, block_table, table_stride, page_size,
                q_heads, kv_heads, window, scale, status);
     return mlr_launched("attention_prefill_tcgen05");
@@ -438,7 +442,7 @@ MLR_API int mlr_attention_prefill_tcgen05(const void* q, int ldq, int q_rows, vo
     MLR_REQUIRE(reinterpret_cast<uintptr_t>(q) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0 &&
                     reinterpret_cast<uintptr_t>(cache) % 16 == 0,
                 "attention_prefill_tcgen05: q, out and the cache must be 16-byte aligned");
-    MLR_REQUIRE(n_tiles >= 0 && q_heads <= 65535, "attention_prefill_tcgen05: bad tile count or too many heads");
+    MLR_REQUIRE(n_tiles >= 0 && n_tiles <= 65535, "attention_prefill_tcgen05: %d tiles in one launch, the most is 65535", n_tiles);
     if (n_tiles == 0) return 0;
     EncodeTiled encode = encode_tiled();
     MLR_REQUIRE(encode != nullptr, "attention_prefill_tcgen05: the driver does not offer cuTensorMapEncodeTiled");
