@@ -69,6 +69,7 @@ class Runtime:
         # result at once, and the decode step is 3-4 % faster that way at 1 to 8 rows.
         self.own_activation_products = False
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.pair_min_tiles = self.sm_count   # ... and only with at least this many 256 x 256 tiles
         self._splits = {}
         self._counters = None
         self._retired = []
@@ -131,7 +132,12 @@ class Runtime:
 
     def _pair(self, x: torch.Tensor, w: torch.Tensor, gated: bool = False) -> bool:
         """Whether this bf16 product runs on the two-SM kernel."""
-        return (gated or self.pair_everything) and x.shape[0] >= self.pair_rows and self._tcgen05_ok(x, w)
+        if not (gated or self.pair_everything) or x.shape[0] < self.pair_rows or not self._tcgen05_ok(x, w):
+            return False
+        # Fewer 256 x 256 tiles than SMs leave pairs idle (a small model's matrices); the library's
+        # smaller tiles do better then.
+        tiles = -(-x.shape[0] // 256) * -(-w.shape[0] // 256)
+        return self.pair_everything or tiles >= self.pair_min_tiles
 
     def _own_gemm(self, x: torch.Tensor, w: torch.Tensor) -> bool:
         """Whether this bf16 product runs on the one-block tcgen05 kernel: always for the few
