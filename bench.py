@@ -215,6 +215,13 @@ def main() -> int:
     layers = cfg["num_hidden_layers"]
     context, page = args.context, args.page_size
     horizon = args.steps + args.warmup + 8
+    # The largest batch of the extra points must fit the memory beside the weights: halve it until it does.
+    head_dim, kv_heads = cfg["head_dim"], cfg["num_key_value_heads"]
+    cache_per_token = 2 * 2 * kv_heads * head_dim * layers
+    weights_estimate = 2 * sum(matmul_params(cfg, layers)) + (0 if cfg["tie_word_embeddings"] else 2 * cfg["vocab_size"] * cfg["hidden_size"])
+    room = 0.85 * torch.cuda.get_device_properties(0).total_memory - weights_estimate
+    while largest_batch > args.batch and largest_batch * (context + horizon + page) * cache_per_token > room:
+        largest_batch //= 2
     batches = [args.batch] if args.no_points else sorted({1, args.batch, largest_batch})
     max_batch = max(batches)
     pages = max_batch * ((context + horizon + page - 1) // page + 1)
