@@ -118,7 +118,9 @@ class Model:
         # the cache is allocated (a wider bucket plans key splits that short contexts leave idle).
         self.graph_bucket_blocks = 64
         self.max_graphs = 48
+        self.graph_after = 2        # steps of a shape that run kernel by kernel before the shape is captured
         self._graphs = {}
+        self._graph_uses = {}
         self._graph_pool = None
         self.graph_launches = 0
 
@@ -264,7 +266,15 @@ class Model:
             max_context = max(s.start + s.count for s in segments)
             columns = (max_context + page - 1) // page
             if graphed:
-                columns = min(-(-columns // self.graph_bucket_blocks) * self.graph_bucket_blocks, self.cache.max_blocks)
+                # A shape is captured once it has come `graph_after` times: capturing costs several
+                # steps' time, which a batch size that lasts a step or two (requests ending one
+                # after the other) never pays back.
+                bucketed = min(-(-columns // self.graph_bucket_blocks) * self.graph_bucket_blocks, self.cache.max_blocks)
+                seen = self._graph_uses.get((rows, bucketed), 0)
+                self._graph_uses[(rows, bucketed)] = seen + 1
+                graphed = (rows, bucketed) in self._graphs or seen >= self.graph_after
+                if graphed:
+                    columns = bucketed
             n_groups = len(self.group_windows)
             # One packed int32 buffer: ids | positions | segment_of_row | info[n,4] | slots | want | tables
             sizes = [rows, rows, rows, 4 * n, n, len(want_rows)] + [n * columns] * n_groups
