@@ -71,6 +71,7 @@ class Runtime:
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.pair_min_tiles = self.sm_count   # ... and only with at least this many 256 x 256 tiles
         self._splits = {}
+        self._views = {}
         self._counters = None
         self._retired = []
         self.status = None        # the model's device status word (set at bind time)
@@ -127,6 +128,16 @@ class Runtime:
         return self._counters
 
     # ---- y = x @ w.T
+    def _transposed(self, w: torch.Tensor) -> torch.Tensor:
+        """The view w.T the library takes, made once per weight matrix (an eager step calls
+        for it some hundred times)."""
+        view = self._views.get(id(w))
+        if view is None or view[0] is not w:
+            if len(self._views) >= 4096:      # someone multiplies by matrices that come and go: do not hold on to them
+                self._views.clear()
+            view = self._views[id(w)] = (w, w.t())
+        return view[1]
+
     def _tcgen05_ok(self, x: torch.Tensor, w: torch.Tensor) -> bool:
         return self.use_tcgen05 and self.status is not None and F.gemm_tcgen05_applies(x, w)
 
@@ -142,7 +153,7 @@ class Runtime:
     def _own_gemm(self, x: torch.Tensor, w: torch.Tensor) -> bool:
         """Whether this bf16 product runs on the one-block tcgen05 kernel: always for the few
         rows of a decode step; beyond those only when `tcgen05_prefill` is set."""
-        return self._tcgen05_ok(x, w) and (x.shape[0] <= self.decode_rows or self.tcgen05_prefill)
+        return (x.shape[0] <= self.decode_rows or self.tcgen05_prefill) and self._tcgen05_ok(x, w)
 
     def linear(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                activation: bool = False) -> torch.Tensor:
@@ -162,8 +173,8 @@ class Runtime:
             F.gemm_bf16_tcgen05(x, w, out, self.status)
             return out
         if out_dtype is torch.bfloat16:
-            return torch.mm(x, w.t())
-        return torch.mm(x, w.t(), out_dtype=out_dtype)
+            return torch.mm(x, self._transposed(w))
+        return torch.mm(x, self._transposed(w), out_dtype=out_dtype)
 
     def linear_partials(self, x: torch.Tensor, w: torch.Tensor, activation: bool = False) -> Optional[torch.Tensor]:
         """For the few rows of a decode step: the product as float32 partial sums [S, M, N]
@@ -194,7 +205,7 @@ class Runtime:
                 F.gemm_bf16_tcgen05_pair(x, w, into, self.status, "add_f32")
                 return None
             if not self._own_gemm(x, w):
-                torch.addmm(into, x, w.t(), out_dtype=torch.float32, out=into)
+                torch.addmm(into, x, self._transposed(w), out_dtype=torch.float32, out=into)
                 return None
         return self.linear(x, w, out_dtype=torch.float32)
 
