@@ -207,3 +207,33 @@ def test_bench_refuses_several_gpus_and_has_no_reference_arm():
     reference = subprocess.run([sys.executable, bench, "--impl", "reference"], capture_output=True, text=True)
     line = json.loads(reference.stdout.strip())
     assert reference.returncode == 0 and line["impl"] == "reference" and line["unavailable"]
+
+
+def test_gate_and_up_rows_interleave_in_blocks_of_128():
+    """The operand of the gated product: 128 gate rows, their 128 "up" rows, and so on, the
+    last block padded with zero rows; the plain formula applied block by block gives the
+    feed-forward's activation back (a CPU restatement of what the kernels read)."""
+    from mini_llm_runtime_b200.ops.functions import GATE_BLOCK, interleave_gate_up
+    inter, width = 300, 24
+    g = torch.Generator().manual_seed(5)
+    gate, up = torch.randn(inter, width, generator=g), torch.randn(inter, width, generator=g)
+    stacked = interleave_gate_up(gate, up)
+    blocks = -(-inter // GATE_BLOCK)
+    assert stacked.shape == (2 * blocks * GATE_BLOCK, width)
+    x = torch.randn(7, width, generator=g)
+    product = (x @ stacked.T).view(7, blocks, 2, GATE_BLOCK)
+    silu = lambda t: t / (1 + torch.exp(-t))
+    act = silu(product[:, :, 0]) * product[:, :, 1]
+    act = act.reshape(7, blocks * GATE_BLOCK)
+    want = silu(x @ gate.T) * (x @ up.T)
+    assert torch.allclose(act[:, :inter], want, atol=1e-5) and (act[:, inter:] == 0).all()
+
+
+def test_split_counts_fill_whole_rounds_of_blocks():
+    from mini_llm_runtime_b200.ops.functions import k_splits_for
+    for rows, K in ((4096, 4096), (24576, 4096), (4096, 12288), (151936, 4096), (1024, 1024), (128, 64)):
+        splits = k_splits_for(rows, K, 148)
+        units = -(-rows // 128) * splits
+        assert 1 <= splits <= 16 and (splits == 1 or -(-K // 64) // splits >= 4)
+        if rows * K >= 4096 * 4096:
+            assert units / (148 * -(-units // 148)) >= 0.85, (rows, K, splits)
