@@ -6,10 +6,13 @@ the generated token ids and timings out.
              [--seed 0] [--context N] [--chunk 32] [--batch 256] [--sequences 4]
              [--page-size 16] [--dtype bfloat16|float32] [--device 0] [--ignore-eos]
     mini-llm --model DIR --random-weights SEED --config CONFIG.json   (writes DIR first)
+    mini-llm --model DIR --inspect             (what the folder holds; needs no GPU)
 
 Names and meanings follow the reference where it has them: --model, --tokens [1,4096],
 --context (cache tokens), --chunk (prompt portion per step), --batch (tokens per
-step), --sequences (request slots), --device, --ignore-eos.  The reference takes text
+step), --sequences (request slots), --device, --ignore-eos, --inspect (container and
+dimensions, apps/mini_main.cpp:54-71), --output FILE (the report also goes to a file,
+apps/cuda_main.cpp:18-26).  The reference takes text
 (--prompt) and tokenises it with llama.cpp; this engine takes ids (--prompt-ids).
 --temperature, --seed, --dtype, --page-size and --random-weights are additions.
 Options are matched exactly; a duplicate, an unknown name or a missing value is an
@@ -24,13 +27,13 @@ import time
 from typing import Dict, List, Sequence
 
 VALUES = {"--model", "--prompt-ids", "--tokens", "--temperature", "--seed", "--context", "--chunk", "--batch",
-          "--sequences", "--page-size", "--dtype", "--device", "--random-weights", "--config", "--policy"}
-FLAGS = {"--help", "--ignore-eos"}
+          "--sequences", "--page-size", "--dtype", "--device", "--random-weights", "--config", "--policy", "--output"}
+FLAGS = {"--help", "--ignore-eos", "--inspect"}
 
 USAGE = ("mini-llm --model DIR [--prompt-ids 1,2,3] [--tokens 32] [--temperature 0] [--seed 0]\n"
          "         [--context N] [--chunk 32] [--batch 256] [--sequences 4] [--page-size 16]\n"
          "         [--dtype bfloat16|float32] [--policy mixed|prefill_first] [--device 0] [--ignore-eos]\n"
-         "         [--random-weights SEED --config CONFIG.json]\n")
+         "         [--random-weights SEED --config CONFIG.json] [--output FILE] [--inspect]\n")
 
 
 class Options:
@@ -89,6 +92,45 @@ def parse_ids(text: str) -> List[int]:
     return ids
 
 
+def emit(report: dict, options: "Options") -> int:
+    text = json.dumps(report, indent=2)
+    print(text)
+    if options.has("--output"):
+        with open(options.get("--output"), "w", encoding="utf-8") as f:
+            f.write(text + "\n")
+    return 0
+
+
+def inspect(model_dir: str) -> dict:
+    """What a model folder holds, read without a GPU: the container's size and tensor
+    count, the architecture and the dimensions the configuration gives, the layer plan in
+    short, and whether the tensors are the ones the architecture expects."""
+    import os
+
+    from . import models as _models  # noqa: F401  (registers the architectures)
+    from .config.registry import config_from_dir, plan_for
+    from .engine.structure import expected_weights
+    from .weights.safetensors_io import SafetensorsFile
+
+    config = config_from_dir(model_dir)
+    plan = plan_for(config)
+    path = os.path.join(model_dir, "model.safetensors")
+    container = SafetensorsFile(path)
+    stored = container.names()
+    expected = set(expected_weights(plan))
+    dtypes = sorted({str(container.dtype(name)).replace("torch.", "") for name in stored})
+    with open(os.path.join(model_dir, "config.json"), "r", encoding="utf-8") as f:
+        raw = json.load(f)
+    keys = ("hidden_size", "num_hidden_layers", "num_attention_heads", "num_key_value_heads", "head_dim",
+            "intermediate_size", "vocab_size", "max_position_embeddings", "rms_norm_eps", "rope_theta",
+            "tie_word_embeddings", "use_sliding_window", "sliding_window", "max_window_layers")
+    windows = sorted({str(layer.mixer.params.get("window")) for layer in plan.layers})
+    return {"container": "safetensors", "bytes": os.path.getsize(path), "tensors": len(stored), "stored_dtypes": dtypes,
+            "architecture": plan.architecture, "dimensions": {k: raw[k] for k in keys if k in raw},
+            "layers": len(plan.layers), "runs": len(plan.schedule), "windows": windows,
+            "missing_tensors": sorted(expected - set(stored)), "unexpected_tensors": sorted(set(stored) - expected)}
+
+
 def main(argv: Sequence[str]) -> int:
     try:
         options = Options(argv)
@@ -102,6 +144,8 @@ def main(argv: Sequence[str]) -> int:
             from .weights.random_init import write_random_model
             with open(options.get("--config"), "r", encoding="utf-8") as f:
                 write_random_model(model_dir, json.load(f), options.integer("--random-weights", 0, 0, 2**31 - 1))
+        if options.has("--inspect"):
+            return emit(inspect(model_dir), options)
         dtype = options.get("--dtype", "bfloat16")
         if dtype not in ("bfloat16", "float32"):
             raise ValueError("--dtype must be bfloat16 or float32")
@@ -148,13 +192,12 @@ def main(argv: Sequence[str]) -> int:
                 result = finished[0]
         elapsed = time.perf_counter() - start
         used_after = sum(b - model.cache.free_pages(g) for g, b in enumerate(free_before))
-        print(json.dumps({
+        return emit({
             "backend": "mini-llm-runtime_b200", "dtype": dtype, "token_ids": result.token_ids,
             "finish_reason": result.finish_reason, "prompt_tokens": len(prompt),
             "completion_tokens": len(result.token_ids), "ttft_ms": ttft_ms, "elapsed_s": elapsed,
             "output_tokens_per_second": len(result.token_ids) / elapsed, "steps": engine.steps,
-            "used_kv_pages_before_release": peak_pages, "used_kv_pages_after_release": used_after}, indent=2))
-        return 0
+            "used_kv_pages_before_release": peak_pages, "used_kv_pages_after_release": used_after}, options)
     except Exception as error:  # the reference prints the message and exits 1 (apps/mini_main.cpp:132-135)
         sys.stderr.write(f"mini-llm: {error}\n")
         return 1

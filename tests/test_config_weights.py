@@ -237,3 +237,21 @@ def test_split_counts_fill_whole_rounds_of_blocks():
         assert 1 <= splits <= 16 and (splits == 1 or -(-K // 64) // splits >= 4)
         if rows * K >= 4096 * 4096:
             assert units / (148 * -(-units // 148)) >= 0.85, (rows, K, splits)
+
+
+def test_inspect_describes_a_folder_without_a_gpu(tmp_path, capsys):
+    """`mini-llm --model DIR --inspect` (the reference's flag, apps/mini_main.cpp:54-71): the
+    container, the architecture and its dimensions, and whether the tensors are the expected
+    ones; `--output` writes the same report to a file."""
+    from mini_llm_runtime_b200 import cli
+    folder = str(tmp_path / "m")
+    write_random_model(folder, tiny_models.get("tiny_c"), seed=1)
+    report_file = str(tmp_path / "report.json")
+    assert cli.main(["--model", folder, "--inspect", "--output", report_file]) == 0
+    report = json.loads(capsys.readouterr().out)
+    assert report == json.load(open(report_file))
+    assert report["architecture"] == "Qwen3ForCausalLM" and report["layers"] == 4 and report["runs"] == 4
+    assert report["dimensions"]["head_dim"] == 48 and report["dimensions"]["vocab_size"] == 515
+    assert report["missing_tensors"] == [] and report["unexpected_tensors"] == []
+    assert report["windows"] == ["40", "None"] and report["tensors"] > 10
+    assert report["bytes"] == os.path.getsize(os.path.join(folder, "model.safetensors"))
