@@ -69,6 +69,9 @@ class ModelPlan:
     final_norm: PartSpec
     lm_head: PartSpec
     eos_token_ids: Tuple[int, ...] = ()
+    # (name, twin): a checkpoint may also store `name`, a second copy of the tensor `twin` that the
+    # model reads (a tied output head stored beside the embedding).  It is accepted if it equals its twin.
+    redundant_tensors: Tuple[Tuple[str, str], ...] = ()
 
     def validate(self) -> None:
         if not self.layers or not self.schedule:

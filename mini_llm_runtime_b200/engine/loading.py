@@ -31,7 +31,7 @@ def load_model(model_dir: str, dtype="bfloat16", cache: Optional[CacheConfig] = 
     plan = plan_for(config)
     model = Model(plan, Runtime(parse_dtype(dtype), device))
     model.config = config
-    tensors = load_checkpoint(model_dir, model.expected_weights())
+    tensors = load_checkpoint(model_dir, model.expected_weights(), plan.redundant_tensors)
     model.bind(tensors)
     if cache is not None:
         model.allocate_cache(cache)

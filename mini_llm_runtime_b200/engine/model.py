@@ -139,15 +139,17 @@ class Model:
         return merge_specs(spec for part in self._all_parts() for spec in part.weight_specs())
 
     def kernel_modules(self) -> List[str]:
-        names = ["host", "sampling"]
+        names = ["host", "sampling", "weights"]
         for part in self._all_parts():
             names += part.kernel_modules(self.rt.dtype)
         return list(dict.fromkeys(names))
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         build.ensure(self.kernel_modules())
+        self.rt.begin_load(tensors)
         for part in self._all_parts():
             part.bind(tensors, self.rt)
+        self.rt.end_load()
         self.status = torch.zeros(1, dtype=torch.int32, device=self.rt.device)
         self.rt.status = self.status
         self._graph_pool = torch.cuda.graph_pool_handle()

@@ -36,6 +36,10 @@ import torch
 from ..ops import functions as F
 
 
+class NonFiniteWeights(ValueError):
+    """A tensor of the checkpoint holds a NaN or an infinity; the message names every such tensor."""
+
+
 class Runtime:
     def __init__(self, dtype: torch.dtype = torch.bfloat16, device: str = "cuda:0"):
         if dtype not in (torch.float32, torch.bfloat16):
@@ -76,6 +80,36 @@ class Runtime:
         self._retired = []
         self.status = None        # the model's device status word (set at bind time)
         self._shared = {}
+        self._load_names = None   # while weights are bound: id(source tensor) -> name, for the finiteness check
+        self._load_flags = None
+        self._load_checked = {}
+
+    # ---- the finiteness check of uploaded weights
+    def begin_load(self, tensors) -> None:
+        """From here to `end_load`, every tensor of `tensors` that `matrix`, `vector` or
+        `shared_matrix` uploads is checked on the device for NaNs and infinities, as the
+        reference refuses such weights when it decodes them (src/minillm/cuda/storage.cpp:314-321).
+        One flag per tensor, read once at the end."""
+        self._load_names = {id(t): name for name, t in tensors.items()}
+        self._load_flags = torch.zeros(max(1, len(tensors)), dtype=torch.int32, device=self.device)
+        self._load_checked = {}
+
+    def _checked(self, source: torch.Tensor, uploaded: torch.Tensor) -> torch.Tensor:
+        name = self._load_names.get(id(source)) if self._load_names is not None else None
+        if name is not None and name not in self._load_checked and uploaded.dtype in (torch.float32, torch.bfloat16):
+            index = self._load_checked[name] = len(self._load_checked)
+            F.finite_check(uploaded, self._load_flags[index:index + 1])
+        return uploaded
+
+    def end_load(self) -> None:
+        names, flags = self._load_checked, self._load_flags
+        self._load_names = self._load_flags = None
+        self._load_checked = {}
+        if names:
+            bad = flags[:len(names)].cpu().tolist()
+            broken = sorted(n for n, i in names.items() if bad[i])
+            if broken:
+                raise NonFiniteWeights(f"weights with non-finite values ({len(broken)}): " + ", ".join(broken))
 
     def own_products_only(self) -> None:
         """Every bfloat16 product on the package's tcgen05 kernels, none on the vendor library:
@@ -96,14 +130,14 @@ class Runtime:
     # ---- weights
     def matrix(self, t: torch.Tensor) -> torch.Tensor:
         """An operand of matrix products: the compute precision, on the device."""
-        return t.to(device=self.device, dtype=self.dtype).contiguous()
+        return self._checked(t, t.to(device=self.device, dtype=self.dtype).contiguous())
 
     def vector(self, t: torch.Tensor) -> torch.Tensor:
         """Norm weights and the like: float32 on the 32-bit path; on the bfloat16 path
         the stored precision is kept (a tensor stored in 32-bit stays 32-bit)."""
         if self.dtype is torch.float32:
-            return t.to(device=self.device, dtype=torch.float32).contiguous()
-        return t.to(device=self.device).contiguous()
+            return self._checked(t, t.to(device=self.device, dtype=torch.float32).contiguous())
+        return self._checked(t, t.to(device=self.device).contiguous())
 
     def shared_matrix(self, name: str, tensors) -> torch.Tensor:
         """A matrix several parts name (a tied embedding and head): one device copy."""

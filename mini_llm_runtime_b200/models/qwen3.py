@@ -55,6 +55,9 @@ def qwen3_plan(cfg: Qwen3Config) -> ModelPlan:
         lm_head=PartSpec("linear_head", {"vocab_size": cfg.vocab_size, "width": cfg.hidden_size},
                          {"weight": embed_name if cfg.tie_word_embeddings else "lm_head.weight"}),
         eos_token_ids=cfg.eos_token_ids,
+        # The reference takes `output.weight` when the file has it and the embedding otherwise
+        # (src/minillm/qwen3_model.cpp:60-61); a tied checkpoint that stores both is the same model.
+        redundant_tensors=(("lm_head.weight", embed_name),) if cfg.tie_word_embeddings else (),
     )
 
 

@@ -230,6 +230,15 @@ def attention_prefill_tcgen05(q: torch.Tensor, out: torch.Tensor, cache: torch.T
          block_table.stride(0), page_size, q_heads, kv_heads, head_dim, int(window), float(scale), ptr(status), stream())
 
 
+def finite_check(t: torch.Tensor, flag: torch.Tensor) -> None:
+    """flag[0] = 1 if `t` (float32 or bfloat16, contiguous) holds a NaN or an infinity."""
+    on_gpu(t, flag)
+    expect(flag, torch.int32, "the flag")
+    if not t.is_contiguous():
+        raise KernelError("finite_check wants a contiguous tensor")
+    call("weights", "mlr_finite_check", ptr(t), is_bf16(t), t.numel(), ptr(flag), stream())
+
+
 def product_modules(dtype) -> list:
     """The kernel modules the matrix products of a precision may call."""
     return ["gemm_f32"] if dtype is torch.float32 else ["gemm_bf16_tcgen05", "gemm_bf16_tcgen05_pair"]

@@ -16,6 +16,7 @@ import torch
 from ..csrc import build
 
 c_int, c_float, c_void_p, c_longlong = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
+c_ulonglong, c_double = ctypes.c_ulonglong, ctypes.c_double
 
 
 class KernelError(RuntimeError):
@@ -65,6 +66,10 @@ _SIGNATURES = {
     },
     "sampling": {
         "mlr_sample": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    },
+    "weights": {
+        "mlr_normal_fill": [c_void_p, c_int, c_longlong, c_ulonglong, c_double, c_int, c_void_p],
+        "mlr_finite_check": [c_void_p, c_int, c_longlong, c_void_p, c_void_p],
     },
 }
 

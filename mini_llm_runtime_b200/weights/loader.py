@@ -15,7 +15,7 @@ What a part does with the stored precision is its own decision at bind time.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, Iterable, List, Tuple
+from typing import Dict, Iterable, List, Sequence, Tuple
 
 import torch
 
@@ -62,9 +62,14 @@ def merge_specs(specs: Iterable[WeightSpec]) -> Dict[str, WeightSpec]:
     return out
 
 
-def check_names_and_shapes(available: Dict[str, Tuple[int, ...]], expected: Dict[str, WeightSpec], where: str) -> None:
+def check_names_and_shapes(available: Dict[str, Tuple[int, ...]], expected: Dict[str, WeightSpec], where: str,
+                           redundant: Sequence[Tuple[str, str]] = ()) -> None:
+    """`redundant`: (name, twin) pairs; a stored `name` that the model does not read is not
+    "unexpected" when the model reads `twin` and both have one shape."""
+    allowed = {n for n, twin in redundant if twin in expected and n in available and twin in available
+               and tuple(available[n]) == tuple(available[twin])}
     missing = sorted(n for n in expected if n not in available)
-    unexpected = sorted(n for n in available if n not in expected)
+    unexpected = sorted(n for n in available if n not in expected and n not in allowed)
     wrong = sorted((n, tuple(available[n]), tuple(expected[n].shape)) for n in expected
                    if n in available and tuple(available[n]) != tuple(expected[n].shape))
     if missing or unexpected or wrong:
@@ -79,9 +84,10 @@ def _kept_precision(tensor: torch.Tensor) -> torch.Tensor:
     return tensor
 
 
-def load_checkpoint(model_dir: str, expected: Dict[str, WeightSpec]) -> Dict[str, torch.Tensor]:
+def load_checkpoint(model_dir: str, expected: Dict[str, WeightSpec],
+                    redundant: Sequence[Tuple[str, str]] = ()) -> Dict[str, torch.Tensor]:
     """Tensors of `model_dir` by name (CPU, mapped from the files), after the
-    name and shape check."""
+    name and shape check.  A stored second copy named in `redundant` must equal its twin."""
     files = open_model_files(model_dir)
     owner: Dict[str, SafetensorsFile] = {}
     for f in files:
@@ -89,5 +95,10 @@ def load_checkpoint(model_dir: str, expected: Dict[str, WeightSpec]) -> Dict[str
             if name in owner:
                 raise WeightFileError(f"tensor {name!r} is stored in both {owner[name].path} and {f.path}")
             owner[name] = f
-    check_names_and_shapes({n: f.shape(n) for n, f in owner.items()}, expected, model_dir)
+    check_names_and_shapes({n: f.shape(n) for n, f in owner.items()}, expected, model_dir, redundant)
+    for name, twin in redundant:
+        if name in owner and name not in expected and twin in expected:
+            if not torch.equal(owner[name].tensor(name), owner[twin].tensor(twin)):
+                raise WeightFileError(f"{model_dir}: {name!r} is stored beside {twin!r}, which the model reads in its "
+                                      f"place, but the two differ")
     return {name: _kept_precision(owner[name].tensor(name)) for name in expected}

@@ -2,6 +2,7 @@
 import json
 import os
 
+import numpy as np
 import pytest
 import torch
 
@@ -168,13 +169,28 @@ def test_loader_keeps_stored_precision(tmp_path):
     assert torch.equal(loaded["model.layers.1.mlp.down_proj.weight"], weights["model.layers.1.mlp.down_proj.weight"])
 
 
-def test_tied_head_with_extra_lm_head_is_unexpected(tmp_path):
+def test_tied_head_stored_beside_the_embedding_is_accepted(tmp_path):
+    """The reference reads `output.weight` when the file has it and the embedding otherwise
+    (src/minillm/qwen3_model.cpp:60-61): a tied checkpoint that stores both copies is the same
+    model.  A second copy that differs from the embedding is refused, and so is any other
+    extra tensor."""
     raw = tiny_models.get("tiny_a")
     weights = plain_qwen3.random_weights(raw, 0)
     weights["lm_head.weight"] = weights["model.embed_tokens.weight"].clone()
-    folder = _folder(tmp_path, raw, weights)
+    folder = _folder(tmp_path / "same", raw, weights)
+    plan = plan_for(config_from_dir(folder))
+    loaded = load_checkpoint(folder, expected_weights(plan), plan.redundant_tensors)
+    assert "lm_head.weight" not in loaded and "model.embed_tokens.weight" in loaded
     with pytest.raises(WeightMismatch, match="unexpected .1.: lm_head.weight"):
-        load_checkpoint(folder, expected_weights(plan_for(config_from_dir(folder))))
+        load_checkpoint(folder, expected_weights(plan))          # without the plan's word for it, it is unexpected
+    weights["lm_head.weight"][3, 5] += 1.0
+    folder = _folder(tmp_path / "differs", raw, weights)
+    with pytest.raises(WeightFileError, match="the two differ"):
+        load_checkpoint(folder, expected_weights(plan), plan.redundant_tensors)
+    weights["model.extra.weight"] = torch.zeros(2, 2)
+    folder = _folder(tmp_path / "extra", raw, weights)
+    with pytest.raises(WeightMismatch, match="unexpected .1.: model.extra.weight"):
+        load_checkpoint(folder, expected_weights(plan), plan.redundant_tensors)
 
 
 def test_random_weights_mode_writes_a_loadable_folder(tmp_path):
@@ -255,3 +271,68 @@ def test_inspect_describes_a_folder_without_a_gpu(tmp_path, capsys):
     assert report["missing_tensors"] == [] and report["unexpected_tensors"] == []
     assert report["windows"] == ["40", "None"] and report["tensors"] > 10
     assert report["bytes"] == os.path.getsize(os.path.join(folder, "model.safetensors"))
+
+
+# --------------------------------------------------------------------------- the portable generator
+def test_portable_generator_is_a_function_of_seed_name_and_index():
+    from mini_llm_runtime_b200.weights import portable_random as pr
+    a = pr.normal_float32(2, "model.layers.0.mlp.up_proj.weight", 50_000, 0.02)
+    assert np.array_equal(a, pr.normal_float32(2, "model.layers.0.mlp.up_proj.weight", 50_000, 0.02, chunk=777))
+    assert np.array_equal(a[:100], pr.normal_float32(2, "model.layers.0.mlp.up_proj.weight", 100, 0.02))   # a prefix of itself
+    assert not np.array_equal(a, pr.normal_float32(3, "model.layers.0.mlp.up_proj.weight", 50_000, 0.02))
+    assert not np.array_equal(a, pr.normal_float32(2, "model.layers.1.mlp.up_proj.weight", 50_000, 0.02))
+    assert abs(a.mean()) < 4 * 0.02 / 50_000 ** 0.5 and abs(a.std() - 0.02) < 3e-4
+    one = pr.normal_float32(2, "model.norm.weight", 50_000, 0.01, one_plus=True)
+    assert abs(one.mean() - 1.0) < 3e-4 and abs(one.std() - 0.01) < 2e-4
+    # Pinned values: the device kernel and any other restatement have to give these bits.
+    first = pr.normal_float32(0, "w", 4, 1.0).view(np.uint32).tolist()
+    assert first == [0xBE134923, 0xBF845A2A, 0xBFCEE0F8, 0xBD1A3326], [hex(v) for v in first]
+
+
+def test_series_of_the_generator_agree_with_the_library():
+    from mini_llm_runtime_b200.weights import portable_random as pr
+    u = np.random.default_rng(0).random(200_000)
+    u[:4] = [2.0 ** -53, 1.0, 0.5, 0.7071067811865476]
+    assert np.abs(pr._ln(u) - np.log(u)).max() < 1e-14
+    t = np.random.default_rng(1).random(200_000)
+    t[:5] = [0.0, 0.125, 0.25, 0.5, 1.0 - 2.0 ** -53]
+    assert np.abs(pr._cos_turns(t) - np.cos(2 * np.pi * t)).max() < 2e-15
+
+
+@pytest.mark.gpu
+def test_device_generator_gives_the_host_generator_bits():
+    """numpy on the host and the kernel on the device make the same tensors: every tensor of
+    tiny B in both stored precisions, and one matrix of the 8B sizes (12288 x 4096)."""
+    from mini_llm_runtime_b200.weights.random_init import random_tensor, random_tensors
+    from mini_llm_runtime_b200.weights.loader import WeightSpec
+    specs = expected_weights(plan_for(config_from_dict(tiny_models.get("tiny_b"))))
+    for dtype in (torch.bfloat16, torch.float32):
+        host = random_tensors(specs, 1, dtype, "cpu")
+        device = random_tensors(specs, 1, dtype, "cuda:0")
+        for name in specs:
+            assert torch.equal(host[name], device[name].cpu()), (name, dtype)
+    spec = WeightSpec("model.layers.0.mlp.gate_proj.weight", (12288, 4096))
+    host = random_tensor(spec.name, spec, 2, torch.bfloat16, "cpu")
+    device = random_tensor(spec.name, spec, 2, torch.bfloat16, "cuda:0")
+    assert torch.equal(host, device.cpu())
+    spec = WeightSpec("model.layers.3.self_attn.o_proj.weight", (1024, 2048))
+    assert torch.equal(random_tensor(spec.name, spec, 3, torch.float32, "cpu"),
+                       random_tensor(spec.name, spec, 3, torch.float32, "cuda:0").cpu())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_non_finite_weights_are_refused_by_name(tmp_path, dtype):
+    """The reference refuses a checkpoint with a NaN or an infinity while it decodes it
+    (src/minillm/cuda/storage.cpp:314-321); here the check runs on the device after the upload and
+    the error names every such tensor."""
+    from mini_llm_runtime_b200.engine.loading import load_model
+    from mini_llm_runtime_b200.engine.runtime import NonFiniteWeights
+    raw = tiny_models.get("tiny_b")
+    weights = plain_qwen3.random_weights(raw, 0)
+    load_model(_folder(tmp_path / "good", raw, weights), dtype)
+    weights["model.layers.1.mlp.down_proj.weight"][5, 7] = float("inf")
+    weights["model.layers.2.self_attn.k_norm.weight"][3] = float("nan")
+    with pytest.raises(NonFiniteWeights) as info:
+        load_model(_folder(tmp_path / "bad", raw, weights), dtype)
+    assert "(2): model.layers.1.mlp.down_proj.weight, model.layers.2.self_attn.k_norm.weight" in str(info.value)
