@@ -96,6 +96,28 @@ static void mlr_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, 
     cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);   // an error shows in mlr_launched()
 }
 
+// Number of SMs of the current device (asked once per device and thread); grid-stride kernels
+// size their grids as a multiple of it.
+static int mlr_sm_count() {
+    static thread_local int cached_device = -1, cached_count = 0;
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device != cached_device) {
+        int count = 0;
+        if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0) count = 1;
+        cached_device = device;
+        cached_count = count;
+    }
+    return cached_count;
+}
+
+// Blocks of a grid-stride kernel over `units` work items of one block each: all of them, up to
+// `per_sm` resident blocks on every SM.
+static int mlr_grid_stride_blocks(size_t units, int per_sm) {
+    const size_t limit = static_cast<size_t>(mlr_sm_count()) * per_sm;
+    return static_cast<int>(units < 1 ? 1 : (units < limit ? units : limit));
+}
+
 #define MLR_REQUIRE(condition, ...) \
     do {                            \
         if (!(condition)) return mlr_fail(__VA_ARGS__); \

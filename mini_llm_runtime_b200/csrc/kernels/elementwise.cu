@@ -636,7 +636,7 @@ MLR_API int mlr_swiglu(const void* gate_up, void* out, int act_bf16, int rows, i
             mlr_launch((swiglu_vec8_kernel<float>), dim3(vgrid), dim3(256), 0, stream, static_cast<const float*>(gate_up), static_cast<float*>(out), rows, inter, block);
         return mlr_launched("swiglu");
     }
-    const int blocks = static_cast<int>(total / 1024 + 1 < 148 * 16 ? total / 1024 + 1 : 148 * 16);
+    const int blocks = mlr_grid_stride_blocks(total / 1024 + 1, 16);
     if (act_bf16)
         mlr_launch((swiglu_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, inter, block);
     else
@@ -651,7 +651,7 @@ MLR_API int mlr_swiglu_sliced(const float* partials, int slices, long long slice
     MLR_REQUIRE(block >= 1 && inter % block == 0, "swiglu_sliced: the width %d is no multiple of the gate block %d", inter, block);
     if (rows == 0) return 0;
     const size_t total = static_cast<size_t>(rows) * inter;
-    const int blocks = static_cast<int>(total / 256 + 1 < 148 * 16 ? total / 256 + 1 : 148 * 16);
+    const int blocks = mlr_grid_stride_blocks(total / 256 + 1, 16);
     if (act_bf16)
         mlr_launch((swiglu_sliced_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream, partials, slices, static_cast<size_t>(slice_stride),
                                                          static_cast<__nv_bfloat16*>(out), rows, inter, block);

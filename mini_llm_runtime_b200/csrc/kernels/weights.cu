@@ -104,8 +104,7 @@ __global__ void finite_check_kernel(const T* __restrict__ data, long long count,
 }
 
 int grid_for(long long count) {
-    const long long blocks = (count + 255) / 256;
-    return static_cast<int>(blocks < 1 ? 1 : (blocks > 148 * 32 ? 148 * 32 : blocks));
+    return mlr_grid_stride_blocks(static_cast<size_t>((count + 255) / 256), 32);
 }
 
 }  // namespace

@@ -15,7 +15,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from ..sampling.sampler import Sampler, SamplingParams, uniform_for
-from .model import Model, StepEntry
+from .model import Model, Poisoned, StepEntry
 from .scheduler import Request, Scheduler
 
 
@@ -81,6 +81,10 @@ class Engine:
     def _sample_and_send_back(self, logits: torch.Tensor, sampled_for: List[Request], ahead: int, all_decode: bool) -> _InFlight:
         """Samples one id per wanted row and starts their copy to the host.  `ahead` is how
         many tokens of each request are still on their way (1 when launching ahead)."""
+        if logits is None or logits.dim() != 2 or logits.shape[0] != len(sampled_for):
+            got = "no logits" if logits is None else f"logits of shape {tuple(logits.shape)}"
+            self.model._poison(f"the step function returned {got} for {len(sampled_for)} wanted rows")
+            raise RuntimeError(f"the step function returned {got} for {len(sampled_for)} wanted rows")
         temps = [r.params.temperature for r in sampled_for]
         uniforms = [uniform_for(r.params.seed, r.request_id, len(r.generated) + ahead) for r in sampled_for]
         ids = self.sampler.sample(logits, temps, uniforms)
@@ -150,13 +154,20 @@ class Engine:
             return finished
         step.ready.synchronize()
         values = step.host.tolist()
+        # The whole set of results is checked before any of it is handed out, as the reference
+        # does (src/engine.cpp:489-511): a status word a kernel set, or an id that is no token,
+        # poisons the model and no request of the step advances.
         if values[-1]:
             self.model.check_status()
+        vocab = self.model.plan.vocab_size
+        for r, token in zip(step.sampled_for, values[:-1]):
+            if not r.finish_reason and not 0 <= token < vocab:
+                why = "the logits were not finite" if token < 0 else f"the sampled id {token} is no token"
+                self.model._poison(f"request {r.request_id}: {why}")
+                raise RuntimeError(f"request {r.request_id}: {why}")
         for r, token in zip(step.sampled_for, values[:-1]):
             if r.finish_reason:
                 continue        # it ended with the step before; this row ran ahead in vain
-            if token < 0:
-                raise RuntimeError(f"request {r.request_id}: the logits were not finite")
             r.generated.append(token)
             if token in self.eos and not r.params.ignore_eos:
                 r.finish_reason = "stop"
@@ -169,7 +180,11 @@ class Engine:
         return finished
 
     def step(self) -> List[Finished]:
-        """One iteration; returns the requests that finished in it."""
+        """One iteration; returns the requests that finished in it.  A poisoned model ends
+        generation: the call raises `Poisoned` and no further token is handed out."""
+        if self.model.poisoned is not None:
+            self._in_flight = None
+            raise Poisoned(f"the model is poisoned and must not be used further ({self.model.poisoned})")
         current, self._in_flight = self._in_flight, None
         if current is not None and all(r.finish_reason for r in current.sampled_for):
             current = None      # every request of the step that ran ahead has ended meanwhile

@@ -39,6 +39,13 @@ class DeviceFault(RuntimeError):
     """A kernel reported a bad index, a bad page or a non-finite value."""
 
 
+class Poisoned(RuntimeError):
+    """The model failed after device work of a step had begun, or a kernel reported a fault:
+    what the device holds can no longer be trusted, and the model refuses every further step
+    and request (the reference's `poisoned` state: src/minillm/cuda/runtime.cpp:241-253,
+    src/minillm/cuda/batch_state.h:9).  Build a new model."""
+
+
 @dataclass
 class StepEntry:
     slot: int
@@ -107,6 +114,10 @@ class Model:
         self._pinned: List[Tuple[torch.Tensor, torch.cuda.Event]] = []
         self._pinned_next = 0
         self._bound = False
+        self.poisoned: Optional[str] = None      # why the model refuses further work, once it does
+        # For tests: called with (group, slots, table rows on the host) after a step's block table is
+        # filled and before it is uploaded; it may change the rows it is given.
+        self.table_hook = None
         self.last_h2d_bytes = 0
         # Decode steps are replayed from CUDA graphs unless a mixer keeps state that a
         # repeated run would advance twice (capturing runs a step more than once) or a part
@@ -187,7 +198,16 @@ class Model:
         return sum(2 * r.need.kv_heads * r.need.head_dim * element for r in self.runs
                    if r.need is not None and r.context.write_cache)
 
+    def _refuse_if_poisoned(self) -> None:
+        if self.poisoned is not None:
+            raise Poisoned(f"the model is poisoned and must not be used further ({self.poisoned})")
+
+    def _poison(self, why: str) -> None:
+        if self.poisoned is None:
+            self.poisoned = why
+
     def open_request(self) -> int:
+        self._refuse_if_poisoned()
         slot = self.cache.open()
         for run in self.runs:
             if run.context.state is not None:
@@ -250,7 +270,13 @@ class Model:
 
         A step of single tokens that wants every row's logits is replayed from a CUDA
         graph (captured on first use per batch size and context bucket).  Its logits
-        live in the graph's memory: read or sample them before the next step."""
+        live in the graph's memory: read or sample them before the next step.
+
+        Failure: a batch that is refused, or a pool that cannot hold it, raises before any
+        device work and changes nothing.  An exception after device work has begun rolls the
+        ledger back (the step's pages, lengths, and the fixed-size state of its requests as
+        they were before the step), poisons the model and is raised again."""
+        self._refuse_if_poisoned()
         segments, rows = self._validate(entries)
         n = len(segments)
         vocab = self.plan.vocab_size
@@ -297,7 +323,15 @@ class Model:
                 if graphed:
                     table.fill_(-1)
                 self.cache.fill_table(g, slots, table, min(columns, self.cache.max_blocks))
+                if self.table_hook is not None:
+                    self.table_hook(g, slots, table)
             self.last_h2d_bytes = 4 * total
+        except BaseException:
+            self.cache.discard()        # nothing has been launched: the model stays usable
+            raise
+        journal = None
+        try:
+            journal = self._journal_state(slots)
 
             def context_on(device: torch.Tensor, bound: Optional[int]) -> StepContext:
                 part = lambda k: device[offsets[k]:offsets[k + 1]]
@@ -318,11 +352,30 @@ class Model:
                     device[:rows].copy_(device_tokens)
                 step = context_on(device, None)
                 logits = self._forward(step, device[offsets[5]:offsets[6]] if want_rows else None)
-        except BaseException:
-            self.cache.discard()
+        except BaseException as error:
+            self._poison(f"a step failed after its device work had begun: {type(error).__name__}: {error}")
+            try:
+                self._restore_state(journal)
+            finally:
+                self.cache.discard()
             raise
+        # Lengths and page maps are published when the step's work is enqueued, not when it has run,
+        # so that the next step can be launched behind it.  A fault a kernel reports in the status
+        # word is read with the step's results (`check_status`, or the engine's read-back) and poisons
+        # the model before any token of that step is handed out.
         self.cache.commit()
         return logits
+
+    def _journal_state(self, slots: Sequence[int]):
+        """Copies of the fixed-size state of the step's requests, for runs that keep one: a mixer
+        updates its state in place, and a step that fails must not leave it half updated."""
+        saved = [(run.context.state, slot, run.context.state[slot].clone())
+                 for run in self.runs if run.context.state is not None for slot in slots]
+        return saved or None
+
+    def _restore_state(self, journal) -> None:
+        for state, slot, saved in journal or ():
+            state[slot].copy_(saved)
 
     def _replay(self, host: torch.Tensor, rows: int, columns: int, context_on, offsets, device_tokens):
         """Decode steps from a CUDA graph: one graph per (batch size, table width).  The
@@ -380,5 +433,6 @@ class Model:
         kernel flagged a fault.  After a fault the model must not be used further."""
         value = int(self.status.item())
         if value:
+            self._poison(f"kernels reported status {value}")
             raise DeviceFault(f"kernels reported status {value} (1 = index outside a table, 2 = page outside the pool, "
                               f"4 = non-finite logits); the cache can no longer be trusted")

@@ -97,10 +97,24 @@ def module(name: str):
 
 
 _functions = {}
+_fail_after = None
+
+
+def fail_after(launches) -> None:
+    """For failure tests that must not touch the GPU's health: after `launches` more calls
+    the next one raises `KernelError` INSTEAD of launching its kernel (None: never).  The
+    reference makes wrapped CUDA calls fail the same way (tests/cuda_runtime_tests.cpp:15-49)."""
+    global _fail_after
+    _fail_after = launches
 
 
 def call(module_name: str, fn: str, *args) -> None:
-    global launch_count
+    global launch_count, _fail_after
+    if _fail_after is not None:
+        if _fail_after <= 0:
+            _fail_after = None
+            raise KernelError(f"injected failure in place of {fn}")
+        _fail_after -= 1
     launch_count += 1
     entry = _functions.get(fn)
     if entry is None:

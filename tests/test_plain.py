@@ -5,6 +5,7 @@ import math
 import pytest
 import torch
 
+import plain_qwen3
 import plain_qwen3 as P
 import tiny_models
 
@@ -111,3 +112,19 @@ def test_sampling_definitions():
     # The engine's restatement of the uniform draw is the same function.
     from mini_llm_runtime_b200.sampling.sampler import uniform_for
     assert all(uniform_for(s, r, t) == P.uniform_for(s, r, t) for s in (0, 7, 2**40) for r in (0, 5) for t in (0, 9))
+
+
+def test_dense_restatement_equals_the_loop():
+    """`plain_dense.forward_rows` (the oracle at real sizes) against `plain_qwen3.forward`, with
+    and without a window, for all rows and for chosen rows."""
+    import plain_dense
+    for name, seed in (("tiny_b", 3), ("tiny_c", 4)):
+        config = tiny_models.get(name)
+        weights = plain_qwen3.random_weights(config, seed)
+        tokens = torch.randint(0, config["vocab_size"], (90,), generator=torch.Generator().manual_seed(seed)).tolist()
+        loop = plain_qwen3.forward(config, weights, tokens, dtype=torch.float64)
+        dense = plain_dense.forward_rows(config, weights, tokens)
+        assert torch.allclose(loop, dense, atol=1e-9, rtol=0)
+        assert torch.allclose(plain_dense.forward_rows(config, weights, tokens, rows=[0, 41, 89]), dense[[0, 41, 89]], atol=1e-12, rtol=0)
+        small_blocks = plain_dense.dense_attention(*(torch.randn(70, h, 16, dtype=torch.float64) for h in (6, 2, 2)), window=9, block=16)
+        assert torch.isfinite(small_blocks).all()
