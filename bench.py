@@ -124,14 +124,59 @@ class ClockSampler:
                 "samples": len(clocks)}
 
 
-def reference_arm():
-    """The reference is a CMake C++ project that reads GGUF files through llama.cpp
-    sources it expects under third_party/ (absent from its tree) and has no Python
-    packaging; `pip install` of it fails at once, so there is nothing to run."""
-    print(json.dumps({"impl": "reference",
-                      "unavailable": "lilong555/mini-llm-runtime has no Python package (pip: neither setup.py nor "
-                                     "pyproject.toml) and its CUDA runtime needs llama.cpp sources and a GGUF "
-                                     "checkpoint that are not in the offline tree"}))
+REFERENCE_BINARY = os.path.join(ROOT, "baseline", "_ref", "ref_bench")
+# The reference's CUDA runtime takes at most 4 sequences of 2048 positions and 128 rows a step, with
+# float32 products (include/minillm/cuda/runtime.h:18-23, include/minillm/cuda/kv_layout.h:29-31), and is
+# written for Qwen3-0.6B: that is the configuration its arm runs.
+REFERENCE_BATCH, REFERENCE_CONTEXT = 4, 2048
+
+
+def reference_arm(args) -> int:
+    """Runs lilong555/mini-llm-runtime's own CUDA runtime, compiled unchanged by
+    `baseline/build_reference.py` into baseline/_ref/ref_bench (a driver over its public
+    `CudaRuntime::forward` with stand-ins for the two classes that need llama.cpp), at the
+    Qwen3-0.6B sizes with synthetic float32 weights: decode at batch 4 and context 2048, its
+    limits.  That is NOT the headline's configuration (8B sizes, batch 8, context 8192), which
+    the reference cannot run; `same_config` says so, and the line of `--impl ours` carries the
+    engine's own figures at this configuration under `reference_point`."""
+    if not os.path.exists(REFERENCE_BINARY):
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "baseline/_ref/ref_bench is not built: run `python baseline/build_reference.py "
+                                         "<checkout of lilong555/mini-llm-runtime>` (the reference is a CMake C++/CUDA project, "
+                                         "`pip install` of it finds neither setup.py nor pyproject.toml)"}))
+        return 0
+    c = QWEN3_06B
+    spec = (f"synthetic:{c['hidden_size']}:{c['num_hidden_layers']}:{c['num_attention_heads']}:{c['num_key_value_heads']}:"
+            f"{c['head_dim']}:{c['intermediate_size']}:{c['vocab_size']}:{c['max_position_embeddings']}:3:1")
+    steps, warmup = args.steps, max(args.warmup, 3)
+    with ClockSampler() as clocks:
+        done = subprocess.run([REFERENCE_BINARY, spec, str(steps), str(warmup), str(REFERENCE_CONTEXT), str(REFERENCE_BATCH)],
+                              capture_output=True, text=True)
+    if done.returncode != 0:
+        reason = (done.stderr.strip().splitlines() or ["no message"])[-1]
+        print(json.dumps({"impl": "reference", "unavailable": f"baseline/_ref/ref_bench exited {done.returncode}: {reason}"}))
+        return 0
+    r = json.loads(done.stdout.strip().splitlines()[-1])
+    d = r["decode"]
+    device_ms, wall_ms = d["device_ms"] / d["steps"], d["wall_ms"] / d["steps"]
+    b1, pf = r["decode_b1"], r["prefill_128"]
+    print(json.dumps({
+        "metric": f"decode tok/s (Qwen3-0.6B sizes, batch {REFERENCE_BATCH}, context {REFERENCE_CONTEXT}, fp32)",
+        "value": REFERENCE_BATCH / device_ms * 1e3, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": device_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32",
+        "data": "synthetic", "impl": "reference", "same_config": False,
+        "config": {"model": "Qwen3-0.6B sizes, synthetic float32 weights", "layers": c["num_hidden_layers"],
+                   "hidden": c["hidden_size"], "q_heads": c["num_attention_heads"], "kv_heads": c["num_key_value_heads"],
+                   "head_dim": c["head_dim"], "intermediate": c["intermediate_size"], "vocab": c["vocab_size"],
+                   "global_batch": REFERENCE_BATCH, "seq_len": REFERENCE_CONTEXT, "parallelism": "single_gpu",
+                   "limits": "the reference's own: 4 sequences, 2048 positions, 128 rows a step, float32 products",
+                   "l2": "inputs>L2 (2.4 GB of float32 weights per step), no flush"},
+        "clocks": clocks.summary(),
+        "e2e": {"value": REFERENCE_BATCH / wall_ms * 1e3, "unit": "tokens/s", "ms_per_step": wall_ms,
+                "h2d_bytes_per_step": 4 * 3 * REFERENCE_BATCH + 4 * REFERENCE_BATCH, "d2h_bytes_per_step": 4 * REFERENCE_BATCH + 8},
+        "points": {"decode_b1_ctx2048": 1.0 / (b1["device_ms"] / b1["steps"]) * 1e3,
+                   "prefill_128_tokens_per_s": 128.0 / (pf["device_ms"] / pf["repeats"]) * 1e3},
+        "load_ms": r["load_ms"], "poisoned": r["poisoned"]}))
     return 0
 
 
@@ -195,7 +240,7 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     if args.impl == "reference":
-        return reference_arm()
+        return reference_arm(args)
     if args.warmup < 5:
         args.warmup = 5      # a decode shape is captured into a graph on its third step, and the first step may end a context bucket
 

@@ -2,7 +2,7 @@
 
 The ledger itself is native code (`csrc/host/cache_manager.cpp`); this class is its
 Python face and adds nothing to its decisions.  It owns no device memory: the pools
-that the page ids index are allocated by the model (`cache/pools.py`).
+that the page ids index are allocated by the model (`engine/model.py`, `allocate_cache`).
 
 Layers are grouped by what they keep: group `g` keeps every key (`window` None) or
 only the last `window` keys.  Each group has `num_pages` page ids and one block

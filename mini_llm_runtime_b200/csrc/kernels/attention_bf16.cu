@@ -26,6 +26,8 @@
 // position - window + 1.  The reference computes them with three SIMT kernels and a
 // materialised score matrix (src/minillm/cuda/attention.cu:97-218).
 #include "common.cuh"
+
+#include <mutex>
 #include "attention_no_alloc.h"
 
 #include <type_traits>
@@ -495,7 +497,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
         bool ok = true;
         for (int it = 0; it < tiles; ++it) {
             const int stage = it % kDecodeStages;
-            ok = mbar_wait(full_bar(stage), (it / kDecodeStages) & 1);
+            ok = __all_sync(0xffffffffu, mbar_wait(full_bar(stage), (it / kDecodeStages) & 1));     // the whole warp goes on, or none of it
             if (!ok) break;
             const int key_base = key_begin + it * kTileKeys + warp * 16;
             if (key_base < key_end) {
@@ -752,7 +754,7 @@ __global__ void __launch_bounds__(kDecodeThreads) __maxnreg__(DMAX <= 128 ? 168 
         bool ok = true;
         for (int it = 0; it < n_tiles; ++it) {
             const int stage = it % kDecodeStages;
-            ok = mbar_wait(ring.full_bar(stage), (it / kDecodeStages) & 1);
+            ok = __all_sync(0xffffffffu, mbar_wait(ring.full_bar(stage), (it / kDecodeStages) & 1));
             if (!ok) break;
             const int key0 = key_begin + it * kTileKeys;
             if (warp_active && key0 <= warp_last && key0 + kTileKeys - 1 >= warp_lo_min) {
@@ -906,29 +908,39 @@ MLR_API int mlr_attention_decode_bf16_no_alloc(const void* q, int ldq, void* out
     MLR_REQUIRE(static_cast<long long>(n_items) * kv_heads <= MLR_ATTENTION_STATIC_COUNTERS,
                 "attention_decode_bf16_no_alloc: %d requests x %d kv heads exceed the %d built-in counters", n_items, kv_heads,
                 MLR_ATTENTION_STATIC_COUNTERS);
-    // Device addresses of the arrays, looked up once per device with that device current.
+    // Device addresses of the arrays, looked up once per device with that device current.  Both
+    // addresses of a device are published together under a lock, so a second host thread never
+    // sees one without the other.
     constexpr int kMaxDevices = 64;
-    static float* address[kMaxDevices] = {};
-    static int* counter_address[kMaxDevices] = {};
+    struct Addresses {
+        float* scratch;
+        int* counters;
+    };
+    static Addresses table[kMaxDevices] = {};
+    static std::mutex table_lock;
     int device = -1;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return mlr_fail("attention_decode_bf16_no_alloc: cudaGetDevice: %s", cudaGetErrorString(e));
     MLR_REQUIRE(device >= 0 && device < kMaxDevices, "attention_decode_bf16_no_alloc: device index %d is not below %d", device, kMaxDevices);
-    if (address[device] == nullptr) {
-        void* found = nullptr;
-        e = cudaGetSymbolAddress(&found, mlr_static_scratch);
-        if (e != cudaSuccess || found == nullptr)
-            return mlr_fail("attention_decode_bf16_no_alloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-        void* found_counters = nullptr;
-        e = cudaGetSymbolAddress(&found_counters, mlr_static_counters);
-        if (e != cudaSuccess || found_counters == nullptr)
-            return mlr_fail("attention_decode_bf16_no_alloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-        counter_address[device] = static_cast<int*>(found_counters);
-        address[device] = static_cast<float*>(found);
+    Addresses found;
+    {
+        std::lock_guard<std::mutex> guard(table_lock);
+        if (table[device].scratch == nullptr) {
+            void* scratch = nullptr;
+            e = cudaGetSymbolAddress(&scratch, mlr_static_scratch);
+            if (e != cudaSuccess || scratch == nullptr)
+                return mlr_fail("attention_decode_bf16_no_alloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            void* counters = nullptr;
+            e = cudaGetSymbolAddress(&counters, mlr_static_counters);
+            if (e != cudaSuccess || counters == nullptr)
+                return mlr_fail("attention_decode_bf16_no_alloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            table[device] = Addresses{static_cast<float*>(scratch), static_cast<int*>(counters)};
+        }
+        found = table[device];
     }
     return mlr_attention_decode_bf16(q, ldq, out, ldo, cache, num_pages, items, n_items, segment_info, block_table,
                                      table_stride, page_size, q_heads, kv_heads, head_dim, window, scale, chunk,
-                                     max_splits, address[device], counter_address[device], status, stream);
+                                     max_splits, found.scratch, found.counters, status, stream);
 }
 
 // tiles: n_tiles pairs {segment, first token of a 64-row tile of that segment}.

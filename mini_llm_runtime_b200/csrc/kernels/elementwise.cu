@@ -154,15 +154,6 @@ __global__ void __launch_bounds__(1024) rmsnorm_cached_kernel(float* __restrict_
     }
 }
 
-// h[row,:] += delta[row,:] for all rows (when no norm follows).
-__global__ void residual_add_kernel(float* __restrict__ h, const float* __restrict__ delta, size_t count) {
-    mlr_grid_dependents_may_start();
-    mlr_grid_wait();
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < count;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x)
-        h[i] += delta[i];
-}
-
 // ------------------------------------------------------------------ q/k norm, rotation, cache write
 // One warp per (row, head).  Heads [0,Hq) are queries (normed and rotated in place),
 // [Hq,Hq+Hkv) keys (normed, rotated, written to the cache; also in place), the last Hkv
@@ -539,14 +530,6 @@ MLR_API int mlr_rmsnorm(float* h, const float* delta, int slices, long long slic
     else MLR_LAUNCH(float, float);
 #undef MLR_LAUNCH
     return mlr_launched("rmsnorm");
-}
-
-MLR_API int mlr_residual_add(float* h, const float* delta, long long count, cudaStream_t stream) {
-    MLR_REQUIRE(count >= 0, "residual_add: negative count");
-    if (count == 0) return 0;
-    const int blocks = static_cast<int>(count / 1024 + 1 < 4096 ? count / 1024 + 1 : 4096);
-    mlr_launch((residual_add_kernel), dim3(blocks), dim3(256), 0, stream, h, delta, static_cast<size_t>(count));
-    return mlr_launched("residual_add");
 }
 
 MLR_API int mlr_qk_norm_rope_cache(void* qkv, int act_bf16, int ld, const float* partials, int slices,

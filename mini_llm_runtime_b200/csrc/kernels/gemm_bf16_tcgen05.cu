@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(kThreads) gemm_tcgen05_kernel(const __grid_con
             const int tile = unit % (tiles_p * tiles_q);
             const int p0 = (tile % tiles_p) * kTileP, q0 = (tile / tiles_p) * BN;
             void* out = static_cast<char*>(out_base) + static_cast<size_t>(split_of(unit)) * split_stride * (out_f32 ? 4 : 2);
-            ok = mbar_wait(acc_full_bar(acc), (local >> 1) & 1);
+            ok = __all_sync(0xffffffffu, mbar_wait(acc_full_bar(acc), (local >> 1) & 1));     // the whole warp goes on, or none of it
             if (!ok) break;
             tmem_fence_after();
             const int p = p0 + quarter * 32 + lane;

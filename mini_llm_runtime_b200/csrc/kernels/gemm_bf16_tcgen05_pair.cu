@@ -149,7 +149,7 @@ __global__ void __launch_bounds__(kThreads) gemm_tcgen05_pair_kernel(const __gri
             const int acc = local & 1;
             const int p = (tile % tiles_p) * 2 * kRows + rank * kRows + quarter * 32 + lane;
             const int q0 = (tile / tiles_p) * kTileN;
-            ok = mbar_wait(acc_full_bar(acc), (local >> 1) & 1);
+            ok = __all_sync(0xffffffffu, mbar_wait(acc_full_bar(acc), (local >> 1) & 1));     // the whole warp goes on, or none of it
             if (!ok) break;
             tmem_fence_after();
             const uint32_t row_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kTileN;

@@ -45,13 +45,6 @@ def rmsnorm(h: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
          ptr(rows), count, h.shape[1], float(eps), int(write_back), stream())
 
 
-def residual_add(h: torch.Tensor, delta: torch.Tensor) -> None:
-    on_gpu(h, delta)
-    expect(h, torch.float32, "the residual stream")
-    expect(delta, torch.float32, "the residual delta")
-    call("elementwise", "mlr_residual_add", ptr(h), ptr(delta), h.numel(), stream())
-
-
 def qk_norm_rope_cache(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int,
                        q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                        cos_sin: Optional[torch.Tensor], positions: torch.Tensor, segment_of_row: torch.Tensor,

@@ -29,7 +29,6 @@ _SIGNATURES = {
         "mlr_rmsnorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
                         c_float, c_int, c_void_p],
         "mlr_swiglu_sliced": [c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-        "mlr_residual_add": [c_void_p, c_void_p, c_longlong, c_void_p],
         "mlr_qk_norm_rope_cache": [c_void_p, c_int, c_int, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int,
                                    c_void_p, c_void_p, c_int,
                                    c_float, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
@@ -54,7 +53,6 @@ _SIGNATURES = {
         "mlr_attention_prefill_tcgen05": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
                                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                           c_void_p, c_void_p],
-        "mlr_attention_prefill_tcgen05_supports": [c_int, c_int],
     },
     "gemm_bf16_tcgen05": {
         "mlr_gemm_bf16_tcgen05": [c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong,

@@ -1,10 +1,10 @@
 """A small, fixed workload for profilers: a few decode steps or one prefill of the
 Qwen3-8B layer sizes with few layers, bracketed by cudaProfilerStart/Stop.
 
-    python -m mini_llm_runtime_b200.profiling decode  [--layers 2] [--batch 8] [--context 8192] [--steps 2]
-    python -m mini_llm_runtime_b200.profiling prefill [--layers 2] [--tokens 2048] [--mma-sync-attention]
-    python -m mini_llm_runtime_b200.profiling attention [--page-size 64]
-    python -m mini_llm_runtime_b200.profiling products  [--tokens 2048]
+    python profile_workload.py decode  [--layers 2] [--batch 8] [--context 8192] [--steps 2]
+    python profile_workload.py prefill [--layers 2] [--tokens 2048] [--mma-sync-attention]
+    python profile_workload.py attention [--page-size 64]
+    python profile_workload.py products  [--tokens 2048]
 
 `attention` times the two bfloat16 attention kernels alone (CUDA events, no model) over a
 range of prompt lengths, contexts, batch sizes and head sizes and prints two tables.
@@ -13,14 +13,26 @@ the 8B layer sizes: the two-SM tcgen05 kernel with each epilogue, the one-block 
 the vendor library, each timed over a loop with the L2 flushed between launches; the profiled
 region holds three launches of the two-SM kernel with the gate epilogue.
 
-Meant to run under `ncu --profile-from-start off ...`: with two layers it holds about
-4 GB on the device and launches a few dozen kernels inside the profiled region, so a
-capture ends by itself within a minute or two.  Run it once without the profiler first;
-it prints the time per step it measured with CUDA events.
+Meant to run under ncu, which must be given `--clock-control none` every time (its default
+locks the GPU's clocks, and the lock can outlast the process on a shared GPU):
+
+    ncu --clock-control none --profile-from-start off --metrics gpu__time_duration.sum \
+        --csv --log-file launches.csv python profile_workload.py decode          (every launch of the region)
+    ncu --clock-control none --profile-from-start off --set full -k regex:<one kernel> -c 2 \
+        -o report python profile_workload.py decode                             (one kernel in depth)
+
+With two layers it holds about 4 GB on the device and launches a few dozen kernels inside
+the profiled region, so a capture ends by itself within a minute or two.  Run the same
+command once without the profiler first; it prints the time per step measured with CUDA events.
+This file is a measurement tool beside `bench.py`; nothing in the package imports it.
 """
 from __future__ import annotations
 
 import argparse
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 import torch
 
@@ -53,9 +65,9 @@ def main() -> int:
     if args.mode == "products":
         return product_table(args.tokens)
 
-    from .engine.loading import random_model
-    from .engine.model import CacheConfig, StepEntry
-    from .sampling.sampler import Sampler
+    from mini_llm_runtime_b200.engine.loading import random_model
+    from mini_llm_runtime_b200.engine.model import CacheConfig, StepEntry
+    from mini_llm_runtime_b200.sampling.sampler import Sampler
 
     cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
     length = args.context if args.mode == "decode" else args.tokens
@@ -124,7 +136,7 @@ def product_table(rows: int) -> int:
     """The products of one layer of the 8B sizes for `rows` tokens, each kernel alone: median
     of 20 launches after 3, a 256 MB buffer written between launches so that operands come
     from DRAM."""
-    from .ops import functions as F
+    from mini_llm_runtime_b200.ops import functions as F
     dev = "cuda:0"
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
@@ -191,8 +203,8 @@ def attention_tables(page: int) -> int:
     in random order for decode; time per launch from CUDA events over 10 launches after 3."""
     import math
 
-    from .ops import attention as A
-    from .ops import functions as F
+    from mini_llm_runtime_b200.ops import attention as A
+    from mini_llm_runtime_b200.ops import functions as F
     dev = "cuda:0"
 
     def timed(fn, reps=10):

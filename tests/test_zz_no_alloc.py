@@ -6,8 +6,10 @@ would break.  `mlr_attention_decode_bf16_no_alloc` keeps the partial results of 
 key splits in an array that is part of the library's device image instead of a
 caller's buffer.  This test calls it through its exported C symbol, twice in a row
 (the second call finds the first call's leftovers in the array), and wants the same
-output as the normal entry point given a scratch buffer.  It also checks that a
-call too large for the array is refused.
+output as the normal entry point given a scratch buffer, and the same as a plain float64
+attention over the same cache.  The driver's count of free device memory must not move
+across a call.  A call too large for the array, or with more requests and kv heads than
+the built-in counters, is refused.
 
 The file sorts last so that a run that stops at the first failure has run every
 other test before it.
@@ -63,14 +65,31 @@ def test_no_alloc_entry_point_matches_the_normal_one():
         F.attention_decode_bf16(qkv, want, cache, None, n, info, table, page, Hq, Hkv, D, 0, scale, chunk, splits,
                                 partial, status)
         got = torch.full((n, Hq * D), float("nan"), dtype=torch.bfloat16, device=DEV)
-        before = torch.cuda.memory_allocated()
+        torch.cuda.synchronize()
+        # Free memory as the driver counts it: an allocation inside the library would show here
+        # (torch's own counters would not see it).  The first call may still load the kernel's
+        # module, so the figure is compared across the second call.
+        free_before = torch.cuda.mem_get_info()[0]
         assert call_no_alloc(qkv, got, status) == 0, lib.mlr_last_error().decode()
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        if round_ == 1:
+            assert torch.cuda.mem_get_info()[0] == free_before, "device memory was taken during the call"
         assert status.item() == 0 and torch.isfinite(got.float()).all()
         # Same kernels, same order of summation: the tolerance of the kernel tests holds with room to spare.
         assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2), f"call {round_}"
         assert torch.equal(got, want), f"call {round_}"
+        # A second witness that shares no code with either entry point: dense float64 attention.
+        plain = torch.empty(n, Hq, D, dtype=torch.float64)
+        host_cache, host_table, q = cache.float().cpu(), table.cpu(), qkv[:, :Hq * D].float().cpu().view(n, Hq, D)
+        for i, c in enumerate(contexts):
+            position = torch.arange(c)
+            rows = host_cache[host_table[i, position // page].long(), :, :, position % page]        # [c, 2, Hkv, D]
+            column = torch.arange(D)[None, :] ^ ((position[:, None] & 7) << 3)                       # the cache's stored order
+            rows = torch.gather(rows, 3, column[:, None, None, :].expand(c, 2, Hkv, D))
+            k, v = (rows[:, j].double().repeat_interleave(Hq // Hkv, 1) for j in (0, 1))             # [c, Hq, D]
+            p = torch.softmax(torch.einsum("hd,thd->ht", q[i].double(), k) * scale, dim=-1)
+            plain[i] = torch.einsum("ht,thd->hd", p, v)
+        assert torch.allclose(got.float().cpu().double().view(n, Hq, D), plain, atol=2e-2, rtol=2e-2), f"call {round_}"
 
     # A call that needs more scratch than the array holds is refused before any launch.
     too_many = 1 << 20
@@ -78,3 +97,10 @@ def test_no_alloc_entry_point_matches_the_normal_one():
               info.data_ptr(), table.data_ptr(), table.stride(0), page, Hq, Hkv, D, 0, scale, 64, too_many,
               status.data_ptr(), stream)
     assert code != 0 and "the built-in array holds" in lib.mlr_last_error().decode()
+    # So is a call with more requests x kv heads than the built-in counters (4096): from its sizes
+    # alone, before anything is read.  (Such a call also outgrows the scratch array, whichever
+    # head size and split count it has; either refusal is a refusal.)
+    code = fn(qkv.data_ptr(), qkv.stride(0), got.data_ptr(), got.stride(0), cache.data_ptr(), pages, None, 4097,
+              info.data_ptr(), table.data_ptr(), table.stride(0), page, Hq, 1, 16, 0, scale, 64, 1,
+              status.data_ptr(), stream)
+    assert code != 0 and "built-in" in lib.mlr_last_error().decode()
