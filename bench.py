@@ -343,15 +343,14 @@ def main() -> int:
 
         for _ in range(warmup):
             one_step()
-        native.launch_count = 0
-        model.graph_launches = 0
+        native.reset_launches()
         if with_clocks:
             with ClockSampler() as clocks:
                 ms = timed(one_step, steps)
             clock_summary = clocks.summary()
         else:
             ms, clock_summary = timed(one_step, steps), None
-        launches = native.launch_count + model.graph_launches
+        launches = native.total_launches()
         for s in slots:
             model.close_request(s)
         return batch / ms * 1e3, ms, launches, clock_summary

@@ -33,6 +33,22 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-Wall"]
 
+
+def cuda_home() -> str:
+    for var in ("CUDA_HOME", "CUDA_PATH"):
+        if os.environ.get(var):
+            return os.environ[var]
+    return "/usr/local/cuda"
+
+
+def host_link_flags() -> List[str]:
+    """The host library calls the CUDA runtime (copies, events, graph capture; linked statically like
+    the kernel modules' own) and the vendor's matrix-product library."""
+    home = cuda_home()
+    lib = os.path.join(home, "lib64")
+    return ["-I", os.path.join(home, "include"), "-L", lib, "-Wl,-rpath," + lib, "-lcublas", "-lcudart_static", "-ldl", "-lrt",
+            "-lpthread"]
+
 # Extra link flags per kernel module (none needs any today: the tensor-map encoder of the
 # driver is looked up at run time through cudaGetDriverEntryPoint).
 MODULE_LINK = {}
@@ -103,12 +119,13 @@ def _target(name: str):
     out_dir = build_dir()
     if name == "host":
         sources = sorted(os.path.join(HOST_DIR, f) for f in os.listdir(HOST_DIR) if f.endswith(".cpp"))
-        tag = _digest(sources, HOST_FLAGS)
+        link = host_link_flags()
+        tag = _digest(sources, HOST_FLAGS + link)
         out = os.path.join(out_dir, f"libmlr_host-{tag}.so")
         cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
         if not cxx:
             raise NativeBuildError("no C++ compiler found (g++ or c++) for the host library")
-        return out, [cxx, *HOST_FLAGS, *sources, "-o"]
+        return out, [cxx, *HOST_FLAGS, *sources, *link, "-o"]
     source = os.path.join(KERNEL_DIR, name + ".cu")
     if not os.path.isfile(source):
         raise NativeBuildError(f"unknown kernel module {name!r}; known: {kernel_modules()}")

@@ -28,6 +28,7 @@ from ..config.registry import part_class
 from ..csrc import build
 from ..parts.base import Block, CacheNeed, RunContext, Segment, StateNeed, StepContext
 from ..weights.loader import WeightSpec, merge_specs
+from .executor import (NativeStepper, STEP_FAILED, STEP_NO_PAGES, STEP_OK, STEP_POISONED, STEP_REFUSED)
 from .runtime import Runtime
 
 
@@ -118,22 +119,21 @@ class Model:
         # For tests: called with (group, slots, table rows on the host) after a step's block table is
         # filled and before it is uploaded; it may change the rows it is given.
         self.table_hook = None
+        self._hook_sent = None
         self.last_h2d_bytes = 0
-        # Decode steps are replayed from CUDA graphs unless a mixer keeps state that a
-        # repeated run would advance twice (capturing runs a step more than once) or a part
-        # says that its forward cannot be captured.
+        # A model whose parts all compile (`Part.compiles`) and keep no per-request state runs its steps
+        # in the native executor (programs of launches, CUDA graphs for decode shapes); any other
+        # model is stepped from Python, part by part, without graphs.
+        self._native: Optional[NativeStepper] = None
+        self._compiles = (all(r.state_need is None for r in self.runs) and all(p.compiles() for p in self._all_parts())
+                          and all(b.compiles() for b in self.blocks))
         self.use_graphs = True
-        self._graphable = all(r.state_need is None for r in self.runs) and all(p.graph_safe for p in self._all_parts())
         # Table width of a graph, in blocks: a graph serves the contexts of one bucket, and its
         # attention launch is planned for the bucket's upper end.  Set to about 1024 tokens when
         # the cache is allocated (a wider bucket plans key splits that short contexts leave idle).
         self.graph_bucket_blocks = 64
         self.max_graphs = 48
-        self.graph_after = 2        # steps of a shape that run kernel by kernel before the shape is captured
-        self._graphs = {}
-        self._graph_uses = {}
-        self._graph_pool = None
-        self.graph_launches = 0
+        self.graph_after = 2        # steps of a shape that run launch by launch before the shape is captured
 
     # ------------------------------------------------------------------ weights
     def _all_parts(self):
@@ -163,7 +163,6 @@ class Model:
         self.rt.end_load()
         self.status = torch.zeros(1, dtype=torch.int32, device=self.rt.device)
         self.rt.status = self.status
-        self._graph_pool = torch.cuda.graph_pool_handle()
         self._bound = True
 
     # ------------------------------------------------------------------ cache
@@ -192,6 +191,37 @@ class Model:
             source = self.plan.schedule[i].kv_from
             if source is not None:
                 run.context.cache = self.runs[source].context.cache
+        self._native = NativeStepper(self) if self._compiles else None
+
+    def emit_program(self, b) -> None:
+        """The whole step as the parts describe it to a program builder: embedding, the runs in the
+        plan's order, the final norm over the wanted rows, the head.  The residual stream lives for
+        the whole step; what a run needs is cut from two alternating banks, so the contribution a run
+        leaves pending for the next norm is not overwritten by that next run."""
+        h = self.embedding.emit(b)
+        b.start_banks()
+        pending = None
+        for run in self.runs:
+            b.next_bank()
+            pending = run.block.emit(b, h, pending, run.context)
+        b.next_bank()
+        x = self.final_norm.emit(b, h, pending, True)
+        self.lm_head.emit(b, x)
+
+    @property
+    def _graphs(self):
+        """The decode shapes that have a CUDA graph (only their number is of interest outside)."""
+        return list(range(self._native.graph_count())) if self._native is not None else []
+
+    @property
+    def graph_launches(self) -> int:
+        """Launches that graph replays stood for so far."""
+        return self._native.graph_launches if self._native is not None else 0
+
+    @property
+    def steady_state_allocations(self) -> int:
+        """How often a buffer of the native stepper had to grow (it stops once the largest step has been seen)."""
+        return self._native.allocations if self._native is not None else 0
 
     def cache_bytes_per_token(self) -> int:
         element = 2 if self.rt.is_bf16 else 4
@@ -205,6 +235,8 @@ class Model:
     def _poison(self, why: str) -> None:
         if self.poisoned is None:
             self.poisoned = why
+            if self._native is not None:
+                self._native.poison(why)
 
     def open_request(self) -> int:
         self._refuse_if_poisoned()
@@ -269,14 +301,64 @@ class Model:
         decode loop can feed sampled ids back without a round trip to the host.
 
         A step of single tokens that wants every row's logits is replayed from a CUDA
-        graph (captured on first use per batch size and context bucket).  Its logits
-        live in the graph's memory: read or sample them before the next step.
+        graph (captured when its batch size and context bucket come for the third time).
+        The logits live in a buffer that the next step writes again: read or sample them
+        before the next step.
 
         Failure: a batch that is refused, or a pool that cannot hold it, raises before any
         device work and changes nothing.  An exception after device work has begun rolls the
         ledger back (the step's pages, lengths, and the fixed-size state of its requests as
         they were before the step), poisons the model and is raised again."""
         self._refuse_if_poisoned()
+        if not self._bound or self.cache is None:
+            raise StepError("the model has no weights or no cache yet")
+        if self._native is not None:
+            return self._native_step(entries, device_tokens)
+        return self._python_step(entries, device_tokens)
+
+    def _native_step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """The step in the native executor: everything from the validation of the entries to the
+        publishing of lengths happens in `mlr_model_step`; this only hands over the entries."""
+        native_model = self._native
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        slots = [e.slot for e in entries]
+        counts = [len(e.tokens) for e in entries]
+        offsets, places = [0], []
+        for e in entries:
+            places.extend(e.want)
+            offsets.append(len(places))
+        rows = sum(counts)
+        tokens = None
+        if device_tokens is None:
+            tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries]) if rows else np.zeros(0, np.int64)
+            if rows and (tokens.min() < 0 or tokens.max() >= self.plan.vocab_size):
+                raise StepError(f"a token id is outside the vocabulary of {self.plan.vocab_size}")
+            tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        elif device_tokens.dtype is not torch.int32 or device_tokens.numel() != rows or not device_tokens.is_cuda:
+            raise StepError("device_tokens must be int32 on the device with one id per row of the step")
+        native_model.set_graphs(self.use_graphs, self.graph_after, self.graph_bucket_blocks, self.max_graphs)
+        if (self.table_hook is None) != (native_model._hook is None) or self.table_hook is not self._hook_sent:
+            native_model.set_table_hook(self.table_hook)
+            self._hook_sent = self.table_hook
+        from ..ops import native
+        code, message, logits = native_model.step(slots, counts, tokens, offsets, places, device_tokens, native.stream())
+        self.last_h2d_bytes = int(native_model.last_info.h2d_bytes)
+        if code == STEP_OK:
+            return logits
+        if code == STEP_REFUSED:
+            raise StepError(message)
+        if code == STEP_NO_PAGES:
+            raise OutOfPages(message)
+        if code == STEP_POISONED:
+            raise Poisoned(message)
+        self.poisoned = self.poisoned or message
+        raise native.KernelError(message)
+
+    def _python_step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """The step driven from Python, for models with parts that do not compile into programs:
+        the same order of work (validate, take pages, pack and upload the metadata, run the parts,
+        publish), every part through its `forward`.  No CUDA graphs on this path."""
         segments, rows = self._validate(entries)
         n = len(segments)
         vocab = self.plan.vocab_size
@@ -287,22 +369,11 @@ class Model:
             raise StepError("device_tokens must be int32 with one id per row of the step")
         want_rows = [s.row + w for s, e in zip(segments, entries) for w in e.want]
         all_single = all(s.count == 1 for s in segments)
-        graphed = self.use_graphs and self._graphable and all_single and len(want_rows) == rows
         self.cache.prepare([s.slot for s in segments], [s.count for s in segments])
         try:
             page = self.cache_config.page_size
             max_context = max(s.start + s.count for s in segments)
             columns = (max_context + page - 1) // page
-            if graphed:
-                # A shape is captured once it has come `graph_after` times: capturing costs several
-                # steps' time, which a batch size that lasts a step or two (requests ending one
-                # after the other) never pays back.
-                bucketed = min(-(-columns // self.graph_bucket_blocks) * self.graph_bucket_blocks, self.cache.max_blocks)
-                seen = self._graph_uses.get((rows, bucketed), 0)
-                self._graph_uses[(rows, bucketed)] = seen + 1
-                graphed = (rows, bucketed) in self._graphs or seen >= self.graph_after
-                if graphed:
-                    columns = bucketed
             n_groups = len(self.group_windows)
             # One packed int32 buffer: ids | positions | segment_of_row | info[n,4] | slots | want | tables
             sizes = [rows, rows, rows, 4 * n, n, len(want_rows)] + [n * columns] * n_groups
@@ -320,8 +391,6 @@ class Model:
             slots = [s.slot for s in segments]
             for g in range(n_groups):
                 table = host[offsets[6 + g]:offsets[7 + g]].view(n, columns)
-                if graphed:
-                    table.fill_(-1)
                 self.cache.fill_table(g, slots, table, min(columns, self.cache.max_blocks))
                 if self.table_hook is not None:
                     self.table_hook(g, slots, table)
@@ -332,26 +401,19 @@ class Model:
         journal = None
         try:
             journal = self._journal_state(slots)
-
-            def context_on(device: torch.Tensor, bound: Optional[int]) -> StepContext:
-                part = lambda k: device[offsets[k]:offsets[k + 1]]
-                return StepContext(
-                    rt=self.rt, num_rows=rows, segments=segments, token_ids=part(0), positions=part(1),
-                    segment_of_row=part(2), segment_info=part(3).view(n, 4), slots=part(4),
-                    tables={g: part(6 + g).view(n, columns) for g in range(n_groups)},
-                    page_size=page, status=self.status, max_count=max(s.count for s in segments),
-                    max_context=max_context, all_single=all_single, context_bound=bound)
-
-            if graphed:
-                logits = self._replay(host[:total], rows, columns, context_on, offsets, device_tokens)
-            else:
-                device = torch.empty(total, dtype=torch.int32, device=self.rt.device)
-                device.copy_(host[:total], non_blocking=True)
-                self._pinned[self._pinned_current][1].record()
-                if device_tokens is not None:
-                    device[:rows].copy_(device_tokens)
-                step = context_on(device, None)
-                logits = self._forward(step, device[offsets[5]:offsets[6]] if want_rows else None)
+            device = torch.empty(total, dtype=torch.int32, device=self.rt.device)
+            device.copy_(host[:total], non_blocking=True)
+            self._pinned[self._pinned_current][1].record()
+            if device_tokens is not None:
+                device[:rows].copy_(device_tokens)
+            part = lambda k: device[offsets[k]:offsets[k + 1]]
+            step = StepContext(
+                rt=self.rt, num_rows=rows, segments=segments, token_ids=part(0), positions=part(1),
+                segment_of_row=part(2), segment_info=part(3).view(n, 4), slots=part(4),
+                tables={g: part(6 + g).view(n, columns) for g in range(n_groups)},
+                page_size=page, status=self.status, max_count=max(s.count for s in segments),
+                max_context=max_context, all_single=all_single, context_bound=None)
+            logits = self._forward(step, part(5) if want_rows else None)
         except BaseException as error:
             self._poison(f"a step failed after its device work had begun: {type(error).__name__}: {error}")
             try:
@@ -376,45 +438,6 @@ class Model:
     def _restore_state(self, journal) -> None:
         for state, slot, saved in journal or ():
             state[slot].copy_(saved)
-
-    def _replay(self, host: torch.Tensor, rows: int, columns: int, context_on, offsets, device_tokens):
-        """Decode steps from a CUDA graph: one graph per (batch size, table width).  The
-        graph reads its metadata from a fixed device buffer that is refreshed before
-        every replay; launch shapes that depend on the context (how the keys are split)
-        are planned for the bucket's upper bound and the kernels read the true lengths
-        from the metadata."""
-        key = (rows, columns)
-        entry = self._graphs.get(key)
-        if entry is None:
-            if len(self._graphs) >= self.max_graphs:
-                self._graphs.pop(next(iter(self._graphs)))
-            static = torch.empty(host.numel(), dtype=torch.int32, device=self.rt.device)
-            static.copy_(host, non_blocking=True)
-            if device_tokens is not None:
-                static[:rows].copy_(device_tokens)
-            step = context_on(static, columns * self.cache_config.page_size)
-            want = static[offsets[5]:offsets[6]]
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                self._forward(step, want)          # warm-up outside the capture (the step is idempotent)
-            torch.cuda.current_stream().wait_stream(side)
-            graph = torch.cuda.CUDAGraph()
-            step.scratch.clear()
-            from ..ops import native
-            before = native.launch_count
-            with torch.cuda.graph(graph, pool=self._graph_pool):
-                logits = self._forward(step, want)
-            entry = (graph, static, logits, native.launch_count - before)
-            self._graphs[key] = entry
-        graph, static, logits, kernels = entry
-        self.graph_launches += kernels      # launches of this package's kernels a replay stands for
-        static.copy_(host, non_blocking=True)
-        self._pinned[self._pinned_current][1].record()
-        if device_tokens is not None:
-            static[:rows].copy_(device_tokens)
-        graph.replay()
-        return logits
 
     def _forward(self, step: StepContext, want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         h = self.embedding.forward(step)

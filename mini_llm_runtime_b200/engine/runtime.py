@@ -34,13 +34,41 @@ from typing import Optional
 import torch
 
 from ..ops import functions as F
+from . import executor
+from .builder import Buf
 
 
 class NonFiniteWeights(ValueError):
     """A tensor of the checkpoint holds a NaN or an infinity; the message names every such tensor."""
 
 
+_library_workspace = {}     # device index -> the vendor library's workspace there (kept for the life of the process)
+
+
+def _give_library_workspace(device: torch.device) -> None:
+    """The vendor library gets 32 MiB of workspace from this package once per device, so that it
+    allocates none of its own: a CUDA graph capture would not allow that, and a step in the steady
+    state is to allocate nothing."""
+    index = device.index or 0
+    if index not in _library_workspace:
+        space = torch.empty(32 << 20, dtype=torch.uint8, device=device)
+        with torch.cuda.device(device):
+            if executor.library().mlr_library_set_workspace(space.data_ptr(), space.numel()) != 0:
+                raise RuntimeError(executor.library().mlr_exec_error().decode())
+        _library_workspace[index] = space
+
+
+_ROUTING = {"use_tcgen05", "tcgen05_prefill", "pair_rows", "pair_everything", "tcgen05_attention", "decode_rows",
+            "own_activation_products", "pair_min_tiles"}
+
+
 class Runtime:
+    def __setattr__(self, name, value):
+        # A change of a routing setting outdates the programs recorded with the old one.
+        if name in _ROUTING:
+            object.__setattr__(self, "routing_version", getattr(self, "routing_version", 0) + 1)
+        object.__setattr__(self, name, value)
+
     def __init__(self, dtype: torch.dtype = torch.bfloat16, device: str = "cuda:0"):
         if dtype not in (torch.float32, torch.bfloat16):
             raise ValueError(f"precision must be float32 or bfloat16, got {dtype}")
@@ -73,11 +101,11 @@ class Runtime:
         # result at once, and the decode step is 3-4 % faster that way at 1 to 8 rows.
         self.own_activation_products = False
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        if dtype is torch.bfloat16:
+            _give_library_workspace(self.device)
         self.pair_min_tiles = self.sm_count   # ... and only with at least this many 256 x 256 tiles
         self._splits = {}
-        self._views = {}
         self._counters = None
-        self._retired = []
         self.status = None        # the model's device status word (set at bind time)
         self._shared = {}
         self._load_names = None   # while weights are bound: id(source tensor) -> name, for the finiteness check
@@ -151,97 +179,114 @@ class Runtime:
 
     def split_counters(self, count: int) -> torch.Tensor:
         """Zeroed int32 counters for kernels that merge their own split results and leave the
-        counters zero again.  One long-lived tensor, made outside any graph capture, so a
-        captured step keeps pointing at it."""
+        counters zero again (steps that Python drives; the native executor has its own)."""
         if self._counters is None or count > self._counters.numel():
-            if torch.cuda.is_current_stream_capturing():
-                raise RuntimeError("the split counters must be sized before a step is captured")
-            if self._counters is not None:
-                self._retired.append(self._counters)     # graphs captured earlier still point at it
             self._counters = torch.zeros(max(2 * count, 1 << 14), dtype=torch.int32, device=self.device)
         return self._counters
 
-    # ---- y = x @ w.T
-    def _transposed(self, w: torch.Tensor) -> torch.Tensor:
-        """The view w.T the library takes, made once per weight matrix (an eager step calls
-        for it some hundred times)."""
-        view = self._views.get(id(w))
-        if view is None or view[0] is not w:
-            if len(self._views) >= 4096:      # someone multiplies by matrices that come and go: do not hold on to them
-                self._views.clear()
-            view = self._views[id(w)] = (w, w.t())
-        return view[1]
+    # ---- y = x @ w.T, described to a builder (engine/builder.py)
+    # `b` is the builder of the step (eager) or of the program being recorded; `x` a Buf of it; `w` a
+    # weight tensor [N, K] on the device.  Every decision on a row count goes through `b.le` /
+    # `b.ge`, so that a recorded program knows for which row counts it holds.
+    def _tcgen05_ok(self, x: Buf, w: torch.Tensor) -> bool:
+        K = w.shape[1]
+        return (self.use_tcgen05 and x.dtype is torch.bfloat16 and w.dtype is torch.bfloat16 and K % 8 == 0 and K >= 8
+                and x.width == K and w.stride(1) == 1 and x.ld % 8 == 0 and w.stride(0) % 8 == 0 and x.ptr % 16 == 0
+                and w.data_ptr() % 16 == 0)
 
-    def _tcgen05_ok(self, x: torch.Tensor, w: torch.Tensor) -> bool:
-        return self.use_tcgen05 and self.status is not None and F.gemm_tcgen05_applies(x, w)
-
-    def _pair(self, x: torch.Tensor, w: torch.Tensor, gated: bool = False) -> bool:
-        """Whether this bf16 product runs on the two-SM kernel."""
-        if not (gated or self.pair_everything) or x.shape[0] < self.pair_rows or not self._tcgen05_ok(x, w):
+    def _pair(self, b, x: Buf, w: torch.Tensor, gated: bool = False) -> bool:
+        """Whether this bf16 product runs on the two-SM kernel: from `pair_rows` rows on, and only
+        with at least `pair_min_tiles` tiles of 256 x 256 (fewer leave pairs of SMs idle: a small
+        model's matrices; the library's smaller tiles do better then)."""
+        if not (gated or self.pair_everything) or not self._tcgen05_ok(x, w):
             return False
-        # Fewer 256 x 256 tiles than SMs leave pairs idle (a small model's matrices); the library's
-        # smaller tiles do better then.
-        tiles = -(-x.shape[0] // 256) * -(-w.shape[0] // 256)
-        return self.pair_everything or tiles >= self.pair_min_tiles
+        first = self.pair_rows
+        if not self.pair_everything:
+            across = -(-w.shape[0] // 256)
+            first = max(first, 256 * (-(-self.pair_min_tiles // across) - 1) + 1)
+        return b.ge(x.rows, first)
 
-    def _own_gemm(self, x: torch.Tensor, w: torch.Tensor) -> bool:
+    def _own_gemm(self, b, x: Buf, w: torch.Tensor) -> bool:
         """Whether this bf16 product runs on the one-block tcgen05 kernel: always for the few
         rows of a decode step; beyond those only when `tcgen05_prefill` is set."""
-        return (x.shape[0] <= self.decode_rows or self.tcgen05_prefill) and self._tcgen05_ok(x, w)
+        return self._tcgen05_ok(x, w) and (self.tcgen05_prefill or b.le(x.rows, self.decode_rows))
 
-    def linear(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-               activation: bool = False) -> torch.Tensor:
+    def _own_launch(self, b, x: Buf, w: torch.Tensor, out: Buf) -> None:
+        """The one-block tcgen05 product into `out` (bf16, float32, or float32 partial sums).  With up
+        to 64 rows the weight matrix takes the 128-row side of the instruction and the result is
+        stored transposed; otherwise x takes that side.  `w` must hold weights: the kernel starts to
+        fetch it before the kernels before it on the stream are done."""
+        N, K = w.shape
+        splits, stride = max(1, out.slices), out.slice_stride
+        f32 = int(out.dtype is torch.float32)
+        if b.le(x.rows, 64):
+            b.launch("gemm_bf16_tcgen05", "mlr_gemm_bf16_tcgen05", w.data_ptr(), w.stride(0), N, x.ptr, x.ld, x.rows, K, out.ptr,
+                     out.ld, f32, 1, 0, splits, stride, 1, b.status, b.stream, need=b.need_for(x.rows))
+        else:
+            b.launch("gemm_bf16_tcgen05", "mlr_gemm_bf16_tcgen05", x.ptr, x.ld, x.rows, w.data_ptr(), w.stride(0), N, K, out.ptr,
+                     out.ld, f32, 0, 0, splits, stride, 2, b.status, b.stream, need=b.need_for(x.rows))
+
+    def _pair_launch(self, b, x: Buf, w: torch.Tensor, out: Buf, epilogue: str) -> None:
+        b.launch("gemm_bf16_tcgen05_pair", "mlr_gemm_bf16_tcgen05_pair", x.ptr, x.ld, x.rows, w.data_ptr(), w.stride(0), w.shape[0],
+                 w.shape[1], out.ptr, out.ld, F.PAIR_EPILOGUES[epilogue], b.status, b.stream, need=b.need_for(x.rows))
+
+    def _library_launch(self, b, x: Buf, w: torch.Tensor, out: Buf, accumulate: bool = False) -> None:
+        """The vendor library's product (cuBLAS), as the reference sends all of its products there
+        (src/minillm/cuda/matrix.cpp:30-36)."""
+        b.launch("host", "mlr_library_gemm", x.ptr, x.ld, x.rows, w.data_ptr(), w.stride(0), w.shape[0], w.shape[1], out.ptr,
+                 out.ld, int(out.dtype is torch.float32), int(accumulate), b.stream, need=b.need_for(x.rows))
+
+    def linear(self, b, x: Buf, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, activation: bool = False,
+               out: Optional[Buf] = None) -> Buf:
         """x W^T.  `activation`: the result feeds a row-wise kernel as an activation (q/k/v,
         gate/up) rather than the residual stream or the logits."""
         out_dtype = out_dtype or self.dtype
+        N, K = w.shape
+        if out is None:
+            out = b.temp(x.rows, N, torch.float32 if self.dtype is torch.float32 else out_dtype)
         if self.dtype is torch.float32:
-            out = torch.empty((x.shape[0], w.shape[0]), dtype=torch.float32, device=self.device)
-            F.gemm_f32(x, w, out)
-            return out
-        if self._pair(x, w):
-            out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=self.device)
-            F.gemm_bf16_tcgen05_pair(x, w, out, self.status, "bf16" if out_dtype is torch.bfloat16 else "f32")
-            return out
-        if self._own_gemm(x, w) and (not activation or self.own_activation_products or self.tcgen05_prefill):
-            out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=self.device)
-            F.gemm_bf16_tcgen05(x, w, out, self.status)
-            return out
-        if out_dtype is torch.bfloat16:
-            return torch.mm(x, self._transposed(w))
-        return torch.mm(x, self._transposed(w), out_dtype=out_dtype)
+            b.launch("gemm_f32", "mlr_gemm_f32", x.ptr, w.data_ptr(), out.ptr, x.rows, N, K, x.ld, w.stride(0), out.ld, b.stream,
+                     need=b.need_for(x.rows))
+        elif self._pair(b, x, w):
+            self._pair_launch(b, x, w, out, "bf16" if out.dtype is torch.bfloat16 else "f32")
+        elif (not activation or self.own_activation_products or self.tcgen05_prefill) and self._own_gemm(b, x, w):
+            self._own_launch(b, x, w, out)
+        else:
+            self._library_launch(b, x, w, out)
+        return out
 
-    def linear_partials(self, x: torch.Tensor, w: torch.Tensor, activation: bool = False) -> Optional[torch.Tensor]:
+    def linear_partials(self, b, x: Buf, w: torch.Tensor, activation: bool = False) -> Optional[Buf]:
         """For the few rows of a decode step: the product as float32 partial sums [S, M, N]
         over S ranges of K (so that a small weight matrix still occupies every SM); the
         kernel that reads them adds them up.  None when the product is not of that kind."""
-        if self.dtype is not torch.bfloat16 or x.shape[0] > self.decode_rows or not self._own_gemm(x, w):
+        if self.dtype is not torch.bfloat16 or (activation and not self.own_activation_products):
             return None
-        if activation and not self.own_activation_products:
+        if not self._tcgen05_ok(x, w) or not b.le(x.rows, self.decode_rows):
             return None
         key = (w.shape[0], w.shape[1])
         splits = self._splits.get(key)
         if splits is None:
-            splits = self._splits[key] = F.k_splits_for(w.shape[0], w.shape[1], self.sm_count)
-        out = torch.empty((splits, x.shape[0], w.shape[0]), dtype=torch.float32, device=self.device)
-        F.gemm_bf16_tcgen05(x, w, out, self.status)
+            splits = self._splits[key] = executor.k_splits_for(w.shape[0], w.shape[1], self.sm_count)
+        out = b.temp(x.rows, w.shape[0], torch.float32, slices=splits)
+        self._own_launch(b, x, w, out)
         return out
 
-    def linear_delta(self, x: torch.Tensor, w: torch.Tensor, into: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    def linear_delta(self, b, x: Buf, w: torch.Tensor, into: Optional[Buf] = None) -> Optional[Buf]:
         """A float32 contribution to the residual stream: [M, N], or [S, M, N] partial sums
         that the next norm adds up.  With `into` (the stream itself, float32 [M, N]) the
         product of a prompt portion adds its result there in its epilogue (into += x W^T,
         one rounding per element as the separate add had) and None is returned."""
-        parts = self.linear_partials(x, w)
+        parts = self.linear_partials(b, x, w)
         if parts is not None:
             return parts
-        if into is not None and self.dtype is torch.bfloat16 and into.dtype is torch.float32 and into.is_contiguous():
-            if self._pair(x, w):
-                F.gemm_bf16_tcgen05_pair(x, w, into, self.status, "add_f32")
+        if into is not None and self.dtype is torch.bfloat16 and into.dtype is torch.float32 and into.ld == into.width:
+            if self._pair(b, x, w):
+                self._pair_launch(b, x, w, into, "add_f32")
                 return None
-            if not self._own_gemm(x, w):
-                torch.addmm(into, x, self._transposed(w), out_dtype=torch.float32, out=into)
+            if not self._own_gemm(b, x, w):
+                self._library_launch(b, x, w, into, accumulate=True)
                 return None
-        return self.linear(x, w, out_dtype=torch.float32)
+        return self.linear(b, x, w, out_dtype=torch.float32)
 
     # ---- the gated pair of matrices of a feed-forward
     def stack_gate_up(self, w_gate: torch.Tensor, w_up: torch.Tensor):
@@ -256,14 +301,19 @@ class Runtime:
             return stacked, stacked.shape[0] // 2
         return torch.cat([w_gate, w_up], dim=0).contiguous(), w_gate.shape[0]
 
-    def gated_linear(self, x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    def gated_linear(self, b, x: Buf, w_gate_up: torch.Tensor) -> Buf:
         """silu(x Wgate^T) * (x Wup^T) for the operand `stack_gate_up` made."""
         inter = w_gate_up.shape[0] // 2
         block = F.GATE_BLOCK if self.dtype is torch.bfloat16 else inter
-        out = torch.empty((x.shape[0], inter), dtype=self.dtype, device=self.device)
-        if self.dtype is torch.bfloat16 and self._pair(x, w_gate_up, gated=True):
-            F.gemm_bf16_tcgen05_pair(x, w_gate_up, out, self.status, "silu_gate")
+        out = b.temp(x.rows, inter, self.dtype)
+        if self.dtype is torch.bfloat16 and self._pair(b, x, w_gate_up, gated=True):
+            self._pair_launch(b, x, w_gate_up, out, "silu_gate")
             return out
-        parts = self.linear_partials(x, w_gate_up, activation=True)
-        F.swiglu(parts if parts is not None else self.linear(x, w_gate_up, activation=True), out, block)
+        parts = self.linear_partials(b, x, w_gate_up, activation=True)
+        if parts is not None:
+            b.launch("elementwise", "mlr_swiglu_sliced", parts.ptr, parts.slices, parts.slice_stride, out.ptr, out.is_bf16, x.rows,
+                     inter, block, b.stream)
+        else:
+            both = self.linear(b, x, w_gate_up, activation=True)
+            b.launch("elementwise", "mlr_swiglu", both.ptr, out.ptr, out.is_bf16, x.rows, inter, block, b.stream)
         return out

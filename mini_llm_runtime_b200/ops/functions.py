@@ -316,19 +316,8 @@ def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor
     return padded.view(2, blocks, GATE_BLOCK, K).transpose(0, 1).reshape(2 * blocks * GATE_BLOCK, K)
 
 
-def k_splits_for(rows: int, K: int, sms: int = 148) -> int:
+def k_splits_for(rows: int, K: int, sms: int) -> int:
     """How many ranges to cut K into when a weight matrix of `rows` rows is streamed in tiles
-    of 128 rows: the smallest count whose units fill whole rounds of `sms` blocks to 93 % or
-    better, with at least four 64-wide blocks of K per range and at most 16 ranges."""
-    tiles = -(-rows // 128)
-    best, best_fill = 1, 0.0
-    for s in range(1, 17):
-        if s > 1 and -(-K // 64) // s < 4:
-            break
-        units = tiles * s
-        fill = units / (sms * -(-units // sms))
-        if fill > best_fill + 1e-9:
-            best, best_fill = s, fill
-        if fill >= 0.93:
-            return s
-    return best
+    of 128 rows by `sms` blocks at a time (decided by the native executor, `mlr_k_splits`)."""
+    from ..engine.executor import k_splits_for as native_k_splits
+    return native_k_splits(rows, K, sms)

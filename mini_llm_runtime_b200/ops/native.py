@@ -65,6 +65,10 @@ _SIGNATURES = {
     "sampling": {
         "mlr_sample": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     },
+    "host": {
+        "mlr_library_gemm": [c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_int, c_int,
+                             c_void_p],
+    },
     "weights": {
         "mlr_normal_fill": [c_void_p, c_int, c_longlong, c_ulonglong, c_double, c_int, c_void_p],
         "mlr_finite_check": [c_void_p, c_int, c_longlong, c_void_p, c_void_p],
@@ -90,6 +94,11 @@ def module(name: str):
             f.argtypes = argtypes
             f.restype = c_int
         lib.mlr_last_error.restype = ctypes.c_char_p
+        if name == "host":
+            lib.mlr_exec_fail_after.argtypes = [c_longlong]
+            lib.mlr_exec_fail_after.restype = None
+            lib.mlr_exec_launch_count.restype = c_longlong
+            lib.mlr_exec_reset_launch_count.restype = None
         _bound[name] = lib
     return lib
 
@@ -99,11 +108,42 @@ _fail_after = None
 
 
 def fail_after(launches) -> None:
-    """For failure tests that must not touch the GPU's health: after `launches` more calls
-    the next one raises `KernelError` INSTEAD of launching its kernel (None: never).  The
-    reference makes wrapped CUDA calls fail the same way (tests/cuda_runtime_tests.cpp:15-49)."""
+    """For failure tests that must not touch the GPU's health: after `launches` more launches
+    the next one fails INSTEAD of launching its kernel (None: never), whether Python makes the
+    launch (`call` raises `KernelError`) or the native executor walks a program (the step
+    returns its failure code).  The reference makes wrapped CUDA calls fail the same way
+    (tests/cuda_runtime_tests.cpp:15-49)."""
     global _fail_after
     _fail_after = launches
+    module("host").mlr_exec_fail_after(-1 if launches is None else int(launches))
+
+
+def total_launches() -> int:
+    """Launches of this package's kernel entry points since the last reset: those Python made and
+    those the native executor made, graph replays counted with the launches they stand for."""
+    return launch_count + int(module("host").mlr_exec_launch_count())
+
+
+def reset_launches() -> None:
+    global launch_count
+    launch_count = 0
+    module("host").mlr_exec_reset_launch_count()
+
+
+def entry_points(module_name: str, fn: str):
+    """Addresses of a kernel entry point and of its module's error text function, for ops of
+    a native program."""
+    lib = module(module_name)
+    as_address = lambda f: ctypes.cast(f, c_void_p).value
+    return as_address(getattr(lib, fn)), as_address(lib.mlr_last_error)
+
+
+def is_bf16_dtype(dtype) -> int:
+    if dtype is torch.bfloat16:
+        return 1
+    if dtype is torch.float32:
+        return 0
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {dtype}")
 
 
 def call(module_name: str, fn: str, *args) -> None:

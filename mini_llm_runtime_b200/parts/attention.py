@@ -21,6 +21,7 @@ import torch
 from ..config.registry import register_part
 from ..ops import functions as F
 from ..ops import attention as A
+from ..ops import native
 from ..weights.loader import WeightSpec
 from .base import CacheNeed, Mixer, RunContext, StepContext
 
@@ -67,21 +68,32 @@ class AttentionMixer(Mixer):
             if self.q_norm.dtype is not self.k_norm.dtype:
                 self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
 
-    def forward(self, x: torch.Tensor, step: StepContext, run: RunContext) -> torch.Tensor:
-        rt = step.rt
+    def emit(self, b, x, run: RunContext):
+        rt = b.rt
         D = self.head_dim
-        partials = rt.linear_partials(x, self.w_qkv, activation=True)
-        qkv = rt.empty(x.shape[0], self.w_qkv.shape[0]) if partials is not None else rt.linear(x, self.w_qkv, activation=True)
-        table = step.tables[run.group]
+        width = self.w_qkv.shape[0]
+        partials = rt.linear_partials(b, x, self.w_qkv, activation=True)
+        qkv = b.temp(x.rows, width, rt.dtype) if partials is not None else rt.linear(b, x, self.w_qkv, activation=True)
         rotation = self.position.rotation_table() if self.position is not None else None
-        F.qk_norm_rope_cache(qkv, self.heads, self.kv_heads, D, self.q_norm, self.k_norm,
-                             self.qk_norm_eps if self.qk_norm_eps is not None else 1.0, rotation,
-                             step.positions, step.segment_of_row, table, step.page_size, run.cache,
-                             run.write_cache, step.status, partials=partials)
-        out = rt.empty(x.shape[0], self.heads * D)
-        A.paged_attention(qkv, out, run.cache, table, step, self.heads, self.kv_heads, D,
-                          self.window or 0, self.scale, cache_group=run.group)
-        return rt.linear_delta(out, self.w_o, into=step.residual)
+        if run.write_cache and run.cache.dtype is not qkv.dtype:
+            raise native.KernelError(f"cache dtype {run.cache.dtype} differs from activation dtype {qkv.dtype}")
+        # In place on qkv: per-head RMS norm of q and k, rotation by the table row of each position, and
+        # the write of k and v into the run's cache (from the product's partial sums when it left those).
+        b.launch("elementwise", "mlr_qk_norm_rope_cache", qkv.ptr, qkv.is_bf16, qkv.ld,
+                 partials.ptr if partials is not None else None, partials.slices if partials is not None else 0,
+                 partials.slice_stride if partials is not None else 0, partials.ld if partials is not None else 0,
+                 x.rows, self.heads, self.kv_heads, D,
+                 self.q_norm.data_ptr() if self.q_norm is not None else None,
+                 self.k_norm.data_ptr() if self.k_norm is not None else None,
+                 native.is_bf16(self.q_norm) if self.q_norm is not None else 0,
+                 float(self.qk_norm_eps) if self.qk_norm_eps is not None else 1.0,
+                 rotation.data_ptr() if rotation is not None else None,
+                 rotation.shape[1] if rotation is not None else 0, rotation.shape[0] if rotation is not None else 0,
+                 b.meta("positions"), b.meta("segment_of_row"), b.table(run.group), b.table_stride(run.group), b.page_size,
+                 run.cache.data_ptr(), run.cache.shape[0], int(run.write_cache), b.status, b.stream)
+        out = b.temp(x.rows, self.heads * D, rt.dtype)
+        A.paged_attention(b, qkv, out, run.cache, run.group, self.heads, self.kv_heads, D, self.window or 0, self.scale)
+        return rt.linear_delta(b, out, self.w_o, into=b.residual)
 
 
 register_part("mixer", "attention", AttentionMixer)

@@ -13,6 +13,13 @@ it is in, which layer it is, or what the other layers are.
 
 `x` is [M, width] in the activation dtype; `h` is the float32 residual stream;
 `delta` is a float32 [M, width] contribution that has not been added to `h` yet.
+
+A part says what it does in one of two ways.  A part written with torch operations overrides
+`forward` (tensors in, tensors out); the model then runs its steps from Python.  A part made
+of this package's kernels overrides `emit(builder, ...)` instead (buffers of the builder in
+and out, see `engine/builder.py`): it lists its launches, and `forward` is the default that
+runs that list at once.  When every part of a model has an `emit`, the model compiles them
+into programs that the native executor walks without Python (`Part.compiles`).
 """
 from __future__ import annotations
 
@@ -114,6 +121,26 @@ class Part:
         """Takes its tensors (CPU or device, stored precision) and keeps device copies
         in the form its kernels want."""
 
+    def emit(self, b, *args):
+        """The part's launches, listed to a builder.  Parts written in torch do not have one."""
+        raise NotImplementedError
+
+    def compiles(self) -> bool:
+        """Whether the native executor may run this part from `emit`: its class brings an `emit`
+        and leaves `forward` as the default that runs `emit` at once."""
+        return _definer(type(self), "emit") not in _INTERFACES and _definer(type(self), "forward") in _INTERFACES
+
+
+def _definer(cls, name):
+    for k in cls.__mro__:
+        if name in k.__dict__:
+            return k
+    return None
+
+
+def _tensor_of(buf):
+    return None if buf is None else buf.tensor
+
 
 class Mixer(Part):
     category = "mixer"
@@ -125,14 +152,18 @@ class Mixer(Part):
         return None
 
     def forward(self, x: torch.Tensor, step: StepContext, run: RunContext) -> torch.Tensor:
-        raise NotImplementedError
+        from ..engine.builder import EagerBuilder
+        b = EagerBuilder(step, residual=step.residual)
+        return _tensor_of(self.emit(b, b.wrap(x), run))
 
 
 class FeedForward(Part):
     category = "feed_forward"
 
     def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
-        raise NotImplementedError
+        from ..engine.builder import EagerBuilder
+        b = EagerBuilder(step, residual=step.residual)
+        return _tensor_of(self.emit(b, b.wrap(x)))
 
 
 class Norm(Part):
@@ -142,8 +173,11 @@ class Norm(Part):
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Adds `delta` into `h` (if given), then returns norm(h) in the activation
         dtype.  With `rows` only those rows are normed and returned (h is then left
-        as it is)."""
-        raise NotImplementedError
+        as it is).  `emit(b, h, delta, wanted_only)` is the same on buffers; the wanted
+        rows are then the step's (`b.meta("want_rows")`, `b.want` of them)."""
+        from ..engine.builder import EagerBuilder
+        b = EagerBuilder(step, want_rows=rows)
+        return _tensor_of(self.emit(b, b.wrap(h), b.wrap(delta), rows is not None))
 
 
 class PositionEncoding(Part):
@@ -158,6 +192,10 @@ class PositionEncoding(Part):
     def add_to_embedding(self, h: torch.Tensor, step: StepContext) -> None:
         """Hook for encodings that act on the embedded tokens; default: nothing."""
 
+    def compiles(self) -> bool:
+        """An encoding that only supplies a rotation table launches nothing of its own."""
+        return _definer(type(self), "add_to_embedding") is PositionEncoding
+
 
 class Block(Part):
     category = "block"
@@ -169,5 +207,33 @@ class Block(Part):
     def forward(self, h: torch.Tensor, pending: Optional[torch.Tensor], step: StepContext,
                 run: RunContext) -> Optional[torch.Tensor]:
         """Runs the layer on the residual stream `h` with a not yet added contribution
-        `pending`; returns the contribution it leaves pending."""
+        `pending`; returns the contribution it leaves pending.  `emit(b, h, pending, run)`
+        arranges the parts' `emit`s the same way."""
         raise NotImplementedError
+
+    def compiles(self) -> bool:
+        return (_definer(type(self), "emit") not in _INTERFACES and self.mixer.compiles() and self.feed_forward.compiles()
+                and all(n.compiles() for n in self.norms.values()))
+
+
+class Embedding(Part):
+    category = "embedding"
+
+    def forward(self, step: StepContext) -> torch.Tensor:
+        """The float32 residual stream [M, width] of the step's tokens; `emit(b)` on buffers."""
+        from ..engine.builder import EagerBuilder
+        return _tensor_of(self.emit(EagerBuilder(step)))
+
+
+class Head(Part):
+    category = "lm_head"
+
+    def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
+        """float32 logits [rows of x, vocab]; `emit(b, x)` on buffers (the logits buffer is `b.logits`)."""
+        from ..engine.builder import EagerBuilder
+        b = EagerBuilder(step)
+        b.want = x.shape[0]
+        return _tensor_of(self.emit(b, b.wrap(x)))
+
+
+_INTERFACES = (Part, Mixer, FeedForward, Norm, PositionEncoding, Block, Embedding, Head)

@@ -21,5 +21,12 @@ class PreNormBlock(Block):
         x = self.norms["pre_feed_forward"].forward(h, mixed, step)
         return self.feed_forward.forward(x, step)
 
+    def emit(self, b, h, pending, run):
+        b.residual = h
+        x = self.norms["pre_mixer"].emit(b, h, pending)
+        mixed = self.mixer.emit(b, x, run)
+        x = self.norms["pre_feed_forward"].emit(b, h, mixed)
+        return self.feed_forward.emit(b, x)
+
 
 register_part("block", "pre_norm", PreNormBlock)

@@ -11,12 +11,11 @@ import torch
 from ..config.registry import register_part
 from ..ops import functions as F
 from ..weights.loader import WeightSpec
-from .base import Part, StepContext
+from ..ops import native
+from .base import Embedding, Head
 
 
-class TokenEmbedding(Part):
-    category = "embedding"
-
+class TokenEmbedding(Embedding):
     def __init__(self, spec):
         super().__init__(spec)
         self.vocab = int(spec.params["vocab_size"])
@@ -32,15 +31,15 @@ class TokenEmbedding(Part):
     def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
         self.table = rt.shared_matrix(self.spec.weights["weight"], tensors)
 
-    def forward(self, step: StepContext) -> torch.Tensor:
-        h = step.rt.empty(step.num_rows, self.width, dtype=torch.float32)
-        F.embed_gather(self.table, step.token_ids, h, step.status)
+    def emit(self, b):
+        """h[r, :] = table[ids[r], :] as float32; an id outside the table zeroes the row and sets a status bit."""
+        h = b.temp(b.rows, self.width, torch.float32)
+        b.launch("elementwise", "mlr_embed_gather", h.ptr, self.table.data_ptr(), native.is_bf16(self.table), b.meta("token_ids"),
+                 b.rows, self.width, self.vocab, b.status, b.stream)
         return h
 
 
-class LinearHead(Part):
-    category = "lm_head"
-
+class LinearHead(Head):
     def __init__(self, spec):
         super().__init__(spec)
         self.vocab = int(spec.params["vocab_size"])
@@ -56,8 +55,8 @@ class LinearHead(Part):
     def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
         self.weight = rt.shared_matrix(self.spec.weights["weight"], tensors)
 
-    def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
-        return step.rt.linear(x, self.weight, out_dtype=torch.float32)
+    def emit(self, b, x):
+        return b.rt.linear(b, x, self.weight, out_dtype=torch.float32, out=b.logits(self.vocab))
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)

@@ -45,10 +45,9 @@ class SwiGLU(FeedForward):
             padded[:, :self.inter] = self.w_down
             self.w_down = padded
 
-    def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
-        rt = step.rt
-        act = rt.gated_linear(x, self.w_gate_up)
-        return rt.linear_delta(act, self.w_down, into=step.residual)
+    def emit(self, b, x):
+        act = b.rt.gated_linear(b, x, self.w_gate_up)
+        return b.rt.linear_delta(b, act, self.w_down, into=b.residual)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

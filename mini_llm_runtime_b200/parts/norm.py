@@ -11,7 +11,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..config.registry import register_part
-from ..ops import functions as F
+from ..ops import native
 from ..weights.loader import WeightSpec
 from .base import Norm, StepContext
 
@@ -32,10 +32,17 @@ class RmsNorm(Norm):
     def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
         self.weight = rt.vector(tensors[self.spec.weights["weight"]])
 
-    def forward(self, h, delta, step: StepContext, rows=None):
-        count = h.shape[0] if rows is None else rows.shape[0]
-        out = step.rt.empty(count, self.width)
-        F.rmsnorm(h, self.weight, self.eps, out, delta=delta, rows=rows, write_back=rows is None)
+    def emit(self, b, h, delta, wanted_only: bool = False):
+        """out[r] = rmsnorm(h[row] + delta[row]) * weight, row = the r-th wanted row or r; unless only
+        the wanted rows are normed, the sum is stored back to h, which moves the residual stream on.
+        `delta` may be partial sums [S, M, width], which are added in order first."""
+        count = b.want if wanted_only else h.rows
+        out = b.temp(count, self.width, b.rt.dtype)
+        slices, stride = (delta.slices or 1, delta.slice_stride) if delta is not None else (1, 0)
+        b.launch("elementwise", "mlr_rmsnorm", h.ptr, delta.ptr if delta is not None else None, slices, stride,
+                 self.weight.data_ptr(), native.is_bf16(self.weight), out.ptr, out.is_bf16,
+                 b.meta("want_rows") if wanted_only else None, count, self.width, self.eps, int(not wanted_only), b.stream,
+                 need="want" if wanted_only else None)
         return out
 
 

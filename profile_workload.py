@@ -203,7 +203,8 @@ def attention_tables(page: int) -> int:
     in random order for decode; time per launch from CUDA events over 10 launches after 3."""
     import math
 
-    from mini_llm_runtime_b200.ops import attention as A
+    from mini_llm_runtime_b200.engine import executor
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
     from mini_llm_runtime_b200.ops import functions as F
     dev = "cuda:0"
 
@@ -243,7 +244,8 @@ def attention_tables(page: int) -> int:
         qkv = torch.randn(batch, (heads + 2 * kv_heads) * dim, device=dev).to(torch.bfloat16)
         out = torch.empty(batch, heads * dim, device=dev, dtype=torch.bfloat16)
         status = torch.zeros(1, dtype=torch.int32, device=dev)
-        chunk, splits = A.split_plan([context] * batch, batch * kv_heads)
+        planned = executor.plan_attention((heads // kv_heads, kv_heads, 0, 1, dim, 1), [(context - 1, 1)] * batch, 0, sms)
+        chunk, splits = planned["chunk"], planned["max_splits"]
         partial = torch.empty(max(1, F.attention_decode_scratch_floats(batch, kv_heads, dim, splits)), device=dev)
         counters = torch.zeros(batch * kv_heads, dtype=torch.int32, device=dev)
         ms = timed(lambda: F.attention_decode_bf16(qkv, out, cache, None, batch, info, table, page, heads, kv_heads, dim, 0,

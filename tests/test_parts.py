@@ -232,7 +232,7 @@ def test_a_toy_mixer_with_state_is_added_from_outside(tmp_path_factory):
     model.bind(tensors)
     model.allocate_cache(CacheConfig(page_size=4, num_pages=64, max_requests=3))
     assert model.runs[1].context.state.shape == (3, H) and model.runs[1].context.cache is None
-    assert not model._graphable                    # a stateful mixer is never replayed from a graph
+    assert model._native is None                   # a mixer with state: the model is stepped from Python, never from a graph
 
     def plain(tokens):
         """Layer 0 as the plain implementation has it, layer 1 with the toy mixer."""
@@ -331,7 +331,7 @@ def test_a_toy_feed_forward_with_routing_is_added_from_outside(tmp_path_factory)
     assert "model.layers.0.mlp.gate_proj.weight" in expected and "model.layers.1.self_attn.q_proj.weight" in expected
     model.bind({n: toy_w[n] if n in toy_w else weights[n] for n in expected})
     model.allocate_cache(CacheConfig(page_size=4, num_pages=64, max_requests=2))
-    assert not model._graphable
+    assert model._native is None
 
     def plain(tokens):
         T = len(tokens)
