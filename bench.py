@@ -21,6 +21,16 @@ A step is one decode step of the whole batch.
              live requests) / step time, against the HBM peak
   points     decode tokens/s at batch 1 and 64 (same context), and at batch 1/8/64
              with 2048 tokens of context
+  checked    before anything is timed, the timed configuration cut to two layers (same seed, so
+             the same tensors) runs its prompts and first decode steps in bfloat16 and in true
+             float32, and the logits and greedy ids of the two must agree (relative RMSE, largest
+             difference and cosine per row); if they do not, no number is printed (`--no-check`
+             skips this)
+  steady_state   the timed decode steps must not grow a buffer of the step executor nor make the
+             allocator ask the driver for memory; weights are never copied again and no logits
+             leave the device
+  reference_point   the engine at the configuration the reference arm runs (Qwen3-0.6B sizes,
+             batch 4, context 2048; bfloat16 here, float32 there), for a like-for-like ratio
 
 Peaks come from MEASURED_PEAKS.json beside this file when it exists, else from the
 fallback figures of an earlier measurement on the same pool (6.65 TB/s, 1.59 PFLOP/s).
@@ -180,6 +190,61 @@ def reference_arm(args) -> int:
     return 0
 
 
+# What bfloat16 may differ from float32 by at the layer sizes of real models, per row of logits and relative to
+# the size of the row (tests/test_real_sizes.py measures 0.012 / 0.060 / 0.99993 against float64).
+CHECK_BOUNDS = {"rmse": 0.025, "max": 0.12, "cosine": 0.99985}
+
+
+def check_configuration(cfg, seed, batch, context, page, steps=3):
+    """The timed configuration with two layers, in bfloat16 and in float32: prompts of `context - 1`
+    tokens in portions of 2048, then `steps` decode steps that both precisions take with the float32
+    path's greedy ids.  Returns a short report; raises if logits or ids disagree."""
+    import torch
+    from mini_llm_runtime_b200.engine.loading import random_model
+    from mini_llm_runtime_b200.engine.model import CacheConfig, StepEntry
+    cut = dict(cfg, num_hidden_layers=min(2, cfg["num_hidden_layers"]))
+    gen = torch.Generator().manual_seed(4321)
+    prompts = [torch.randint(0, cfg["vocab_size"], (context - 1,), generator=gen).tolist() for _ in range(batch)]
+    first = torch.randint(0, cfg["vocab_size"], (batch,), generator=gen).tolist()
+    pages = batch * ((context + steps + page) // page + 1)
+    rows = {}
+    for dtype in ("float32", "bfloat16"):
+        model = random_model(cut, seed=seed, dtype=dtype,
+                             cache=CacheConfig(page_size=page, num_pages=pages, max_requests=batch, max_model_len=context + steps + page))
+        slots = [model.open_request() for _ in range(batch)]
+        for slot, prompt in zip(slots, prompts):
+            for pos in range(0, len(prompt), 2048):
+                model.step([StepEntry(slot, prompt[pos:pos + 2048], [])])
+        tokens, out = list(first), []
+        for step in range(steps):
+            logits = model.step([StepEntry(s, [t], [0]) for s, t in zip(slots, tokens)]).clone()
+            out.append(logits)
+            tokens = (rows["float32"][step] if dtype == "bfloat16" else logits).argmax(-1).tolist()
+        model.check_status()
+        rows[dtype] = out
+        del model
+        torch.cuda.empty_cache()
+    worst = {"rmse": 0.0, "max": 0.0, "cosine": 1.0}
+    flips = 0
+    for want, got in zip(rows["float32"], rows["bfloat16"]):
+        want, got = want.double(), got.double()
+        size = want.pow(2).mean(-1).sqrt()
+        diff = got - want
+        worst["rmse"] = max(worst["rmse"], float((diff.pow(2).mean(-1).sqrt() / size).max()))
+        worst["max"] = max(worst["max"], float((diff.abs().amax(-1) / size).max()))
+        worst["cosine"] = min(worst["cosine"], float(((got * want).sum(-1) / (got.norm(dim=-1) * want.norm(dim=-1))).min()))
+        for r in range(want.shape[0]):
+            a, b = int(want[r].argmax()), int(got[r].argmax())
+            if a != b:
+                if float(want[r, a] - want[r, b]) > 2 * CHECK_BOUNDS["max"] * float(size[r]):
+                    raise RuntimeError(f"check: bfloat16 picks token {b} where float32 picks {a}, {float(want[r, a] - want[r, b]):.4f} apart")
+                flips += 1
+    if worst["rmse"] > CHECK_BOUNDS["rmse"] or worst["max"] > CHECK_BOUNDS["max"] or worst["cosine"] < CHECK_BOUNDS["cosine"]:
+        raise RuntimeError(f"check: bfloat16 and float32 logits disagree: {worst} against the bounds {CHECK_BOUNDS}")
+    return {"layers": cut["num_hidden_layers"], "decode_steps": steps, "rows": steps * batch, "relative_rmse": round(worst["rmse"], 5),
+            "relative_max": round(worst["max"], 5), "cosine": round(worst["cosine"], 7), "near_tie_flips": flips}
+
+
 def matmul_params(cfg, layers):
     H, D = cfg["hidden_size"], cfg["head_dim"]
     per_layer = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * D * H + cfg["num_attention_heads"] * D * H \
@@ -235,6 +300,7 @@ def main() -> int:
     ap.add_argument("--own-products", action="store_true",
                     help="every matrix product on the package's tcgen05 kernel, none on the vendor library (slower)")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (the baseline's configuration has 16; 64 is a little faster)")
+    ap.add_argument("--no-check", action="store_true", help="skip the agreement check of bfloat16 and float32 before the measurement")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -271,6 +337,14 @@ def main() -> int:
     max_batch = max(batches)
     pages = max_batch * ((context + horizon + page - 1) // page + 1)
     pk = peaks()
+
+    checked = None
+    if not args.no_check and not args.serving:
+        try:
+            checked = check_configuration(cfg, weights_seed, args.batch, context, page)
+        except RuntimeError as error:
+            print(f"bench.py: {error}; no number is reported", file=sys.stderr)
+            return 1
 
     torch.manual_seed(0)
     model = random_model(cfg, seed=weights_seed, dtype="bfloat16",
@@ -330,6 +404,8 @@ def main() -> int:
                 last = model.step([StepEntry(slot, part, [len(part) - 1] if final else [])])
         return slots
 
+    steady = {"executor_buffer_growths": 0, "driver_allocations": 0, "weight_h2d_bytes": 0, "logits_d2h_bytes": 0}
+
     def decode_rate(batch, ctx, steps, warmup, with_clocks=False):
         slots = fill(batch, ctx)
         ids = torch.randint(0, cfg["vocab_size"], (batch,), generator=gen).to(torch.int32).to(model.rt.device)
@@ -344,6 +420,7 @@ def main() -> int:
         for _ in range(warmup):
             one_step()
         native.reset_launches()
+        grown, asked = model.steady_state_allocations, torch.cuda.memory_stats().get("num_device_alloc", 0)
         if with_clocks:
             with ClockSampler() as clocks:
                 ms = timed(one_step, steps)
@@ -351,6 +428,9 @@ def main() -> int:
         else:
             ms, clock_summary = timed(one_step, steps), None
         launches = native.total_launches()
+        # The steady-state gates of the reference's protocol (benchmarks/runtime-inputs/qwen3-cuda-v0.json:137-144).
+        steady["executor_buffer_growths"] += model.steady_state_allocations - grown
+        steady["driver_allocations"] += torch.cuda.memory_stats().get("num_device_alloc", 0) - asked
         for s in slots:
             model.close_request(s)
         return batch / ms * 1e3, ms, launches, clock_summary
@@ -390,6 +470,37 @@ def main() -> int:
     e2e = {"value": args.batch / e2e_ms * 1e3, "unit": "tokens/s", "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": model.last_h2d_bytes, "d2h_bytes_per_step": 4 * (args.batch + 1)}
 
+    if steady["executor_buffer_growths"] or steady["driver_allocations"]:
+        print(f"bench.py: the timed decode steps allocated device memory ({steady}); no number is reported", file=sys.stderr)
+        return 1
+
+    # ---------------------------------------------------------------- the reference arm's configuration, on this engine
+    reference_point = None
+    if args.model == "qwen3-8b" and not args.quick and not args.no_points:
+        del engine, model
+        torch.cuda.empty_cache()
+        small = dict(QWEN3_06B)
+        model = random_model(small, seed=3, dtype="bfloat16",
+                             cache=CacheConfig(page_size=page, num_pages=REFERENCE_BATCH * (REFERENCE_CONTEXT // page + 8),
+                                               max_requests=REFERENCE_BATCH, max_model_len=REFERENCE_CONTEXT + 64, fill_nan=False))
+        sampler = Sampler(model.rt.device, model.status)
+        cfg_main, cfg = cfg, small
+        short = max(8, args.steps // 2)
+        b4 = decode_rate(REFERENCE_BATCH, REFERENCE_CONTEXT - short - args.warmup, short, args.warmup)[0]
+        b1 = decode_rate(1, REFERENCE_CONTEXT - short - args.warmup, short, args.warmup)[0]
+        portion = prompt_of(128)
+
+        def portion_once():
+            slot = model.open_request()
+            model.step([StepEntry(slot, portion, [127])])
+            model.close_request(slot)
+
+        for _ in range(3):
+            portion_once()
+        reference_point = {"model": "Qwen3-0.6B sizes", "batch": REFERENCE_BATCH, "context": REFERENCE_CONTEXT, "dtype": "bf16",
+                           "decode_tok_s": b4, "decode_b1_tok_s": b1, "prefill_128_tok_s": 128 / timed(portion_once, 5) * 1e3}
+        cfg = cfg_main
+
     name = {"qwen3-8b": "Qwen3-8B", "qwen3-0.6b": "Qwen3-0.6B", "qwen3-32b": "Qwen3-32B"}[args.model]
     config = {"model": f"{name} sizes, random weights (seed {weights_seed})" if not args.quick else "quick check model",
               "layers": layers, "layers_of_model": full_layers, "hidden": cfg["hidden_size"],
@@ -403,7 +514,8 @@ def main() -> int:
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
         "config": config, "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "prefill": prefill,
-        "roofline": roofline, "points": points}))
+        "roofline": roofline, "points": points, "checked": checked is not None, "check": checked, "steady_state": steady,
+        "reference_point": reference_point}))
     return 0
 
 
