@@ -71,6 +71,10 @@ class Buf:
     slices: int = 0
     slice_stride: int = 0
     tensor: Optional[torch.Tensor] = None
+    # A norm that has not been launched: `ptr` is None and this holds (stream Buf, weight tensor, eps,
+    # wanted rows only).  A product that can norm its own input takes it as it is; anyone else asks the
+    # runtime to `materialize` it first.
+    norm: Optional[tuple] = None
 
     @property
     def is_bf16(self) -> int:

@@ -34,6 +34,7 @@ from typing import Optional
 import torch
 
 from ..ops import functions as F
+from ..ops import native
 from . import executor
 from .builder import Buf
 
@@ -58,7 +59,7 @@ def _give_library_workspace(device: torch.device) -> None:
         _library_workspace[index] = space
 
 
-_ROUTING = {"use_tcgen05", "tcgen05_prefill", "pair_rows", "pair_everything", "tcgen05_attention", "decode_rows",
+_ROUTING = {"gemv_rows", "use_tcgen05", "tcgen05_prefill", "pair_rows", "pair_everything", "tcgen05_attention", "decode_rows",
             "own_activation_products", "pair_min_tiles"}
 
 
@@ -100,7 +101,13 @@ class Runtime:
         # gate/up) go to the vendor library unless this is set: its kernels write the bfloat16
         # result at once, and the decode step is 3-4 % faster that way at 1 to 8 rows.
         self.own_activation_products = False
+        # Up to this many rows a product is a pass over the weights on the CUDA cores (`gemv_bf16.cu`), with
+        # the norm before it, the gate or the residual add after it folded in: measured against the other
+        # routes it wins at one and two rows and loses from three on, where its multiply-adds and
+        # shared-memory reads per weight byte catch up with the memory system.
+        self.gemv_rows = 2
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.shared_memory_limit = torch.cuda.get_device_properties(self.device).shared_memory_per_block_optin
         if dtype is torch.bfloat16:
             _give_library_workspace(self.device)
         self.pair_min_tiles = self.sm_count   # ... and only with at least this many 256 x 256 tiles
@@ -236,6 +243,46 @@ class Runtime:
         b.launch("host", "mlr_library_gemm", x.ptr, x.ld, x.rows, w.data_ptr(), w.stride(0), w.shape[0], w.shape[1], out.ptr,
                  out.ld, int(out.dtype is torch.float32), int(accumulate), b.stream, need=b.need_for(x.rows))
 
+    # ---- few rows: a pass over the weights with the neighbouring row-wise work folded in
+    def _gemv_fits(self, K: int) -> bool:
+        return K % 8 == 0 and 4 * self.gemv_rows * K + 1024 <= self.shared_memory_limit
+
+    def norm_can_wait(self, b, count, width: int) -> bool:
+        """Whether a norm over `count` rows of `width` need not be launched because the product that
+        reads it will do it in its prologue."""
+        return self.dtype is torch.bfloat16 and self.gemv_rows > 0 and self._gemv_fits(width) and b.le(count, self.gemv_rows)
+
+    def _gemv(self, b, x: Buf, w: torch.Tensor) -> bool:
+        """Whether this bf16 product is a few-row pass over the weights."""
+        if self.dtype is not torch.bfloat16 or self.gemv_rows <= 0 or w.dtype is not torch.bfloat16 or not self._gemv_fits(w.shape[1]):
+            return False
+        if w.stride(1) != 1 or w.stride(0) % 8 or w.data_ptr() % 16 or x.width != w.shape[1]:
+            return False
+        if x.norm is None and (x.dtype is not torch.bfloat16 or x.ld % 8 or x.ptr % 16):
+            return False
+        return b.le(x.rows, self.gemv_rows)
+
+    def _gemv_launch(self, b, x: Buf, w: torch.Tensor, out: Buf, mode: str) -> None:
+        if x.norm is not None:
+            h, weight, eps, wanted_only = x.norm
+            source = (h.ptr, h.ld, 1, weight.data_ptr(), native.is_bf16(weight), float(eps), b.meta("want_rows") if wanted_only else None)
+        else:
+            source = (x.ptr, x.ld, 0, None, 0, 0.0, None)
+        b.launch("gemv_bf16", "mlr_gemv_bf16", w.data_ptr(), w.stride(0), w.shape[0], w.shape[1], *source, x.rows, out.ptr, out.ld,
+                 F.GEMV_MODES[mode], b.stream, need=b.need_for(x.rows))
+
+    def materialize(self, b, x: Buf) -> Buf:
+        """The result of a norm that waited for a product (`Buf.norm`), for a reader that cannot norm its own input."""
+        if x.norm is None:
+            return x
+        h, weight, eps, wanted_only = x.norm
+        out = b.temp(x.rows, x.width, x.dtype)
+        b.launch("elementwise", "mlr_rmsnorm", h.ptr, None, 1, 0, weight.data_ptr(), native.is_bf16(weight), out.ptr, out.is_bf16,
+                 b.meta("want_rows") if wanted_only else None, x.rows, x.width, float(eps), 0, b.stream,
+                 need="want" if wanted_only else None)
+        x.ptr, x.tensor, x.ld, x.norm = out.ptr, out.tensor, out.ld, None        # every later reader finds the result
+        return x
+
     def linear(self, b, x: Buf, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, activation: bool = False,
                out: Optional[Buf] = None) -> Buf:
         """x W^T.  `activation`: the result feeds a row-wise kernel as an activation (q/k/v,
@@ -244,6 +291,10 @@ class Runtime:
         N, K = w.shape
         if out is None:
             out = b.temp(x.rows, N, torch.float32 if self.dtype is torch.float32 else out_dtype)
+        if self._gemv(b, x, w):
+            self._gemv_launch(b, x, w, out, "bf16" if out.dtype is torch.bfloat16 else "f32")
+            return out
+        x = self.materialize(b, x)
         if self.dtype is torch.float32:
             b.launch("gemm_f32", "mlr_gemm_f32", x.ptr, w.data_ptr(), out.ptr, x.rows, N, K, x.ld, w.stride(0), out.ld, b.stream,
                      need=b.need_for(x.rows))
@@ -259,8 +310,9 @@ class Runtime:
         """For the few rows of a decode step: the product as float32 partial sums [S, M, N]
         over S ranges of K (so that a small weight matrix still occupies every SM); the
         kernel that reads them adds them up.  None when the product is not of that kind."""
-        if self.dtype is not torch.bfloat16 or (activation and not self.own_activation_products):
+        if self.dtype is not torch.bfloat16 or (activation and not self.own_activation_products) or self._gemv(b, x, w):
             return None
+        x = self.materialize(b, x)
         if not self._tcgen05_ok(x, w) or not b.le(x.rows, self.decode_rows):
             return None
         key = (w.shape[0], w.shape[1])
@@ -276,10 +328,15 @@ class Runtime:
         that the next norm adds up.  With `into` (the stream itself, float32 [M, N]) the
         product of a prompt portion adds its result there in its epilogue (into += x W^T,
         one rounding per element as the separate add had) and None is returned."""
+        direct = into is not None and self.dtype is torch.bfloat16 and into.dtype is torch.float32 and into.ld == into.width
+        if direct and self._gemv(b, x, w):
+            self._gemv_launch(b, x, w, into, "add_f32")
+            return None
         parts = self.linear_partials(b, x, w)
         if parts is not None:
             return parts
-        if into is not None and self.dtype is torch.bfloat16 and into.dtype is torch.float32 and into.ld == into.width:
+        x = self.materialize(b, x)
+        if direct:
             if self._pair(b, x, w):
                 self._pair_launch(b, x, w, into, "add_f32")
                 return None
@@ -306,6 +363,10 @@ class Runtime:
         inter = w_gate_up.shape[0] // 2
         block = F.GATE_BLOCK if self.dtype is torch.bfloat16 else inter
         out = b.temp(x.rows, inter, self.dtype)
+        if self._gemv(b, x, w_gate_up) and w_gate_up.shape[0] % (2 * F.GATE_BLOCK) == 0:
+            self._gemv_launch(b, x, w_gate_up, out, "silu_gate")
+            return out
+        x = self.materialize(b, x)
         if self.dtype is torch.bfloat16 and self._pair(b, x, w_gate_up, gated=True):
             self._pair_launch(b, x, w_gate_up, out, "silu_gate")
             return out

@@ -232,9 +232,36 @@ def finite_check(t: torch.Tensor, flag: torch.Tensor) -> None:
     call("weights", "mlr_finite_check", ptr(t), is_bf16(t), t.numel(), ptr(flag), stream())
 
 
+GEMV_MODES = {"bf16": 0, "f32": 1, "add_f32": 2, "silu_gate": 3}
+
+
+def gemv_bf16(w: torch.Tensor, x: torch.Tensor, out: torch.Tensor, mode: str = "bf16", norm_weight: Optional[torch.Tensor] = None,
+              eps: float = 0.0, rows: Optional[torch.Tensor] = None) -> None:
+    """out = f(x w^T) for one to four rows (a pass over the weights on the CUDA cores).  x is bfloat16 [M, K];
+    or, with `norm_weight`, the float32 residual stream, of which row r (row rows[r] when `rows` is given)
+    is RMS-normed first.  `mode`: "bf16" / "f32" store, "add_f32" adds into the float32 out, "silu_gate"
+    takes w as a stacked gate/up matrix (`interleave_gate_up`) and stores silu(gate) * up in out [M, N / 2]."""
+    on_gpu(w, x, out, norm_weight, rows)
+    M = out.shape[0]
+    N, K = w.shape
+    norm = norm_weight is not None
+    if w.dtype is not torch.bfloat16 or w.stride(1) != 1 or x.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemv_bf16: bfloat16 weights and unit inner strides are wanted")
+    if x.dtype is not (torch.float32 if norm else torch.bfloat16) or x.shape[1] != K:
+        raise KernelError("gemv_bf16: x must be bfloat16 [M, K], or the float32 stream when a norm weight is given")
+    columns = N // 2 if mode == "silu_gate" else N
+    want = torch.bfloat16 if mode in ("bf16", "silu_gate") else torch.float32
+    if out.shape[1] != columns or out.dtype is not want or (not norm and x.shape[0] != M):
+        raise KernelError(f"gemv_bf16: an output {tuple(out.shape)} of {out.dtype} does not fit mode {mode!r}")
+    if rows is not None:
+        expect(rows, torch.int32, "row indices")
+    call("gemv_bf16", "mlr_gemv_bf16", ptr(w), w.stride(0), N, K, ptr(x), x.stride(0), int(norm), ptr(norm_weight),
+         is_bf16(norm_weight) if norm else 0, float(eps), ptr(rows), M, ptr(out), out.stride(0), GEMV_MODES[mode], stream())
+
+
 def product_modules(dtype) -> list:
     """The kernel modules the matrix products of a precision may call."""
-    return ["gemm_f32"] if dtype is torch.float32 else ["gemm_bf16_tcgen05", "gemm_bf16_tcgen05_pair"]
+    return ["gemm_f32"] if dtype is torch.float32 else ["gemm_bf16_tcgen05", "gemm_bf16_tcgen05_pair", "gemv_bf16"]
 
 
 def gemm_tcgen05_applies(x: torch.Tensor, w: torch.Tensor) -> bool:

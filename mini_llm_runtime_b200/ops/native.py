@@ -69,6 +69,11 @@ _SIGNATURES = {
         "mlr_library_gemm": [c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_int, c_int,
                              c_void_p],
     },
+    "gemv_bf16": {
+        "mlr_gemv_bf16": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_int, c_float, c_void_p, c_int,
+                          c_void_p, c_longlong, c_int, c_void_p],
+        "mlr_gemv_bf16_fits": [c_int, c_int],
+    },
     "weights": {
         "mlr_normal_fill": [c_void_p, c_int, c_longlong, c_ulonglong, c_double, c_int, c_void_p],
         "mlr_finite_check": [c_void_p, c_int, c_longlong, c_void_p, c_void_p],

@@ -138,8 +138,12 @@ def _definer(cls, name):
     return None
 
 
-def _tensor_of(buf):
-    return None if buf is None else buf.tensor
+def _tensor_of(buf, b=None):
+    if buf is None:
+        return None
+    if buf.norm is not None:            # a norm that waited for a product to take it: a caller in Python wants the tensor
+        buf = b.rt.materialize(b, buf)
+    return buf.tensor
 
 
 class Mixer(Part):
@@ -177,7 +181,7 @@ class Norm(Part):
         rows are then the step's (`b.meta("want_rows")`, `b.want` of them)."""
         from ..engine.builder import EagerBuilder
         b = EagerBuilder(step, want_rows=rows)
-        return _tensor_of(self.emit(b, b.wrap(h), b.wrap(delta), rows is not None))
+        return _tensor_of(self.emit(b, b.wrap(h), b.wrap(delta), rows is not None), b)
 
 
 class PositionEncoding(Part):

@@ -11,6 +11,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..config.registry import register_part
+from ..engine.builder import Buf
 from ..ops import native
 from ..weights.loader import WeightSpec
 from .base import Norm, StepContext
@@ -37,6 +38,10 @@ class RmsNorm(Norm):
         the wanted rows are normed, the sum is stored back to h, which moves the residual stream on.
         `delta` may be partial sums [S, M, width], which are added in order first."""
         count = b.want if wanted_only else h.rows
+        if delta is None and b.rt.norm_can_wait(b, count, self.width):
+            # The product that reads this norm's result will norm its own input (a few-row product
+            # streams the weights once and has the rows in shared memory anyway): nothing to launch here.
+            return Buf(None, count, self.width, b.rt.dtype, self.width, norm=(h, self.weight, self.eps, wanted_only))
         out = b.temp(count, self.width, b.rt.dtype)
         slices, stride = (delta.slices or 1, delta.slice_stride) if delta is not None else (1, 0)
         b.launch("elementwise", "mlr_rmsnorm", h.ptr, delta.ptr if delta is not None else None, slices, stride,

@@ -191,6 +191,70 @@ def test_gemm_bf16_tcgen05(M, N, K, out_dtype):
             assert torch.allclose(parts.double().sum(0), want, atol=tol * (1 + want.abs().max().item()), rtol=tol)
 
 
+@pytest.mark.parametrize("M", [1, 2, 3, 4])
+@pytest.mark.parametrize("N,K", [(512, 264), (4096, 4096), (6144, 1024), (301, 96), (2, 8)])
+def test_gemv_bf16_and_what_it_folds_in(M, N, K):
+    """The few-row product on the CUDA cores: plain, added into the float32 stream, with the RMS norm of
+    the stream (all rows, or indexed rows) as its prologue; odd row counts and widths that are no power of two."""
+    x = (torch.randn(M, K, generator=gen(1)) * 0.7).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=gen(2)) * 0.05).to(torch.bfloat16)
+    want = x.double() @ w.double().T
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    F().gemv_bf16(w.to(DEV), x.to(DEV), out, "bf16")
+    assert torch.allclose(out.cpu().double(), want, atol=2e-2, rtol=2e-2)
+    out32 = torch.full((M, N), float("nan"), device=DEV)
+    F().gemv_bf16(w.to(DEV), x.to(DEV), out32, "f32")
+    assert torch.allclose(out32.cpu().double(), want, atol=1e-4, rtol=1e-4)
+    h = torch.randn(M, N, generator=gen(3))
+    stream = h.clone().to(DEV)
+    F().gemv_bf16(w.to(DEV), x.to(DEV), stream, "add_f32")
+    assert torch.allclose(stream.cpu().double(), h.double() + want, atol=1e-4, rtol=1e-4)
+    if K % 4 == 0:
+        # The norm of the stream as the prologue, against the norm kernel followed by the plain product.
+        rows_of_stream = 7
+        hs = torch.randn(rows_of_stream, K, generator=gen(4)) * 3
+        nw = (1 + 0.1 * torch.randn(K, generator=gen(5))).to(torch.bfloat16)
+        index = torch.tensor([5, 0, 6, 2][:M], dtype=torch.int32)
+        for rows in (None, index):
+            source = hs[:M] if rows is None else hs[rows.long()]
+            normed = P.rms_norm(source, nw.float(), 1e-5).to(torch.bfloat16)
+            want_n = normed.double() @ w.double().T
+            got = torch.full((M, N), float("nan"), device=DEV)
+            F().gemv_bf16(w.to(DEV), hs.to(DEV), got, "f32", norm_weight=nw.to(DEV), eps=1e-5,
+                          rows=rows.to(DEV) if rows is not None else None)
+            assert torch.allclose(got.cpu().double(), want_n, atol=3e-2, rtol=3e-2), (got.cpu().double() - want_n).abs().max()
+
+
+@pytest.mark.parametrize("M,inter,K", [(1, 256, 128), (4, 12288, 4096), (3, 300, 104)])
+def test_gemv_bf16_gate(M, inter, K):
+    """silu(gate) * up in the epilogue, over the stacked operand the feed-forward keeps (blocks of 128 gate
+    rows and their up rows, padded with zero rows)."""
+    x = torch.randn(M, K, generator=gen(1)).to(torch.bfloat16)
+    wg = (torch.randn(inter, K, generator=gen(2)) * 0.08).to(torch.bfloat16)
+    wu = (torch.randn(inter, K, generator=gen(3)) * 0.08).to(torch.bfloat16)
+    stacked = F().interleave_gate_up(wg.to(DEV), wu.to(DEV))
+    g, u = x.double() @ wg.double().T, x.double() @ wu.double().T
+    want = (g / (1 + torch.exp(-g))) * u
+    out = torch.full((M, stacked.shape[0] // 2), float("nan"), dtype=torch.bfloat16, device=DEV)
+    F().gemv_bf16(stacked, x.to(DEV), out, "silu_gate")
+    got = out.cpu().double()
+    assert torch.allclose(got[:, :inter], want, atol=2e-2, rtol=2e-2) and (got[:, inter:] == 0).all()
+
+
+def test_gemv_bf16_refuses_what_it_cannot_do():
+    x = torch.zeros(5, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(128, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(Exception, match="1 to 4 rows"):
+        F().gemv_bf16(w, x, torch.empty(5, 128, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(Exception, match="multiple of 8"):
+        F().gemv_bf16(w[:, :60].contiguous(), x[:1, :60].contiguous(), torch.empty(1, 128, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(Exception, match="multiple of 256"):
+        F().gemv_bf16(w, x[:1], torch.empty(1, 64, dtype=torch.bfloat16, device=DEV), "silu_gate")
+    big = torch.zeros(4, 65536, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(Exception, match="do not fit shared memory"):
+        F().gemv_bf16(torch.zeros(8, 65536, dtype=torch.bfloat16, device=DEV), big, torch.empty(4, 8, dtype=torch.bfloat16, device=DEV))
+
+
 def test_gemm_bf16_tcgen05_every_tile_width():
     x = (torch.randn(400, 512, generator=gen(0)) * 0.5).to(torch.bfloat16).to(DEV)
     w = (torch.randn(700, 512, generator=gen(1)) * 0.1).to(torch.bfloat16).to(DEV)
