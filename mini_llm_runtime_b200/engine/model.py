@@ -30,6 +30,7 @@ from ..parts.base import Block, CacheNeed, RunContext, Segment, StateNeed, StepC
 from ..weights.loader import WeightSpec, merge_specs
 from .executor import (NativeStepper, STEP_FAILED, STEP_NO_PAGES, STEP_OK, STEP_POISONED, STEP_REFUSED)
 from .runtime import Runtime
+from .structure import build_part, build_parts
 
 
 class StepError(ValueError):
@@ -72,26 +73,13 @@ class _RunPlan:
     state_need: Optional[StateNeed]
 
 
-def build_part(category: str, spec: PartSpec):
-    return part_class(category, spec.kind)(spec)
-
-
 class Model:
     def __init__(self, plan: ModelPlan, rt: Runtime):
         plan.validate()
         self.plan, self.rt = plan, rt
-        self.positions = {name: build_part("position", spec) for name, spec in plan.positions.items()}
-        self.embedding = build_part("embedding", plan.embedding)
-        self.final_norm = build_part("norm", plan.final_norm)
-        self.lm_head = build_part("lm_head", plan.lm_head)
-        self.blocks: List[Block] = []
-        for layer in plan.layers:
-            mixer = build_part("mixer", layer.mixer)
-            if getattr(mixer, "position_name", None) is not None:
-                mixer.position = self.positions[mixer.position_name]
-            ff = build_part("feed_forward", layer.feed_forward)
-            norms = {slot: build_part("norm", spec) for slot, spec in layer.norms.items()}
-            self.blocks.append(part_class("block", layer.block)(PartSpec(layer.block), mixer, ff, norms))
+        self.parts = build_parts(plan)
+        self.positions, self.embedding = self.parts.positions, self.parts.embedding
+        self.final_norm, self.lm_head, self.blocks = self.parts.final_norm, self.parts.lm_head, self.parts.blocks
         # Cache groups: runs whose mixers keep the same span of keys share page ids.
         self.group_windows: List[Optional[int]] = []
         self.runs: List[_RunPlan] = []
@@ -137,14 +125,7 @@ class Model:
 
     # ------------------------------------------------------------------ weights
     def _all_parts(self):
-        yield self.embedding
-        yield from self.positions.values()
-        for block in self.blocks:
-            yield block.mixer
-            yield block.feed_forward
-            yield from block.norms.values()
-        yield self.final_norm
-        yield self.lm_head
+        return iter(self.parts)
 
     def expected_weights(self) -> Dict[str, WeightSpec]:
         return merge_specs(spec for part in self._all_parts() for spec in part.weight_specs())

@@ -101,11 +101,12 @@ class Runtime:
         # gate/up) go to the vendor library unless this is set: its kernels write the bfloat16
         # result at once, and the decode step is 3-4 % faster that way at 1 to 8 rows.
         self.own_activation_products = False
-        # Up to this many rows a product is a pass over the weights on the CUDA cores (`gemv_bf16.cu`), with
-        # the norm before it, the gate or the residual add after it folded in: measured against the other
-        # routes it wins at one and two rows and loses from three on, where its multiply-adds and
-        # shared-memory reads per weight byte catch up with the memory system.
-        self.gemv_rows = 2
+        # Up to this many rows (at most 8) a product is one pass over the weights by `gemv_bf16.cu`, with the norm
+        # before it and the gate or the residual add after it folded in: a decode layer is then six launches
+        # instead of nine and the vendor library is off the decode path.  Off by default (0): in the decode step
+        # of the 8B sizes its four products take 92 us a layer at one row and 125 us at eight, against 89 us for the
+        # split-K tcgen05 products, the library's q/k/v and gate/up and the three row-wise kernels between them.
+        self.gemv_rows = 0
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.shared_memory_limit = torch.cuda.get_device_properties(self.device).shared_memory_per_block_optin
         if dtype is torch.bfloat16:
@@ -245,12 +246,13 @@ class Runtime:
 
     # ---- few rows: a pass over the weights with the neighbouring row-wise work folded in
     def _gemv_fits(self, K: int) -> bool:
-        return K % 8 == 0 and 4 * self.gemv_rows * K + 1024 <= self.shared_memory_limit
+        rows = min(self.gemv_rows, 8)
+        return K % 8 == 0 and 16384 + rows * (2 * K + 128) + 1024 <= self.shared_memory_limit
 
     def norm_can_wait(self, b, count, width: int) -> bool:
         """Whether a norm over `count` rows of `width` need not be launched because the product that
         reads it will do it in its prologue."""
-        return self.dtype is torch.bfloat16 and self.gemv_rows > 0 and self._gemv_fits(width) and b.le(count, self.gemv_rows)
+        return self.dtype is torch.bfloat16 and self.gemv_rows > 0 and self._gemv_fits(width) and b.le(count, min(self.gemv_rows, 8))
 
     def _gemv(self, b, x: Buf, w: torch.Tensor) -> bool:
         """Whether this bf16 product is a few-row pass over the weights."""
@@ -260,7 +262,7 @@ class Runtime:
             return False
         if x.norm is None and (x.dtype is not torch.bfloat16 or x.ld % 8 or x.ptr % 16):
             return False
-        return b.le(x.rows, self.gemv_rows)
+        return b.le(x.rows, min(self.gemv_rows, 8))
 
     def _gemv_launch(self, b, x: Buf, w: torch.Tensor, out: Buf, mode: str) -> None:
         if x.norm is not None:

@@ -5,6 +5,7 @@ always float32; activations are float32 or bfloat16.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Optional
 
 import torch
@@ -237,7 +238,7 @@ GEMV_MODES = {"bf16": 0, "f32": 1, "add_f32": 2, "silu_gate": 3}
 
 def gemv_bf16(w: torch.Tensor, x: torch.Tensor, out: torch.Tensor, mode: str = "bf16", norm_weight: Optional[torch.Tensor] = None,
               eps: float = 0.0, rows: Optional[torch.Tensor] = None) -> None:
-    """out = f(x w^T) for one to four rows (a pass over the weights on the CUDA cores).  x is bfloat16 [M, K];
+    """out = f(x w^T) for one to eight rows (a pass over the weights).  x is bfloat16 [M, K];
     or, with `norm_weight`, the float32 residual stream, of which row r (row rows[r] when `rows` is given)
     is RMS-normed first.  `mode`: "bf16" / "f32" store, "add_f32" adds into the float32 out, "silu_gate"
     takes w as a stacked gate/up matrix (`interleave_gate_up`) and stores silu(gate) * up in out [M, N / 2]."""
@@ -257,6 +258,32 @@ def gemv_bf16(w: torch.Tensor, x: torch.Tensor, out: torch.Tensor, mode: str = "
         expect(rows, torch.int32, "row indices")
     call("gemv_bf16", "mlr_gemv_bf16", ptr(w), w.stride(0), N, K, ptr(x), x.stride(0), int(norm), ptr(norm_weight),
          is_bf16(norm_weight) if norm else 0, float(eps), ptr(rows), M, ptr(out), out.stride(0), GEMV_MODES[mode], stream())
+
+
+class GemvLink(ctypes.Structure):
+    """One link of `mlr_gemv_chain` as the kernel module declares it (MlrGemvLink)."""
+    _fields_ = [("W", ctypes.c_void_p), ("ldw", ctypes.c_longlong), ("N", ctypes.c_int), ("K", ctypes.c_int), ("x", ctypes.c_void_p),
+                ("ldx", ctypes.c_longlong), ("norm", ctypes.c_int), ("norm_weight_bf16", ctypes.c_int), ("norm_weight", ctypes.c_void_p),
+                ("row_index", ctypes.c_void_p), ("eps", ctypes.c_float), ("mode", ctypes.c_int), ("out", ctypes.c_void_p),
+                ("ldo", ctypes.c_longlong)]
+
+
+def gemv_chain(links, M: int, counter: torch.Tensor, status: torch.Tensor) -> None:
+    """Several few-row products in one launch, each as `gemv_bf16` takes it (dicts with w, x, out, mode and, for
+    a norm prologue, norm_weight and eps), each reading what earlier ones wrote.  `counter`: one zeroed int32 on
+    the device that the kernel leaves zero."""
+    array = (GemvLink * len(links))()
+    for link, spec in zip(array, links):
+        w, x, out = spec["w"], spec["x"], spec["out"]
+        on_gpu(w, x, out, spec.get("norm_weight"))
+        nw = spec.get("norm_weight")
+        link.W, link.ldw, link.N, link.K = ptr(w), w.stride(0), w.shape[0], w.shape[1]
+        link.x, link.ldx, link.norm = ptr(x), x.stride(0), int(nw is not None)
+        link.norm_weight, link.norm_weight_bf16 = ptr(nw), (is_bf16(nw) if nw is not None else 0)
+        link.row_index, link.eps, link.mode = None, float(spec.get("eps", 0.0)), GEMV_MODES[spec["mode"]]
+        link.out, link.ldo = ptr(out), out.stride(0)
+    expect(counter, torch.int32, "the meeting counter")
+    call("gemv_bf16", "mlr_gemv_chain", array, len(links), M, ptr(counter), ptr(status), stream())
 
 
 def product_modules(dtype) -> list:

@@ -18,12 +18,16 @@ from typing import Dict, List, Optional
 
 import torch
 
+from ..config.base import ConfigError
 from ..config.registry import register_part
 from ..ops import functions as F
 from ..ops import attention as A
 from ..ops import native
 from ..weights.loader import WeightSpec
 from .base import CacheNeed, Mixer, RunContext, StepContext
+
+
+MAX_HEAD_DIM = 256        # the generic kernel keeps two values of a head per thread of its 128
 
 
 class AttentionMixer(Mixer):
@@ -40,6 +44,9 @@ class AttentionMixer(Mixer):
         self.position_name = p.get("position")
         if self.heads % self.kv_heads:
             raise ValueError(f"{self.heads} query heads cannot share {self.kv_heads} kv heads")
+        # What no attention kernel of the package takes is refused here, when the plan is built, not at the first step.
+        if not 1 <= self.head_dim <= MAX_HEAD_DIM:
+            raise ConfigError(f"head size {self.head_dim} is outside what the attention kernels take (1 to {MAX_HEAD_DIM})")
         self.position = None       # set by the model from the plan's position encodings
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
 

@@ -55,6 +55,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--gemv-rows", type=int, default=-1,
+                    help="up to how many rows a product takes the CUDA-core pass over the weights (default: the runtime's setting)")
     ap.add_argument("--mma-sync-attention", action="store_true",
                     help="prompt attention on the mma.sync kernel instead of the tcgen05 one")
     args = ap.parse_args()
@@ -76,6 +78,8 @@ def main() -> int:
                                                          max_requests=batch, max_model_len=length + 64, fill_nan=False))
     model.use_graphs = not args.no_graphs
     model.rt.tcgen05_attention = not args.mma_sync_attention
+    if args.gemv_rows >= 0:
+        model.rt.gemv_rows = args.gemv_rows
     g = torch.Generator().manual_seed(0)
     tokens = lambda n: torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

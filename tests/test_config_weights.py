@@ -336,3 +336,12 @@ def test_non_finite_weights_are_refused_by_name(tmp_path, dtype):
     with pytest.raises(NonFiniteWeights) as info:
         load_model(_folder(tmp_path / "bad", raw, weights), dtype)
     assert "(2): model.layers.1.mlp.down_proj.weight, model.layers.2.self_attn.k_norm.weight" in str(info.value)
+
+
+def test_a_head_size_no_kernel_takes_is_refused_when_the_model_is_planned():
+    """The configuration accepts sizes up to a million (src/minillm/qwen3_model.cpp:13-19); the attention kernels of
+    this engine end at 256 per head, and say so before any weight is read."""
+    from mini_llm_runtime_b200.engine.structure import expected_weights as expected
+    raw = dict(tiny_models.get("tiny_a"), head_dim=272)
+    with pytest.raises(ConfigError, match="head size 272"):
+        expected(plan_for(config_from_dict(raw)))

@@ -109,3 +109,22 @@ def test_every_product_on_the_own_kernel(tmp_path_factory):
     model.check_status()
     for i in range(12):
         assert_close(logits[i:i + 1], want[20 + i:21 + i], "bfloat16", f"own products, request {i} of a batch of 12")
+
+
+def test_few_row_products_as_one_pass_over_the_weights(tmp_path_factory):
+    """The route that is off by default (`Runtime.gemv_rows`): decode steps of up to eight rows on the kernel that
+    norms its own input, gates and adds into the stream; one request token by token, and eight requests together."""
+    from mini_llm_runtime_b200.engine.model import StepEntry
+    folder, config, weights = tiny_folder(tmp_path_factory, "tiny_d", seed=41)
+    tokens = random_tokens(config, 120, 6)
+    want = plain_qwen3.forward(config, weights, tokens)
+    model = engine_model(folder, "bfloat16", num_pages=96, max_requests=8)
+    model.rt.gemv_rows = 8
+    assert_close(run_portions(model, tokens, [60, 1]), want, "bfloat16", "one pass over the weights, token by token")
+    slots = [model.open_request() for _ in range(8)]
+    model.step([StepEntry(s, tokens[:30 + i], []) for i, s in enumerate(slots)])
+    for step in range(4):
+        logits = model.step([StepEntry(s, [tokens[30 + i + step]], [0]) for i, s in enumerate(slots)]).float().cpu()
+        for i in range(8):
+            assert_close(logits[i:i + 1], want[30 + i + step:31 + i + step], "bfloat16", f"request {i} of eight, step {step}")
+    model.check_status()

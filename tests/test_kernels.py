@@ -191,8 +191,8 @@ def test_gemm_bf16_tcgen05(M, N, K, out_dtype):
             assert torch.allclose(parts.double().sum(0), want, atol=tol * (1 + want.abs().max().item()), rtol=tol)
 
 
-@pytest.mark.parametrize("M", [1, 2, 3, 4])
-@pytest.mark.parametrize("N,K", [(512, 264), (4096, 4096), (6144, 1024), (301, 96), (2, 8)])
+@pytest.mark.parametrize("M", [1, 2, 3, 5, 8])
+@pytest.mark.parametrize("N,K", [(512, 264), (4096, 4096), (6144, 1024), (301, 96), (2, 8), (100, 12288)])
 def test_gemv_bf16_and_what_it_folds_in(M, N, K):
     """The few-row product on the CUDA cores: plain, added into the float32 stream, with the RMS norm of
     the stream (all rows, or indexed rows) as its prologue; odd row counts and widths that are no power of two."""
@@ -209,12 +209,12 @@ def test_gemv_bf16_and_what_it_folds_in(M, N, K):
     stream = h.clone().to(DEV)
     F().gemv_bf16(w.to(DEV), x.to(DEV), stream, "add_f32")
     assert torch.allclose(stream.cpu().double(), h.double() + want, atol=1e-4, rtol=1e-4)
-    if K % 4 == 0:
+    if K % 4 == 0 and M * K <= 8 * 4096:
         # The norm of the stream as the prologue, against the norm kernel followed by the plain product.
-        rows_of_stream = 7
+        rows_of_stream = 9
         hs = torch.randn(rows_of_stream, K, generator=gen(4)) * 3
         nw = (1 + 0.1 * torch.randn(K, generator=gen(5))).to(torch.bfloat16)
-        index = torch.tensor([5, 0, 6, 2][:M], dtype=torch.int32)
+        index = torch.tensor([5, 0, 6, 2, 2, 1, 3, 4][:M], dtype=torch.int32)
         for rows in (None, index):
             source = hs[:M] if rows is None else hs[rows.long()]
             normed = P.rms_norm(source, nw.float(), 1e-5).to(torch.bfloat16)
@@ -225,7 +225,7 @@ def test_gemv_bf16_and_what_it_folds_in(M, N, K):
             assert torch.allclose(got.cpu().double(), want_n, atol=3e-2, rtol=3e-2), (got.cpu().double() - want_n).abs().max()
 
 
-@pytest.mark.parametrize("M,inter,K", [(1, 256, 128), (4, 12288, 4096), (3, 300, 104)])
+@pytest.mark.parametrize("M,inter,K", [(1, 256, 128), (4, 12288, 4096), (3, 300, 104), (8, 1000, 512)])
 def test_gemv_bf16_gate(M, inter, K):
     """silu(gate) * up in the epilogue, over the stacked operand the feed-forward keeps (blocks of 128 gate
     rows and their up rows, padded with zero rows)."""
@@ -242,17 +242,71 @@ def test_gemv_bf16_gate(M, inter, K):
 
 
 def test_gemv_bf16_refuses_what_it_cannot_do():
-    x = torch.zeros(5, 64, dtype=torch.bfloat16, device=DEV)
+    x = torch.zeros(9, 64, dtype=torch.bfloat16, device=DEV)
     w = torch.zeros(128, 64, dtype=torch.bfloat16, device=DEV)
-    with pytest.raises(Exception, match="1 to 4 rows"):
-        F().gemv_bf16(w, x, torch.empty(5, 128, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(Exception, match="1 to 8 rows"):
+        F().gemv_bf16(w, x, torch.empty(9, 128, dtype=torch.bfloat16, device=DEV))
     with pytest.raises(Exception, match="multiple of 8"):
         F().gemv_bf16(w[:, :60].contiguous(), x[:1, :60].contiguous(), torch.empty(1, 128, dtype=torch.bfloat16, device=DEV))
     with pytest.raises(Exception, match="multiple of 256"):
         F().gemv_bf16(w, x[:1], torch.empty(1, 64, dtype=torch.bfloat16, device=DEV), "silu_gate")
-    big = torch.zeros(4, 65536, dtype=torch.bfloat16, device=DEV)
+    big = torch.zeros(8, 65536, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(Exception, match="do not fit shared memory"):
-        F().gemv_bf16(torch.zeros(8, 65536, dtype=torch.bfloat16, device=DEV), big, torch.empty(4, 8, dtype=torch.bfloat16, device=DEV))
+        F().gemv_bf16(torch.zeros(8, 65536, dtype=torch.bfloat16, device=DEV), big, torch.empty(8, 8, dtype=torch.bfloat16, device=DEV))
+
+
+def test_gemv_chain_is_the_links_one_after_the_other():
+    """Four products of a layer's shape in one launch (each link reads what earlier links wrote; the blocks meet
+    between links) against the same four as launches of their own: the same bits, twice in a row (the meeting
+    counter is left at zero), for several row counts."""
+    H, I, QKV = 256, 768, 384
+    for M in (1, 3, 8):
+        g = lambda seed, *shape: (torch.randn(*shape, generator=gen(seed)) * 0.05).to(torch.bfloat16).to(DEV)
+        w_o, w_down, w_qkv = g(1, H, H), g(2, H, I), g(3, QKV, H)
+        w_gate_up = F().interleave_gate_up(g(4, I, H), g(5, I, H))
+        attn = g(6, M, H)
+        norm1 = (1 + 0.1 * torch.randn(H, generator=gen(7))).to(torch.bfloat16).to(DEV)
+        norm2 = (1 + 0.1 * torch.randn(H, generator=gen(8))).to(torch.bfloat16).to(DEV)
+        stream0 = torch.randn(M, H, generator=gen(9)).to(DEV)
+
+        def separate():
+            h = stream0.clone()
+            act = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+            qkv = torch.empty(M, QKV, dtype=torch.bfloat16, device=DEV)
+            F().gemv_bf16(w_o, attn, h, "add_f32")
+            F().gemv_bf16(w_gate_up, h, act, "silu_gate", norm_weight=norm1, eps=1e-6)
+            F().gemv_bf16(w_down, act, h, "add_f32")
+            F().gemv_bf16(w_qkv, h, qkv, "bf16", norm_weight=norm2, eps=1e-6)
+            return h, act, qkv
+
+        def chained(counter):
+            h = stream0.clone()
+            act = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+            qkv = torch.full((M, QKV), float("nan"), dtype=torch.bfloat16, device=DEV)
+            F().gemv_chain([dict(w=w_o, x=attn, out=h, mode="add_f32"),
+                            dict(w=w_gate_up, x=h, out=act, mode="silu_gate", norm_weight=norm1, eps=1e-6),
+                            dict(w=w_down, x=act, out=h, mode="add_f32"),
+                            dict(w=w_qkv, x=h, out=qkv, mode="bf16", norm_weight=norm2, eps=1e-6)], M, counter, status())
+            return h, act, qkv
+
+        want = separate()
+        counter = torch.zeros(1, dtype=torch.int32, device=DEV)
+        for _ in range(2):
+            got = chained(counter)
+            assert int(counter.item()) == 0
+            for a, b in zip(want, got):
+                assert torch.equal(a, b)
+        # ... and the separate launches are right: the stream after o_proj, the gate, down.
+        attn_, h0 = attn.cpu().double(), stream0.cpu().double()
+        h1 = h0 + attn_ @ w_o.cpu().double().T
+        n1 = P.rms_norm(h1.float(), norm1.cpu().float(), 1e-6).to(torch.bfloat16).double()
+        both = n1 @ w_gate_up.cpu().double().T
+        both = both.view(M, -1, 2, 128)
+        gate, up = both[:, :, 0].reshape(M, -1), both[:, :, 1].reshape(M, -1)
+        act = ((gate / (1 + torch.exp(-gate))) * up).to(torch.bfloat16)
+        assert torch.allclose(want[1].cpu().double(), act.double(), atol=3e-2, rtol=3e-2)
+        h2 = h1 + act.double() @ w_down.cpu().double().T
+        assert torch.allclose(want[0].cpu().double(), h2, atol=3e-2, rtol=3e-2)
 
 
 def test_gemm_bf16_tcgen05_every_tile_width():
