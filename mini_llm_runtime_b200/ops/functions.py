@@ -288,7 +288,7 @@ def gemv_chain(links, M: int, counter: torch.Tensor, status: torch.Tensor) -> No
 
 def product_modules(dtype) -> list:
     """The kernel modules the matrix products of a precision may call."""
-    return ["gemm_f32"] if dtype is torch.float32 else ["gemm_bf16_tcgen05", "gemm_bf16_tcgen05_pair", "gemv_bf16"]
+    return ["gemm_f32"] if dtype is torch.float32 else ["gemm_bf16_tcgen05", "gemm_bf16_tcgen05_pair"]
 
 
 def gemm_tcgen05_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
