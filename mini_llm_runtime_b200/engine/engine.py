@@ -59,8 +59,11 @@ class Engine:
         self.steps_ahead = 0      # how many of them were launched before the step before was read back
         self.batch_log: List[Dict[str, int]] = []   # per step: prefill and decode tokens (a step trace)
         self._in_flight: Optional[_InFlight] = None
-        # Two pinned buffers for the ids coming back: one being read while the next is filled.
+        # Two pinned buffers for the ids coming back (one being read while the next is filled), and two device
+        # buffers for the ids and the status word of a step (the ids of the step in flight feed the step launched
+        # ahead of it, whose own ids go to the other buffer).
         self._readback = [torch.empty(model.cache.max_requests + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._sampled = [torch.empty(model.cache.max_requests + 1, dtype=torch.int32, device=model.rt.device) for _ in range(2)]
         self._readback_turn = 0
 
     def submit(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
@@ -87,10 +90,13 @@ class Engine:
             raise RuntimeError(f"the step function returned {got} for {len(sampled_for)} wanted rows")
         temps = [r.params.temperature for r in sampled_for]
         uniforms = [uniform_for(r.params.seed, r.request_id, len(r.generated) + ahead) for r in sampled_for]
-        ids = self.sampler.sample(logits, temps, uniforms)
-        host = self._readback[self._readback_turn][:len(sampled_for) + 1]
+        n = len(sampled_for)
+        packed = self._sampled[self._readback_turn]
+        ids = self.sampler.sample(logits, temps, uniforms, out=packed[:n])
+        packed[n:n + 1].copy_(self.model.status)
+        host = self._readback[self._readback_turn][:n + 1]
         self._readback_turn ^= 1
-        host.copy_(torch.cat([ids, self.model.status]), non_blocking=True)     # one copy: the tokens and the status word
+        host.copy_(packed[:n + 1], non_blocking=True)     # one copy: the tokens and the status word
         ready = torch.cuda.Event()
         ready.record()
         return _InFlight(sampled_for, ids, host, ready, all_decode)

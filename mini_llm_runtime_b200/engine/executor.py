@@ -133,6 +133,9 @@ class NativeStepper:
         vocab = self.model.plan.vocab_size
         changed = False
         if self.device_meta is None or info.need_meta_ints > self.device_meta.numel():
+            # The executor copies from the pinned buffers itself, so the allocator does not know when a copy
+            # out of an old buffer has finished: wait for the stream before the old buffers are let go.
+            torch.cuda.current_stream(device).synchronize()
             size = max(1 << 16, 2 * info.need_meta_ints)
             self.device_meta = torch.empty(size, dtype=torch.int32, device=device)
             self.pinned = [torch.empty(size, dtype=torch.int32).pin_memory() for _ in range(_PINNED)]

@@ -48,21 +48,45 @@ class SamplingParams:
 
 
 class Sampler:
-    """Samples one token per logits row on the device."""
+    """Samples one token per logits row on the device.  Temperatures and uniform numbers go to the device
+    from two small pinned buffers (a ring of four, so a buffer is not written again while its copy may still
+    be in flight), never from pageable memory."""
+    _RING = 4
 
-    def __init__(self, device, status: torch.Tensor):
+    def __init__(self, device, status: torch.Tensor, max_rows: int = 256):
         self.device = device
         self.status = status
+        self._rows = 0
+        self._turn = 0
+        self._reserve(max_rows)
+
+    def _reserve(self, rows: int) -> None:
+        self._rows = rows
+        self._host_t = [torch.empty(rows, dtype=torch.float32).pin_memory() for _ in range(self._RING)]
+        self._host_u = [torch.empty(rows, dtype=torch.float64).pin_memory() for _ in range(self._RING)]
+        self._done = [torch.cuda.Event() for _ in range(self._RING)]
+        self._dev_t = torch.empty(rows, dtype=torch.float32, device=self.device)
+        self._dev_u = torch.empty(rows, dtype=torch.float64, device=self.device)
 
     def sample(self, logits: torch.Tensor, temperatures: Optional[Sequence[float]] = None,
-               uniforms: Optional[Sequence[float]] = None) -> torch.Tensor:
-        """int32 [rows] on the device; a row of non-finite logits gives -1."""
+               uniforms: Optional[Sequence[float]] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """int32 [rows] on the device (written to `out` when given); a row of non-finite logits gives -1."""
         rows = logits.shape[0]
-        out = torch.empty(rows, dtype=torch.int32, device=self.device)
+        if out is None:
+            out = torch.empty(rows, dtype=torch.int32, device=self.device)
         if temperatures is None or not any(t > 0 for t in temperatures):
             F.sample(logits, out, self.status)
             return out
-        t = torch.tensor(list(temperatures), dtype=torch.float32).to(self.device, non_blocking=True)
-        u = torch.tensor(list(uniforms), dtype=torch.float64).to(self.device, non_blocking=True)
-        F.sample(logits, out, self.status, t, u)
+        if rows > self._rows:
+            torch.cuda.current_stream(self.device).synchronize()
+            self._reserve(2 * rows)
+        turn = self._turn
+        self._turn = (turn + 1) % self._RING
+        self._done[turn].synchronize()
+        self._host_t[turn][:rows] = torch.tensor(list(temperatures), dtype=torch.float32)
+        self._host_u[turn][:rows] = torch.tensor(list(uniforms), dtype=torch.float64)
+        self._dev_t[:rows].copy_(self._host_t[turn][:rows], non_blocking=True)
+        self._dev_u[:rows].copy_(self._host_u[turn][:rows], non_blocking=True)
+        self._done[turn].record()
+        F.sample(logits, out, self.status, self._dev_t[:rows], self._dev_u[:rows])
         return out

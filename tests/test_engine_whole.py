@@ -128,3 +128,26 @@ def test_few_row_products_as_one_pass_over_the_weights(tmp_path_factory):
         for i in range(8):
             assert_close(logits[i:i + 1], want[30 + i + step:31 + i + step], "bfloat16", f"request {i} of eight, step {step}")
     model.check_status()
+
+
+def test_thirty_two_query_heads_per_kv_head_decode_from_graphs(tmp_path_factory):
+    """More than 16 query heads per kv head: single tokens then take the flash kernel with a tile list instead
+    of the split-KV kernel.  The list travels in the step's metadata, so such steps are captured and replayed
+    like any other decode step."""
+    import tiny_models
+    from helpers import write_model_folder
+    from mini_llm_runtime_b200.engine.model import StepEntry
+    config = dict(tiny_models.get("tiny_a"), num_attention_heads=32, num_key_value_heads=1, head_dim=16, hidden_size=64)
+    weights = plain_qwen3.random_weights(config, 17)
+    folder = str(tmp_path_factory.mktemp("group32"))
+    write_model_folder(folder, config, weights)
+    tokens = random_tokens(config, 60, 3)
+    want = plain_qwen3.forward(config, weights, tokens)
+    for dtype in ("bfloat16", "float32"):
+        model = engine_model(folder, dtype, num_pages=16)
+        slot = model.open_request()
+        rows = [model.step([StepEntry(slot, tokens[:20], list(range(20)))]).float().cpu()]
+        rows += [model.step([StepEntry(slot, [t], [0])]).float().cpu() for t in tokens[20:]]
+        model.check_status()
+        assert model._graphs
+        assert_close(torch.cat(rows), want, dtype, f"32 query heads per kv head, {dtype}")
