@@ -1,35 +1,47 @@
-// Products of a decode step's few rows (one to eight): out[M, N] = f(x[M, K] W[N, K]^T), alone or
-// several in a CHAIN that one persistent grid runs without a launch boundary in between.
+// Products of a decode step's few rows (one to eight): out[M, N] = f(x[M, K] W[N, K]^T).
 //
-// With so few rows a product is a pass over the weight matrix and nothing else, so the kernel is
-// built around the memory system.  A group of four warps takes 16 rows of W at a time and cuts K among
-// its warps; every lane reads 16 contiguous bytes of two weight rows per load, straight from global
-// memory into the registers that are the A operand of `mma.sync.m16n8k16` (the order of the k
-// values inside an instruction is permuted the same way for W and for x, which a sum does not
-// notice), several loads in flight per lane, no staging of weights in shared memory.  The B operand
-// is the step's activations, which the block keeps in shared memory as bfloat16 (at most 8 rows;
-// rows beyond M are zero registers).  The tensor cores do the multiply-adds of all rows at once, so
-// eight rows cost what one costs; the sums over the warps' K ranges are added in shared memory
-// in a fixed order, so a result depends neither on the grid nor on timing.  (`mma.sync` is the
-// older tensor-core instruction; `tcgen05.mma` wants both operands in shared memory, which is
-// exactly the copy this kernel avoids.  The products of prompt portions use tcgen05.)
+// With so few rows a product is a pass over the weight matrix and nothing else, so the kernel is built
+// around the memory system.  One warp of each block does nothing but fetch: it keeps a ring of two slots
+// of shared memory filled with the weights of 16 rows of W (a "unit") over a chunk of K, a bulk copy
+// (`cp.async.bulk`, completion counted by an mbarrier) of up to 4 KB per row.  A bulk copy costs the copy
+// engine about 50 ns whatever its size, so the rows are copied in pieces as long as shared memory allows;
+// and because the copies land in shared memory, what is in flight does not depend on how much L1 the
+// activations leave (loads into registers did: with eight rows of activations in shared memory they fell
+// to half the bandwidth).  Weights have no writer, so the fetching warp starts before the kernel before
+// this one has finished (programmatic dependent launch) and memory streams while the others still wait.
+// The 16 other warps multiply: warp w takes values 32 w .. 32 w + 31 of every 512 of a chunk, a lane reads
+// 16 bytes of two weight rows and of its token's activations from shared memory, and these are the
+// operands of two `mma.sync.m16n8k16` (the order of the k values inside an instruction is permuted the
+// same way for W and for x, which a sum does not notice).  The tensor cores do the multiply-adds of all
+// rows at once, so eight rows cost what one costs; the 16 warps' sums are added in shared memory in a fixed
+// order, so a result depends neither on the grid nor on timing.  (`mma.sync` is the older tensor-core
+// instruction; `tcgen05.mma` pays off when both operands are tiles of 64 rows and more, as in the products
+// of prompt portions, which use it.)
 //
 // Folded in, so that they are no launches of their own:
-//  * prologue: the RMS norm of the rows of the float32 residual stream that feed the product
-//    (`(h * 1/sqrt(mean(h^2) + eps)) * w`, rounded to bfloat16 as the norm kernel rounds it), on
-//    all rows or on the rows an index names (the final norm before the output head);
-//  * epilogue: store as bfloat16 or float32, ADD into the float32 residual stream (each element
-//    has one owner, so the add is a plain read-modify-write), or the SiLU gate of a stacked
-//    gate/up matrix (blocks of 128 gate rows followed by their 128 "up" rows): a block's 16 rows
-//    are then 8 gate rows and their 8 up rows, and it stores silu(gate) * up.
+//  * prologue: the RMS norm of the rows of the float32 residual stream that feed the product: the rows
+//    times the norm's weight go to shared memory as bfloat16 while their squares are summed, and the row's
+//    1/rms multiplies the finished sums (it is one factor for a whole row of x); on all rows or on the
+//    rows an index names (the final norm before the output head);
+//  * epilogue: store as bfloat16 or float32, ADD into the float32 residual stream (each element has one
+//    owner, so the add is a plain read-modify-write), or the SiLU gate of a stacked gate/up matrix (blocks
+//    of 128 gate rows followed by their 128 "up" rows): a unit's 16 rows are then 8 gate rows and their 8
+//    up rows, and it stores silu(gate) * up.
 //
-// A chain (o_proj -> gate/up -> down -> the next layer's q/k/v, say) is run link by link by the same
-// blocks; between two links all blocks meet at a barrier in global memory (a counter; the wait is
-// bounded and a block that gives up sets MLR_STATUS_TIMEOUT and leaves), and before a warp goes
-// to the barrier it has issued the loads of its first weights of the next link, so that memory
-// keeps streaming while the blocks meet.  Measured on a B200 with the 8B layer sizes: four
-// products as four launches 72 us, as one pass 58 us (6.6 TB/s).  Inside a chain everything that
-// another block may have written (activations, the stream) is read past L1.
+// Two more things keep eight rows as fast as one:
+//  * A product that ADDS into the stream and whose activations would not leave room for the ring (eight
+//    rows of a feed-forward's inner width are 200 KB) is cut along K into parts: each stages only its
+//    columns of x and adds its partial product into the stream (a cell has the same owner in every part).
+//  * Every block needs all of a product's activations, so 148 blocks reading eight float32 rows of the
+//    stream for a norm is 19 MB through L2 (8 us).  The product that added into that stream last has the
+//    final values in hand: `mlr_gemv_bf16_add_prepare` stores them a second time as bfloat16, already times
+//    the norm's weight, and the sum of squares of its 16 rows per token; `mlr_gemv_bf16_prepared` then
+//    stages half the bytes in one pass and adds up the partial sums in a fixed order for the row's 1/rms.
+//
+// Measured on a B200 with the 8B layer sizes in a CUDA graph (o_proj, gate/up, down, q/k/v as launches of
+// their own): 7.3 / 31.5 / 18.6 / 9.8 us at one row, 8.0 / 32.3 / 21.5 / 10.2 us at eight, 6.4 TB/s on the
+// largest.  Run by one persistent grid with meetings of all blocks between the products instead of launch
+// boundaries they took 3.5 us longer per layer, so that form was dropped.
 //
 // The reference sends these products to cuBLAS gemv kernels (src/minillm/cuda/matrix.cpp:30-36) and
 // runs norm, gate and residual add as kernels of their own (src/minillm/cuda/layer.cpp:42-70).
@@ -37,14 +49,17 @@
 
 namespace {
 
-constexpr int kThreads = 512;
-constexpr int kWarps = kThreads / 32;
+constexpr int kConsumerWarps = 16;          // the warps that multiply; they cut each 512 values of K among them
+constexpr int kConsumers = kConsumerWarps * 32;
+constexpr int kThreads = kConsumers + 32;   // and the warp that fetches weights
 constexpr int kUnitRows = 16;
-constexpr int kGroupWarps = 4;           // warps that share a unit of 16 rows (they cut K among them)
-constexpr int kGroups = kWarps / kGroupWarps;
+constexpr int kSlots = 2;
+constexpr int kMostChunk = 2048;            // values of K of a unit's 16 rows in one slot of the ring, at most (4 KB copies)
+constexpr int kStageLoads = 8;              // loads a thread has in flight while a part's activations are staged
 constexpr int kGateBlock = 128;
-constexpr int kMaxLinks = 8;
+constexpr int kMaxParts = 12;
 constexpr int kMaxRows = 8;
+constexpr int kPartialBytes = 2 * kConsumerWarps * kUnitRows * kMaxRows * 4;
 constexpr long long kWaitLimitCycles = 4000000000LL;      // about two seconds
 
 enum Mode : int { kStoreBf16 = 0, kStoreF32 = 1, kAddF32 = 2, kSiluGateBf16 = 3 };
@@ -53,258 +68,319 @@ struct Link {
     const __nv_bfloat16* W;
     long long ldw;
     int N, K;
-    const void* x;              // bfloat16 activations [M, K], or the float32 stream when `norm`
+    const void* x;              // bfloat16 activations [M, K]; the float32 stream when `norm` is 1
     long long ldx;
-    int norm;
+    int norm;                   // 0: x as it is; 1: the RMS norm of the stream in the prologue; 2: x was prepared by the product before
     int norm_weight_bf16;
     const void* norm_weight;
-    const int* row_index;       // with `norm`: row r of the product is row row_index[r] of the stream (null: r)
+    const int* row_index;       // with `norm` 1: row r of the product is row row_index[r] of the stream (null: r)
     float eps;
     int mode;
     void* out;
     long long ldo;
+    // An adding product that prepares the norm of the product after it:
+    __nv_bfloat16* side;        // [M, N] bfloat16: the new stream times `side_weight`
+    const void* side_weight;
+    int side_weight_bf16;
+    float* squares;             // producer: [units][8] sums of squares of a unit's rows per token; consumer (norm 2): the same, to add up
+    int n_squares;              // consumer: how many lines `squares` has
 };
 
-struct Chain {
-    Link links[kMaxLinks];
-    int n_links;
+// One product as the kernel runs it: whole, or cut along K into parts that each add into the stream.
+struct Job {
+    Link parts[kMaxParts];
+    int n_parts;
     int M;
-    unsigned* barrier;          // zero at launch, zero again when the grid has finished
+    int chunk;                  // values of K per ring slot: a multiple of 512
+    int x_bytes;                // shared memory for the activations
     int* status;
 };
 
-__device__ __forceinline__ uint4 load_stream(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.cs.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ unsigned load_acquire(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
 __device__ __forceinline__ void mma_16x8x16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};\n"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ uint4 load_shared16(uint32_t address) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(address));
+    return v;
+}
 
-// The two weight rows a lane reads in unit `u`: rows `first` + g and `first` + g + 8 of a plain matrix; in
-// a stacked gate/up matrix gate row j and its up row, for the 8 outputs j = 8 u .. 8 u + 7.
-__device__ __forceinline__ void rows_of_lane(const Link& l, int unit, int g, int& row_a, int& row_b) {
-    if (l.mode == kSiluGateBf16) {
-        const int j = unit * 8 + g;
-        row_a = (j / kGateBlock) * 2 * kGateBlock + j % kGateBlock;
-        row_b = row_a + kGateBlock;
-    } else {
-        row_a = unit * kUnitRows + g;
-        row_b = row_a + 8;
+// ---- mbarriers and bulk copies (the ring of weights)
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(done)
+                 : "r"(bar), "r"(parity)
+                 : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
+// Waits for a phase of a barrier, but not for ever.  A wait that runs out (about two seconds) sets the block's
+// `failed` flag and MLR_STATUS_TIMEOUT; from then on no wait of the block waits, so that every thread still walks
+// through the same barriers to the kernel's end (its results are then worthless, and the status says so).
+__device__ __forceinline__ void wait_phase(uint32_t bar, uint32_t parity, volatile int* failed, int* status) {
+    if (mbar_try_wait(bar, parity)) return;
+    const long long start = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (*failed) return;
+        if (clock64() - start > kWaitLimitCycles) {
+            *failed = 1;
+            if (status) atomicOr(status, MLR_STATUS_TIMEOUT);
+            return;
+        }
     }
+}
+__device__ __forceinline__ void consumers_sync() { asm volatile("bar.sync 2, %0;\n" ::"n"(kConsumers) : "memory"); }
+
+// Row `r` (0..15) of unit `unit` in W: rows 16 u .. 16 u + 15 of a plain matrix; in a stacked gate/up matrix the gate
+// rows of the 8 outputs j = 8 u .. 8 u + 7 (r < 8) and their up rows (r >= 8).
+__device__ __forceinline__ int row_of_unit(const Link& l, int unit, int r) {
+    if (l.mode == kSiluGateBf16) {
+        const int j = unit * 8 + (r & 7);
+        return (j / kGateBlock) * 2 * kGateBlock + j % kGateBlock + (r >= 8 ? kGateBlock : 0);
+    }
+    return unit * kUnitRows + r;
 }
 __host__ __device__ inline int units_of(const Link& l) {
     return l.mode == kSiluGateBf16 ? l.N / kUnitRows : (l.N + kUnitRows - 1) / kUnitRows;
 }
-// Bytes between rows of the activations in shared memory: K values and a pad that makes it 64 modulo 128,
-// so that the 16-byte reads of the eight rows a quarter-warp touches fall into different banks.
-__host__ __device__ inline int x_stride_bytes(int K) { return K * 2 + ((64 - (K * 2) % 128) + 128) % 128; }
+// Bytes between rows of the activations in shared memory, and between a slot's rows of weights: the values and a
+// pad that makes it 64 modulo 128, so that the 16-byte reads of the eight rows a quarter-warp touches fall into
+// different banks.
+__host__ __device__ inline int pitch_bytes(int values) { return values * 2 + ((64 - (values * 2) % 128) + 128) % 128; }
+__host__ __device__ inline size_t x_region_bytes(int M, int K) { return (static_cast<size_t>(M) * pitch_bytes(K) + 127) / 128 * 128; }
+__host__ __device__ inline size_t ring_bytes(int chunk) { return static_cast<size_t>(kSlots) * kUnitRows * pitch_bytes(chunk); }
 
-// One batch of a lane's weights: two windows of 64 values of its two rows in `unit`, as four 16-byte loads per
-// row (the halves of a window are 32 values apart); nothing beyond K or beyond the warp's last window.
-__device__ __forceinline__ void load_batch(const Link& l, int unit, int win, int win_end, int g, int t, uint4 (&a)[4], uint4 (&b)[4]) {
-    int row_a, row_b;
-    rows_of_lane(l, unit, g, row_a, row_b);
-    const __nv_bfloat16* wa = l.W + static_cast<size_t>(min(row_a, l.N - 1)) * l.ldw;
-    const __nv_bfloat16* wb = l.W + static_cast<size_t>(min(row_b, l.N - 1)) * l.ldw;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int k = (win + (i >> 1)) * 64 + (i & 1) * 32 + t * 8;
-        const bool in = win + (i >> 1) < win_end && k < l.K;
-        a[i] = in ? load_stream(wa + k) : make_uint4(0, 0, 0, 0);
-        b[i] = in ? load_stream(wb + k) : make_uint4(0, 0, 0, 0);
-    }
-}
-
-// All blocks of the grid meet; `target` arrivals in total.  False if the wait ran out.
-__device__ bool grid_meeting(unsigned* counter, unsigned target, int* status, int* shared_flag) {
-    __syncthreads();
+__global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant__ Job job) {
+    extern __shared__ __align__(128) unsigned char shared[];
+    __shared__ float reduce_scratch[32];
+    __shared__ float row_scale[kMaxRows];
+    __shared__ __align__(16) float square_scratch[kConsumerWarps * kMaxRows];
+    __shared__ __align__(8) unsigned long long barriers[2 * kSlots];
+    __shared__ int failed_flag;
+    // [2][16 warps][16 rows][8 tokens] partial sums of the warps' K ranges | the activations | the ring of weights
+    float* partial = reinterpret_cast<float*>(shared);
+    unsigned char* xs = shared + kPartialBytes;
+    const int slot_pitch = pitch_bytes(job.chunk), slot_bytes = kUnitRows * slot_pitch;
+    const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(xs + job.x_bytes));
+    const uint32_t bars = static_cast<uint32_t>(__cvta_generic_to_shared(barriers));
+    auto full_bar = [&](int slot) { return bars + 8u * slot; };
+    auto empty_bar = [&](int slot) { return bars + 8u * (kSlots + slot); };
+    volatile int* failed = &failed_flag;
+    mlr_grid_dependents_may_start();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int M = job.M;
     if (threadIdx.x == 0) {
-        __threadfence();
-        atomicAdd(counter, 1u);
-        int ok = 1;
-        if (load_acquire(counter) < target) {
-            const long long start = clock64();
-            while (load_acquire(counter) < target) {
-                if (clock64() - start > kWaitLimitCycles) {
-                    ok = 0;
-                    break;
+        failed_flag = 0;
+        for (int s = 0; s < kSlots; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), kConsumerWarps);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == kConsumerWarps) {
+        // ---- the warp that fetches: slot after slot, 16 rows x one chunk of W each, a bulk copy per row issued
+        // by 16 lanes, as far ahead as the ring has room.  It does not wait for the kernels before this one.
+        int i = 0;
+        for (int part = 0; part < job.n_parts; ++part) {
+            const Link& l = job.parts[part];
+            const int units = units_of(l), chunks = (l.K + job.chunk - 1) / job.chunk;
+            for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
+                const int row = row_of_unit(l, unit, lane & 15);
+                const bool valid = lane < kUnitRows && row < l.N;
+                const int n_valid = __popc(__ballot_sync(0xffffffffu, valid));
+                const __nv_bfloat16* src = l.W + static_cast<size_t>(valid ? row : 0) * l.ldw;
+                for (int c = 0; c < chunks; ++c, ++i) {
+                    const int slot = i % kSlots;
+                    if (i >= kSlots) wait_phase(empty_bar(slot), ((i / kSlots) - 1) & 1, failed, job.status);
+                    const int k0 = c * job.chunk;
+                    const uint32_t bytes = static_cast<uint32_t>(min(job.chunk, l.K - k0)) * 2u;
+                    if (lane == 0) mbar_expect_tx(full_bar(slot), bytes * n_valid);
+                    __syncwarp();
+                    if (valid && !*failed) bulk_copy(ring + slot * slot_bytes + lane * slot_pitch, src + k0, bytes, full_bar(slot));
                 }
             }
         }
-        __threadfence();
-        if (!ok && status) atomicOr(status, MLR_STATUS_TIMEOUT);
-        *shared_flag = ok;
+        if (*failed) {
+            // Leave only when the copies that were issued have landed (or after another bounded wait): the block's
+            // shared memory must not be given to another block with copies into it in flight.
+            for (int back = 1; back <= kSlots && back <= i; ++back) {
+                const int j = i - back;
+                const long long start = clock64();
+                while (!mbar_try_wait(full_bar(j % kSlots), (j / kSlots) & 1) && clock64() - start < kWaitLimitCycles) {
+                }
+            }
+        }
+        return;
     }
-    __syncthreads();
-    return *shared_flag != 0;
-}
 
-__global__ void __launch_bounds__(kThreads, 1) chain_kernel(const __grid_constant__ Chain chain) {
-    extern __shared__ __align__(16) unsigned char shared[];
-    __shared__ float reduce_scratch[32];
-    __shared__ int meeting_flag;
-    // [2][kWarps][16 rows][8 tokens] partial sums of the warps' K ranges, then the activations.
-    float* partial = reinterpret_cast<float*>(shared);
-    unsigned char* xs = shared + 2 * kWarps * kUnitRows * kMaxRows * sizeof(float);
-    mlr_grid_dependents_may_start();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // ---- the 16 warps that multiply
     const int g = lane >> 2, t = lane & 3;
-    const int group = warp / kGroupWarps, in_group = warp % kGroupWarps;
-    const int M = chain.M;
-    const bool chained = chain.n_links > 1;
-
-    // A warp's first batch of weights of a link is loaded BEFORE the link starts: before the kernels before
-    // this one are done (weights have no writer), and before the blocks meet between two links.
-    uint4 a[4], b[4];
-    int unit = 0, win = 0, win_begin = 0, win_end = 0;
-    bool have = false;
-    auto start_link = [&](const Link& l) {
-        const int windows = (l.K + 63) / 64;
-        win_begin = in_group * windows / kGroupWarps;
-        win_end = (in_group + 1) * windows / kGroupWarps;
-        unit = blockIdx.x * kGroups + group;
-        win = win_begin;
-        have = unit < units_of(l) && win_begin < win_end;
-        if (have) load_batch(l, unit, win, win_end, g, t, a, b);
-    };
-    start_link(chain.links[0]);
     mlr_grid_wait();
+    int parity = 0, i = 0;
+    for (int part = 0; part < job.n_parts; ++part) {
+        const Link& l = job.parts[part];
+        const int K = l.K, stride = pitch_bytes(K);
+        consumers_sync();        // the block's warps are done with the activations of the part before
 
-    int parity = 0;
-    for (int link = 0; link < chain.n_links; ++link) {
-        const Link& l = chain.links[link];
-        const int K = l.K, stride = x_stride_bytes(K);
-        if (link > 0 && !grid_meeting(chain.barrier, static_cast<unsigned>(link) * gridDim.x, chain.status, &meeting_flag)) return;
-
-        // ---- this link's activations into shared memory (what another block wrote is read past L1)
+        // ---- this part's activations into shared memory (read past L1: the kernel before this one wrote them)
         // Rows are dealt to the warps (16 warps: all of them on one row, or 8, 4, 2 warps per row), and every
         // thread issues its loads in batches of eight before it touches any of them, so that a row costs a
         // round trip or two to L2 however many rows there are.
         const int rows_pow2 = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
-        const int row_warps = kWarps / rows_pow2, m = warp / row_warps;
+        const int row_warps = kConsumerWarps / rows_pow2, m = warp / row_warps;
         const int in_row = (warp % row_warps) * 32 + lane, row_threads = row_warps * 32;
-        if (l.norm) {
+        if (l.norm == 1) {
+            // One pass: x * weight goes to shared memory as bfloat16 while the squares are summed; the row's
+            // 1/rms multiplies the finished sums instead (it is one factor for the whole row of x).
             const float* h = static_cast<const float*>(l.x);
             const float* row = h + static_cast<size_t>(m < M ? (l.row_index ? l.row_index[m] : m) : 0) * l.ldx;
             const int quads = K >> 2;
             float sum = 0.0f;
-            if (m < M)
-                for (int base = in_row; base < quads; base += row_threads * 8) {
-                    float4 v[8];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int q = base + j * row_threads;
-                        v[j] = q < quads ? __ldcg(reinterpret_cast<const float4*>(row) + q) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                    }
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) sum += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
-                }
-            sum = mlr_warp_sum(sum);
-            if (lane == 0) reduce_scratch[warp] = sum;
-            __syncthreads();
             if (m < M) {
-                float total = 0.0f;
-                for (int w = 0; w < row_warps; ++w) total += reduce_scratch[m * row_warps + w];
-                const float scale = 1.0f / sqrtf(total / static_cast<float>(K) + l.eps);
                 __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(xs + static_cast<size_t>(m) * stride);
-                for (int base = in_row; base < quads; base += row_threads * 8) {
-                    float4 v[8];
+                for (int base = in_row; base < quads; base += row_threads * kStageLoads) {
+                    float4 v[kStageLoads];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
+                    for (int j = 0; j < kStageLoads; ++j) {
                         const int q = base + j * row_threads;
                         v[j] = q < quads ? __ldcg(reinterpret_cast<const float4*>(row) + q) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                     }
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
+                    for (int j = 0; j < kStageLoads; ++j) {
                         const int q = base + j * row_threads;
+                        sum += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
                         if (q < quads) {
                             float w[4];
                             if (l.norm_weight_bf16) mlr_load4(static_cast<const __nv_bfloat16*>(l.norm_weight) + 4 * q, w);
                             else mlr_load4(static_cast<const float*>(l.norm_weight) + 4 * q, w);
-                            mlr_store4(dst + 4 * q, (v[j].x * scale) * w[0], (v[j].y * scale) * w[1], (v[j].z * scale) * w[2],
-                                       (v[j].w * scale) * w[3]);
+                            mlr_store4(dst + 4 * q, v[j].x * w[0], v[j].y * w[1], v[j].z * w[2], v[j].w * w[3]);
                         }
                     }
                 }
             }
-        } else if (m < M) {
+            sum = mlr_warp_sum(sum);
+            if (lane == 0) reduce_scratch[warp] = sum;
+            consumers_sync();
+            if (threadIdx.x < kMaxRows) {
+                float total = 0.0f;
+                if (threadIdx.x < M)
+                    for (int w = 0; w < row_warps; ++w) total += reduce_scratch[threadIdx.x * row_warps + w];
+                row_scale[threadIdx.x] = 1.0f / sqrtf(total / static_cast<float>(K) + l.eps);
+            }
+        } else {
+            if (l.norm == 2) {
+                // The product before left a line of 8 sums of squares per unit.  Thread j takes the half lines j, j + 512, ...
+                // (4 tokens each, one load per round), lanes 2 apart add up, then the warps in order.
+                const int halves = 2 * l.n_squares;
+                float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int j = threadIdx.x; j < halves; j += kConsumers) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(l.squares) + j);
+                    total.x += v.x, total.y += v.y, total.z += v.z, total.w += v.w;
+                }
+#pragma unroll
+                for (int step = 2; step < 32; step <<= 1) {
+                    total.x += __shfl_xor_sync(0xffffffffu, total.x, step);
+                    total.y += __shfl_xor_sync(0xffffffffu, total.y, step);
+                    total.z += __shfl_xor_sync(0xffffffffu, total.z, step);
+                    total.w += __shfl_xor_sync(0xffffffffu, total.w, step);
+                }
+                if (lane < 2) *reinterpret_cast<float4*>(square_scratch + warp * kMaxRows + lane * 4) = total;
+                consumers_sync();
+                if (threadIdx.x < kMaxRows) {
+                    float sum = 0.0f;
+                    for (int w = 0; w < kConsumerWarps; ++w) sum += square_scratch[w * kMaxRows + threadIdx.x];
+                    row_scale[threadIdx.x] = 1.0f / sqrtf(sum / static_cast<float>(K) + l.eps);
+                }
+            } else if (threadIdx.x < kMaxRows) {
+                row_scale[threadIdx.x] = 1.0f;
+            }
+            if (m < M) {
             const uint4* x = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(l.x) + static_cast<size_t>(m) * l.ldx);
             uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<size_t>(m) * stride);
             const int octs = K >> 3;
-            for (int base = in_row; base < octs; base += row_threads * 8) {
-                uint4 v[8];
+            for (int base = in_row; base < octs; base += row_threads * kStageLoads) {
+                uint4 v[kStageLoads];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
+                for (int j = 0; j < kStageLoads; ++j) {
                     const int q = base + j * row_threads;
                     v[j] = q < octs ? __ldcg(x + q) : make_uint4(0, 0, 0, 0);
                 }
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
+                for (int j = 0; j < kStageLoads; ++j) {
                     const int q = base + j * row_threads;
                     if (q < octs) dst[q] = v[j];
                 }
             }
+            }
         }
-        __syncthreads();
+        consumers_sync();
 
-        // ---- the rows: a group of four warps takes 16 at a time and cuts K among its warps in windows of 64
-        // values.  A warp's loads run one batch (two windows) ahead of its multiply-adds, across the end of a
-        // unit too, so that its requests to memory never pause.
-        const int units = units_of(l);
-        const unsigned char* xrow = xs + static_cast<size_t>(g) * stride;
-        const int unit_stride = gridDim.x * kGroups;
-        const bool idle_warp = win_begin >= win_end;       // more warps than windows: this one only meets the others
-        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        while (unit < units) {
-            int next_unit = unit, next_win = win + 2;
-            if (next_win >= win_end) {
-                next_unit = unit + unit_stride;
-                next_win = win_begin;
-            }
-            uint4 na[4], nb[4];
-            const bool next_have = next_unit < units && !idle_warp;
-            if (next_have) load_batch(l, next_unit, next_win, win_end, g, t, na, nb);
-            if (have) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int k = (win + (i >> 1)) * 64 + (i & 1) * 32 + t * 8;
-                    const bool in = win + (i >> 1) < win_end && k < K && g < M;
-                    const uint4 x = in ? *reinterpret_cast<const uint4*>(xrow + k * 2) : make_uint4(0, 0, 0, 0);
-                    mma_16x8x16(c, a[i].x, b[i].x, a[i].y, b[i].y, x.x, x.y);
-                    mma_16x8x16(c, a[i].z, b[i].z, a[i].w, b[i].w, x.z, x.w);
+        // ---- the rows: a unit of 16 at a time, chunk by chunk as the ring delivers them
+        const int units = units_of(l), chunks = (K + job.chunk - 1) / job.chunk, subs = job.chunk / 512;
+        const uint32_t x_at = static_cast<uint32_t>(__cvta_generic_to_shared(xs)) + g * stride;
+        const uint32_t in_slot = (warp * 32 + t * 8) * 2;
+        for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
+            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (int chunk = 0; chunk < chunks; ++chunk, ++i) {
+                const int slot = i % kSlots;
+                wait_phase(full_bar(slot), (i / kSlots) & 1, failed, job.status);
+                for (int sub = 0; sub < subs; ++sub) {
+                    const int k = chunk * job.chunk + sub * 512 + warp * 32 + t * 8;
+                    const bool in = k < K;
+                    const uint32_t at = ring + slot * slot_bytes + sub * 1024 + in_slot;
+                    const uint4 zero = make_uint4(0, 0, 0, 0);
+                    const uint4 a = in ? load_shared16(at + g * slot_pitch) : zero;
+                    const uint4 b = in ? load_shared16(at + (g + 8) * slot_pitch) : zero;
+                    const uint4 x = in && g < M ? load_shared16(x_at + k * 2) : zero;
+                    mma_16x8x16(c, a.x, b.x, a.y, b.y, x.x, x.y);
+                    mma_16x8x16(c, a.z, b.z, a.w, b.w, x.z, x.w);
                 }
+                __syncwarp();          // every lane's reads of the slot have ended in its multiply-adds
+                if (lane == 0) mbar_arrive(empty_bar(slot));
             }
-            if (next_unit != unit) {
-                // The group's four sums meet in shared memory; its 128 threads add them in warp order and finish the rows.
-                float* mine = partial + (((parity * kGroups + group) * kGroupWarps + in_group) * kUnitRows) * kMaxRows;
+            {
+                // The 16 warps' sums meet in shared memory; 128 threads add them in warp order and finish the rows.
+                float* mine = partial + ((parity * kConsumerWarps + warp) * kUnitRows) * kMaxRows;
                 mine[g * kMaxRows + 2 * t] = c[0];
                 mine[g * kMaxRows + 2 * t + 1] = c[1];
                 mine[(g + 8) * kMaxRows + 2 * t] = c[2];
                 mine[(g + 8) * kMaxRows + 2 * t + 1] = c[3];
-                c[0] = c[1] = c[2] = c[3] = 0.0f;
-                asm volatile("bar.sync %0, %1;\n" ::"r"(1 + group), "r"(kGroupWarps * 32) : "memory");
-                {
-                    const int i = in_group * 32 + lane, r = i >> 3, m = i & 7;
-                    const float* sums = partial + ((parity * kGroups + group) * kGroupWarps * kUnitRows) * kMaxRows + r * kMaxRows + m;
-                    float y = 0.0f;
+                asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumers) : "memory");
+                if (threadIdx.x < kUnitRows * kMaxRows) {
+                    // Thread i finishes row i % 16 of token i / 16: a token's 16 rows are neighbours in memory and in a warp.
+                    const int r = threadIdx.x & 15, m = threadIdx.x >> 4;
+                    const float* sums = partial + (parity * kConsumerWarps * kUnitRows) * kMaxRows + r * kMaxRows + m;
+                    float y = 0.0f, square = 0.0f;
 #pragma unroll
-                    for (int w = 0; w < kGroupWarps; ++w) y += sums[w * kUnitRows * kMaxRows];
+                    for (int w = 0; w < kConsumerWarps; ++w) y += sums[w * kUnitRows * kMaxRows];
+                    y *= row_scale[m];
                     if (m < M) {
                         const size_t at = static_cast<size_t>(m) * l.ldo;
                         if (l.mode == kSiluGateBf16) {
                             if (r < 8) {
                                 float up = 0.0f;
 #pragma unroll
-                                for (int w = 0; w < kGroupWarps; ++w) up += sums[w * kUnitRows * kMaxRows + 8 * kMaxRows];
+                                for (int w = 0; w < kConsumerWarps; ++w) up += sums[w * kUnitRows * kMaxRows + 8 * kMaxRows];
+                                up *= row_scale[m];
                                 static_cast<__nv_bfloat16*>(l.out)[at + unit * 8 + r] = __float2bfloat16_rn((y / (1.0f + expf(-y))) * up);
                             }
                         } else {
@@ -314,45 +390,31 @@ __global__ void __launch_bounds__(kThreads, 1) chain_kernel(const __grid_constan
                                 else if (l.mode == kStoreF32) static_cast<float*>(l.out)[at + row] = y;
                                 else {
                                     float* cell = static_cast<float*>(l.out) + at + row;
-                                    *cell = __ldcg(cell) + y;
+                                    float w = 0.0f;
+                                    if (l.side)
+                                        w = l.side_weight_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(l.side_weight)[row])
+                                                               : static_cast<const float*>(l.side_weight)[row];
+                                    const float sum = __ldcg(cell) + y;
+                                    *cell = sum;
+                                    if (l.side) {
+                                        l.side[static_cast<size_t>(m) * l.N + row] = __float2bfloat16_rn(sum * w);
+                                        square = sum * sum;
+                                    }
                                 }
                             }
                         }
                     }
+                    if (l.side) {
+                        // The squares of a token's 16 rows, added up over the 16 lanes that hold them: one line of 8 per unit.
+#pragma unroll
+                        for (int step = 1; step < 16; step <<= 1) square += __shfl_xor_sync(0xffffffffu, square, step);
+                        if (r == 0) l.squares[static_cast<size_t>(unit) * kMaxRows + m] = square;
+                    }
                 }
                 parity ^= 1;
             }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                a[i] = na[i];
-                b[i] = nb[i];
-            }
-            unit = next_unit;
-            win = next_win;
-            have = next_have;
-        }
-
-        // ---- before the blocks meet: the first weights of the next link
-        if (link + 1 < chain.n_links) start_link(chain.links[link + 1]);
-    }
-    if (chained) {
-        // The last block to leave sets the counter back to zero for the next launch.
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            __threadfence();
-            const unsigned total = static_cast<unsigned>(chain.n_links) * gridDim.x;
-            if (atomicAdd(chain.barrier, 1u) + 1u == total) *chain.barrier = 0u;
         }
     }
-}
-
-size_t shared_bytes_for(const Chain& chain) {
-    size_t most = 0;
-    for (int i = 0; i < chain.n_links; ++i) {
-        const size_t rows = static_cast<size_t>(chain.M) * x_stride_bytes(chain.links[i].K);
-        most = rows > most ? rows : most;
-    }
-    return 2 * kWarps * kUnitRows * kMaxRows * sizeof(float) + most;
 }
 
 int sm_limit_bytes() {
@@ -362,75 +424,92 @@ int sm_limit_bytes() {
     return bytes;
 }
 
-int check_link(const Link& l, int index) {
-    MLR_REQUIRE(l.N >= 1 && l.K >= 8 && l.K % 8 == 0, "gemv_bf16: link %d: bad sizes N=%d K=%d (K must be a multiple of 8)", index, l.N, l.K);
-    MLR_REQUIRE(l.mode >= kStoreBf16 && l.mode <= kSiluGateBf16, "gemv_bf16: link %d: unknown mode %d", index, l.mode);
-    MLR_REQUIRE(l.mode != kSiluGateBf16 || l.N % (2 * kGateBlock) == 0,
-                "gemv_bf16: link %d: a stacked gate/up matrix has a multiple of 256 rows, got %d", index, l.N);
-    MLR_REQUIRE(l.ldw % 8 == 0 && reinterpret_cast<uintptr_t>(l.W) % 16 == 0, "gemv_bf16: link %d: the weight rows must be 16-byte aligned", index);
-    MLR_REQUIRE(l.norm ? (l.ldx % 4 == 0 && reinterpret_cast<uintptr_t>(l.x) % 16 == 0 && l.norm_weight != nullptr &&
-                          reinterpret_cast<uintptr_t>(l.norm_weight) % 16 == 0)
-                       : (l.ldx % 8 == 0 && reinterpret_cast<uintptr_t>(l.x) % 16 == 0),
-                "gemv_bf16: link %d: the activation rows must be 16-byte aligned (and a norm needs its weight)", index);
+// The longest chunk (a multiple of 512 values, at most kMostChunk) whose ring fits beside `x_bytes` of activations; 0: none does.
+int chunk_for(size_t x_bytes) {
+    const size_t room = static_cast<size_t>(sm_limit_bytes()) - 2048;        // the kernel's static shared memory and what the driver keeps
+    for (int chunk = kMostChunk; chunk >= 512; chunk -= 512)
+        if (kPartialBytes + x_bytes + ring_bytes(chunk) <= room) return chunk;
     return 0;
 }
 
-int launch_chain(const Chain& chain, cudaStream_t stream) {
-    MLR_REQUIRE(chain.M >= 1 && chain.M <= kMaxRows, "gemv_bf16: takes 1 to %d rows, got %d", kMaxRows, chain.M);
-    MLR_REQUIRE(chain.n_links >= 1 && chain.n_links <= kMaxLinks, "gemv_bf16: a chain has 1 to %d links, got %d", kMaxLinks, chain.n_links);
-    MLR_REQUIRE(chain.n_links == 1 || chain.barrier != nullptr, "gemv_bf16: a chain of several links needs its meeting counter");
-    for (int i = 0; i < chain.n_links; ++i)
-        if (int e = check_link(chain.links[i], i)) return e;
-    const size_t bytes = shared_bytes_for(chain);
-    MLR_REQUIRE(bytes + 1024 <= static_cast<size_t>(sm_limit_bytes()), "gemv_bf16: rows of %d values do not fit shared memory",
-                chain.links[0].K);
+// How many parts a product over K values is cut into for M rows (1: it stays whole), and the width of a part.  Only a
+// product that adds into the stream can be cut; it is, when its activations would push the ring below its best size.
+int parts_of(int M, int K, int mode, int norm, int& part_width) {
+    part_width = K;
+    if (mode != kAddF32 || norm != 0 || chunk_for(x_region_bytes(M, K)) == kMostChunk) return 1;
+    for (int least = kMostChunk; least >= 512; least -= kMostChunk - 512)       // the best ring if some cut allows it, else any ring
+        for (int parts = 2; parts <= kMaxParts; ++parts) {
+            const int width = ((K + parts - 1) / parts + 63) / 64 * 64;
+            if (chunk_for(x_region_bytes(M, width)) >= least) {
+                part_width = width;
+                return (K + width - 1) / width;
+            }
+        }
+    return 1;
+}
+
+int check_link(const Link& l) {
+    MLR_REQUIRE(l.N >= 1 && l.K >= 8 && l.K % 8 == 0, "gemv_bf16: bad sizes N=%d K=%d (K must be a multiple of 8)", l.N, l.K);
+    MLR_REQUIRE(l.mode >= kStoreBf16 && l.mode <= kSiluGateBf16, "gemv_bf16: unknown mode %d", l.mode);
+    MLR_REQUIRE(l.mode != kSiluGateBf16 || l.N % (2 * kGateBlock) == 0,
+                "gemv_bf16: a stacked gate/up matrix has a multiple of 256 rows, got %d", l.N);
+    MLR_REQUIRE(l.ldw % 8 == 0 && reinterpret_cast<uintptr_t>(l.W) % 16 == 0, "gemv_bf16: the weight rows must be 16-byte aligned");
+    MLR_REQUIRE(l.norm == 1 ? (l.ldx % 4 == 0 && reinterpret_cast<uintptr_t>(l.x) % 16 == 0 && l.norm_weight != nullptr &&
+                               reinterpret_cast<uintptr_t>(l.norm_weight) % 16 == 0)
+                            : (l.ldx % 8 == 0 && reinterpret_cast<uintptr_t>(l.x) % 16 == 0),
+                "gemv_bf16: the activation rows must be 16-byte aligned (and a norm needs its weight)");
+    return 0;
+}
+
+int launch(const Link& l, int M, int* status, cudaStream_t stream) {
+    MLR_REQUIRE(M >= 1 && M <= kMaxRows, "gemv_bf16: takes 1 to %d rows, got %d", kMaxRows, M);
+    if (int e = check_link(l)) return e;
+    Job job = {};
+    job.M = M;
+    job.status = status;
+    int width = 0;
+    job.n_parts = parts_of(M, l.K, l.mode, l.norm, width);
+    for (int part = 0; part < job.n_parts; ++part) {
+        Link& p = job.parts[part];
+        p = l;
+        if (job.n_parts > 1) {
+            const int from = part * width;
+            p.W = l.W + from;
+            p.x = static_cast<const __nv_bfloat16*>(l.x) + from;
+            p.K = l.K - from < width ? l.K - from : width;
+            if (part + 1 < job.n_parts) p.side = nullptr, p.squares = nullptr;       // the last part has the stream's final values
+        }
+    }
+    const size_t x_bytes = x_region_bytes(M, job.parts[0].K);
+    job.chunk = chunk_for(x_bytes);
+    MLR_REQUIRE(job.chunk > 0, "gemv_bf16: %d rows of %d values do not fit shared memory", M, l.K);
+    job.x_bytes = static_cast<int>(x_bytes);
+    const size_t bytes = kPartialBytes + x_bytes + ring_bytes(job.chunk);
     static size_t allowed = 0;
     if (bytes > allowed) {
-        if (cudaFuncSetAttribute(chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) != cudaSuccess) {
+        if (cudaFuncSetAttribute(gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) != cudaSuccess) {
             cudaGetLastError();
             return mlr_fail("gemv_bf16: %zu bytes of shared memory were refused", bytes);
         }
         allowed = bytes;
     }
-    // As many blocks as are resident at once (a chain's blocks wait for one another), at most one per unit of the largest link.
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, chain_kernel, kThreads, bytes) != cudaSuccess || per_sm < 1) {
-        cudaGetLastError();
-        return mlr_fail("gemv_bf16: the kernel does not fit an SM with %zu bytes of shared memory", bytes);
-    }
-    int most_units = 0;
-    for (int i = 0; i < chain.n_links; ++i) most_units = units_of(chain.links[i]) > most_units ? units_of(chain.links[i]) : most_units;
-    const int resident = mlr_sm_count() * per_sm;
-    const int wanted = (most_units + kGroups - 1) / kGroups;          // a block's four groups take a unit each
-    const int grid = wanted < resident ? wanted : resident;
-    mlr_launch((chain_kernel), dim3(grid), dim3(kThreads), bytes, stream, chain);
+    const int units = units_of(l), sms = mlr_sm_count();
+    mlr_launch((gemv_kernel), dim3(units < sms ? units : sms), dim3(kThreads), bytes, stream, job);
     return mlr_launched("gemv_bf16");
 }
 
 }  // namespace
 
-// One link as the host describes it (mirrored by the Python binding).
-struct MlrGemvLink {
-    const void* W;
-    long long ldw;
-    int N, K;
-    const void* x;
-    long long ldx;
-    int norm;
-    int norm_weight_bf16;
-    const void* norm_weight;
-    const int* row_index;
-    float eps;
-    int mode;
-    void* out;
-    long long ldo;
-};
-
-// Whether mlr_gemv_bf16 takes a product of `M` rows over K values (its activations must fit shared memory).
+// Whether mlr_gemv_bf16 takes a product of `M` rows over K values that does not add into the stream (its activations
+// must fit shared memory beside the ring; a product that adds is cut into parts that do).
 MLR_API int mlr_gemv_bf16_fits(int M, int K) {
-    return M >= 1 && M <= kMaxRows && K >= 8 && K % 8 == 0 &&
-           2 * kWarps * kUnitRows * kMaxRows * sizeof(float) + static_cast<size_t>(M) * x_stride_bytes(K) + 1024 <=
-               static_cast<size_t>(sm_limit_bytes());
+    return M >= 1 && M <= kMaxRows && K >= 8 && K % 8 == 0 && chunk_for(x_region_bytes(M, K)) > 0;
+}
+
+// Into how many parts along K an adding product of `M` rows is cut.
+MLR_API int mlr_gemv_bf16_parts(int M, int K) {
+    int width = 0;
+    return parts_of(M < 1 ? 1 : M > kMaxRows ? kMaxRows : M, K, kAddF32, 0, width);
 }
 
 // out = f(x W^T) for 1 <= M <= 8 rows.  W: [N, K] bfloat16, rows `ldw` elements apart (a multiple of 8),
@@ -439,31 +518,40 @@ MLR_API int mlr_gemv_bf16_fits(int M, int K) {
 // bfloat16 or float32, `eps`) of its row row_index[r] (r when row_index is null), rounded to bfloat16.
 // mode 0: out bfloat16 [M, N]; 1: out float32 [M, N]; 2: out float32 [M, N] += the product; 3: W is a
 // stacked gate/up matrix (blocks of 128 gate rows, each followed by its 128 "up" rows; N a multiple of
-// 256) and out is bfloat16 [M, N / 2] = silu(gate) * up.  `ldo`: elements between rows of out.
+// 256) and out is bfloat16 [M, N / 2] = silu(gate) * up.  `ldo`: elements between rows of out.  `status`: a
+// device word in which a wait that ran out sets MLR_STATUS_TIMEOUT.
 MLR_API int mlr_gemv_bf16(const void* W, long long ldw, int N, int K, const void* x, long long ldx, int norm,
                           const void* norm_weight, int norm_weight_bf16, float eps, const int* row_index, int M, void* out,
-                          long long ldo, int mode, cudaStream_t stream) {
-    Chain chain = {};
-    chain.links[0] = Link{static_cast<const __nv_bfloat16*>(W), ldw, N, K, x, ldx, norm, norm_weight_bf16, norm_weight, row_index, eps, mode, out, ldo};
-    chain.n_links = 1;
-    chain.M = M;
-    return launch_chain(chain, stream);
+                          long long ldo, int mode, int* status, cudaStream_t stream) {
+    Link l = {static_cast<const __nv_bfloat16*>(W), ldw, N, K, x, ldx, norm, norm_weight_bf16, norm_weight, row_index, eps, mode, out, ldo};
+    return launch(l, M, status, stream);
 }
 
-// Several such products, each reading what earlier ones wrote, run link by link by one persistent grid
-// (see the head of this file).  `links`: host memory.  `barrier`: one unsigned on the device, zero before the
-// first launch; the kernel leaves it zero.  Launches that share a counter must not overlap on the GPU.
-MLR_API int mlr_gemv_chain(const MlrGemvLink* links, int n_links, int M, unsigned* barrier, int* status, cudaStream_t stream) {
-    MLR_REQUIRE(n_links >= 1 && n_links <= kMaxLinks, "gemv_bf16: a chain has 1 to %d links, got %d", kMaxLinks, n_links);
-    Chain chain = {};
-    for (int i = 0; i < n_links; ++i) {
-        const MlrGemvLink& s = links[i];
-        chain.links[i] = Link{static_cast<const __nv_bfloat16*>(s.W), s.ldw, s.N, s.K, s.x, s.ldx, s.norm, s.norm_weight_bf16, s.norm_weight,
-                              s.row_index, s.eps, s.mode, s.out, s.ldo};
-    }
-    chain.n_links = n_links;
-    chain.M = M;
-    chain.barrier = barrier;
-    chain.status = status;
-    return launch_chain(chain, stream);
+// The two halves of a norm that a product prepares for the product after it.
+// `mlr_gemv_bf16_add_prepare`: out [M, N] float32 += x W^T, and for the RMS norm (weight `norm_weight`) that
+// reads `out` next: `side` [M, N] bfloat16 = the new out times the weight, `squares` [ceil(N / 16)][8] float32 =
+// the sums of squares of 16 columns of out per row.  `mlr_gemv_bf16_prepared`: the product whose input is that
+// norm: x W^T with x = side * 1/sqrt(sum(squares) / K + eps), modes as mlr_gemv_bf16.
+MLR_API int mlr_gemv_bf16_add_prepare(const void* W, long long ldw, int N, int K, const void* x, long long ldx, int M, void* out,
+                                      long long ldo, void* side, const void* norm_weight, int norm_weight_bf16, float* squares,
+                                      int* status, cudaStream_t stream) {
+    MLR_REQUIRE(side != nullptr && norm_weight != nullptr && squares != nullptr && reinterpret_cast<uintptr_t>(side) % 16 == 0 &&
+                    reinterpret_cast<uintptr_t>(squares) % 16 == 0 && N % 8 == 0,
+                "gemv_bf16: preparing a norm takes a side buffer, the norm's weight and room for the squares, 16-byte aligned");
+    Link l = {static_cast<const __nv_bfloat16*>(W), ldw, N, K, x, ldx, 0, 0, nullptr, nullptr, 0.0f, kAddF32, out, ldo};
+    l.side = static_cast<__nv_bfloat16*>(side);
+    l.side_weight = norm_weight;
+    l.side_weight_bf16 = norm_weight_bf16;
+    l.squares = squares;
+    return launch(l, M, status, stream);
+}
+
+MLR_API int mlr_gemv_bf16_prepared(const void* W, long long ldw, int N, int K, const void* side, const float* squares, float eps, int M,
+                                   void* out, long long ldo, int mode, int* status, cudaStream_t stream) {
+    MLR_REQUIRE(side != nullptr && squares != nullptr && reinterpret_cast<uintptr_t>(squares) % 16 == 0,
+                "gemv_bf16: a prepared norm is a side buffer and its squares");
+    Link l = {static_cast<const __nv_bfloat16*>(W), ldw, N, K, side, K, 2, 0, nullptr, nullptr, eps, mode, out, ldo};
+    l.squares = const_cast<float*>(squares);
+    l.n_squares = (K + kUnitRows - 1) / kUnitRows;
+    return launch(l, M, status, stream);
 }

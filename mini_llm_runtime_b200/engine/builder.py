@@ -72,8 +72,8 @@ class Buf:
     slice_stride: int = 0
     tensor: Optional[torch.Tensor] = None
     # A norm that has not been launched: `ptr` is None and this holds (stream Buf, weight tensor, eps,
-    # wanted rows only).  A product that can norm its own input takes it as it is; anyone else asks the
-    # runtime to `materialize` it first.
+    # wanted rows only, what a product prepared of it or None).  A product that can norm its own input takes
+    # it as it is; anyone else asks the runtime to `materialize` it first.
     norm: Optional[tuple] = None
 
     @property
@@ -93,7 +93,18 @@ def _element_size(dtype: torch.dtype) -> int:
 
 
 # --------------------------------------------------------------------------- eager
-class EagerBuilder:
+class _NormHints:
+    """What parts tell one another through the builder about the norm that reads the residual stream next.
+
+    `norm_ahead`: set by whoever arranges the parts (a block, the model) before a part that adds into the stream
+    is described: what `Norm.foldable()` of the next norm returned, or None.  A product that adds into the stream
+    may then prepare that norm (`Runtime.linear_delta`) and says so in `prepared`; the norm's `emit` takes it."""
+    norm_ahead = None
+    norm_after_block = None
+    prepared = None
+
+
+class EagerBuilder(_NormHints):
     """Runs a part's description at once, for one step that Python drives."""
     recording = False
 
@@ -200,7 +211,7 @@ class _PlanField(Sym):
     pass
 
 
-class ProgramBuilder:
+class ProgramBuilder(_NormHints):
     """Records a part's description as ops for a range [lo, hi] of row counts.  Buffers are cut
     from a workspace at `base` (two alternating banks after a fixed part, see `next_bank`)."""
     recording = True
@@ -219,6 +230,7 @@ class ProgramBuilder:
         self.segments = Sym(K_SEGMENTS)
         self.residual: Optional[Buf] = None
         self.ops: List[OpRecord] = []
+        self.names: List[str] = []          # the entry point of each op, for whoever wants to read a program
         self.plans = plans                   # specs registered with the native model, by index
         self._fixed_top = 0                  # bytes of buffers that live for the whole step
         self._bank_top = [0, 0]
@@ -338,6 +350,7 @@ class ProgramBuilder:
             else:
                 raise TypeError(f"{function}: argument {k} of type {type(value).__name__} cannot be recorded")
         self.ops.append(op)
+        self.names.append(function)
 
     _patches: List[tuple]
 

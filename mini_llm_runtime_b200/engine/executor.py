@@ -107,6 +107,7 @@ class NativeStepper:
         self._plans_sent = 0
         self.capacity_rows = 0
         self.allocations = 0             # times a buffer had to grow
+        self.programs = {}               # (rows lo, hi, wanted lo, hi) -> the entry points of the program, in order
         self.workspace = self.logits = self.scratch = self.counters = self.device_meta = None
         self.pinned: List[torch.Tensor] = []
         self._hook = None
@@ -163,6 +164,7 @@ class NativeStepper:
             self._build_program(int(info.need_rows), int(info.need_want))
 
     def _clear_programs(self) -> None:
+        self.programs.clear()
         self.lib.mlr_model_clear_programs(self.handle)
 
     # ---- programs
@@ -197,6 +199,7 @@ class NativeStepper:
             self.lib.mlr_model_add_plan(self.handle, (ctypes.c_int32 * 6)(*spec))
         self._plans_sent = len(self.plans)
         ops = builder.finish()
+        self.programs[(lo, hi, want_lo, want_hi)] = list(builder.names)
         if self.lib.mlr_model_add_program(self.handle, lo, hi, want_lo, want_hi, ops, len(ops)) != 0:
             raise RuntimeError(self.lib.mlr_exec_error().decode())
 

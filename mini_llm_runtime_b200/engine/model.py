@@ -182,9 +182,12 @@ class Model:
         h = self.embedding.emit(b)
         b.start_banks()
         pending = None
-        for run in self.runs:
+        for at, run in enumerate(self.runs):
             b.next_bank()
+            following = self.runs[at + 1].block.first_norm() if at + 1 < len(self.runs) else None
+            b.norm_after_block = following.foldable() if following is not None else None
             pending = run.block.emit(b, h, pending, run.context)
+        b.norm_after_block = None
         b.next_bank()
         x = self.final_norm.emit(b, h, pending, True)
         self.lm_head.emit(b, x)

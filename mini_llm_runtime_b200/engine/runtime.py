@@ -103,16 +103,18 @@ class Runtime:
         self.own_activation_products = False
         # Up to this many rows (at most 8) a product is one pass over the weights by `gemv_bf16.cu`, with the norm
         # before it and the gate or the residual add after it folded in: a decode layer is then six launches
-        # instead of nine and the vendor library is off the decode path.  Off by default (0): in the decode step
-        # of the 8B sizes its four products take 92 us a layer at one row and 125 us at eight, against 89 us for the
-        # split-K tcgen05 products, the library's q/k/v and gate/up and the three row-wise kernels between them.
-        self.gemv_rows = 0
+        # instead of nine and the vendor library is off the decode path.  In the decode step of the 8B sizes
+        # (8 layers, context 2000, CUDA events) a step takes 0.887 ms at one request and 0.994 ms at eight that
+        # way, against 1.013 and 1.087 ms with the split-K tcgen05 products, the library's q/k/v and gate/up and
+        # the three row-wise kernels between them (0 switches back to those).
+        self.gemv_rows = 8
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.shared_memory_limit = torch.cuda.get_device_properties(self.device).shared_memory_per_block_optin
         if dtype is torch.bfloat16:
             _give_library_workspace(self.device)
         self.pair_min_tiles = self.sm_count   # ... and only with at least this many 256 x 256 tiles
         self._splits = {}
+        self._gemv_fit = {}
         self._counters = None
         self.status = None        # the model's device status word (set at bind time)
         self._shared = {}
@@ -245,18 +247,23 @@ class Runtime:
                  out.ld, int(out.dtype is torch.float32), int(accumulate), b.stream, need=b.need_for(x.rows))
 
     # ---- few rows: a pass over the weights with the neighbouring row-wise work folded in
-    def _gemv_fits(self, K: int) -> bool:
-        rows = min(self.gemv_rows, 8)
-        return K % 8 == 0 and 16384 + rows * (2 * K + 128) + 1024 <= self.shared_memory_limit
+    def _gemv_fits(self, K: int, adds: bool = False) -> bool:
+        """Whether the few-row kernel takes `gemv_rows` rows of K values (a product that adds into the stream is cut
+        along K until it does)."""
+        key = (min(self.gemv_rows, 8), K, adds)
+        if key not in self._gemv_fit:
+            self._gemv_fit[key] = K % 8 == 0 and (adds or bool(native.module("gemv_bf16").mlr_gemv_bf16_fits(key[0], K)))
+        return self._gemv_fit[key]
 
     def norm_can_wait(self, b, count, width: int) -> bool:
         """Whether a norm over `count` rows of `width` need not be launched because the product that
         reads it will do it in its prologue."""
         return self.dtype is torch.bfloat16 and self.gemv_rows > 0 and self._gemv_fits(width) and b.le(count, min(self.gemv_rows, 8))
 
-    def _gemv(self, b, x: Buf, w: torch.Tensor) -> bool:
-        """Whether this bf16 product is a few-row pass over the weights."""
-        if self.dtype is not torch.bfloat16 or self.gemv_rows <= 0 or w.dtype is not torch.bfloat16 or not self._gemv_fits(w.shape[1]):
+    def _gemv(self, b, x: Buf, w: torch.Tensor, adds: bool = False) -> bool:
+        """Whether this bf16 product (`adds`: into the float32 stream) is a few-row pass over the weights."""
+        if (self.dtype is not torch.bfloat16 or self.gemv_rows <= 0 or w.dtype is not torch.bfloat16
+                or not self._gemv_fits(w.shape[1], adds and x.norm is None)):
             return False
         if w.stride(1) != 1 or w.stride(0) % 8 or w.data_ptr() % 16 or x.width != w.shape[1]:
             return False
@@ -265,19 +272,39 @@ class Runtime:
         return b.le(x.rows, min(self.gemv_rows, 8))
 
     def _gemv_launch(self, b, x: Buf, w: torch.Tensor, out: Buf, mode: str) -> None:
+        N, K = w.shape
+        ahead = None
+        if mode == "add_f32":
+            ahead, b.norm_ahead = b.norm_ahead, None
+        if x.norm is not None and x.norm[4] is not None:
+            # The product that added into the stream last left this norm half done.
+            prepared = x.norm[4]
+            b.launch("gemv_bf16", "mlr_gemv_bf16_prepared", w.data_ptr(), w.stride(0), N, K, prepared["side"].ptr, prepared["squares"].ptr,
+                     float(x.norm[2]), x.rows, out.ptr, out.ld, F.GEMV_MODES[mode], b.status, b.stream, need=b.need_for(x.rows))
+            return
+        if x.norm is None and ahead is not None and ahead[0] == "rms" and ahead[3] == N and N % 8 == 0 and out.ld == N and self._gemv_fits(N):
+            # The RMS norm that reads the stream next: its input times its weight as bfloat16 and the sums of
+            # squares come out of this product's epilogue, which has the stream's new values in hand.
+            _, weight, eps, _ = ahead
+            side = b.temp(x.rows, N, torch.bfloat16)
+            squares = b.temp((N + 15) // 16, 8, torch.float32)
+            b.launch("gemv_bf16", "mlr_gemv_bf16_add_prepare", w.data_ptr(), w.stride(0), N, K, x.ptr, x.ld, x.rows, out.ptr, out.ld,
+                     side.ptr, weight.data_ptr(), native.is_bf16(weight), squares.ptr, b.status, b.stream, need=b.need_for(x.rows))
+            b.prepared = {"stream": out.ptr, "weight": weight, "side": side, "squares": squares}
+            return
         if x.norm is not None:
-            h, weight, eps, wanted_only = x.norm
+            h, weight, eps, wanted_only, _ = x.norm
             source = (h.ptr, h.ld, 1, weight.data_ptr(), native.is_bf16(weight), float(eps), b.meta("want_rows") if wanted_only else None)
         else:
             source = (x.ptr, x.ld, 0, None, 0, 0.0, None)
-        b.launch("gemv_bf16", "mlr_gemv_bf16", w.data_ptr(), w.stride(0), w.shape[0], w.shape[1], *source, x.rows, out.ptr, out.ld,
-                 F.GEMV_MODES[mode], b.stream, need=b.need_for(x.rows))
+        b.launch("gemv_bf16", "mlr_gemv_bf16", w.data_ptr(), w.stride(0), N, K, *source, x.rows, out.ptr, out.ld,
+                 F.GEMV_MODES[mode], b.status, b.stream, need=b.need_for(x.rows))
 
     def materialize(self, b, x: Buf) -> Buf:
         """The result of a norm that waited for a product (`Buf.norm`), for a reader that cannot norm its own input."""
         if x.norm is None:
             return x
-        h, weight, eps, wanted_only = x.norm
+        h, weight, eps, wanted_only, _ = x.norm
         out = b.temp(x.rows, x.width, x.dtype)
         b.launch("elementwise", "mlr_rmsnorm", h.ptr, None, 1, 0, weight.data_ptr(), native.is_bf16(weight), out.ptr, out.is_bf16,
                  b.meta("want_rows") if wanted_only else None, x.rows, x.width, float(eps), 0, b.stream,
@@ -331,7 +358,7 @@ class Runtime:
         product of a prompt portion adds its result there in its epilogue (into += x W^T,
         one rounding per element as the separate add had) and None is returned."""
         direct = into is not None and self.dtype is torch.bfloat16 and into.dtype is torch.float32 and into.ld == into.width
-        if direct and self._gemv(b, x, w):
+        if direct and self._gemv(b, x, w, adds=True):
             self._gemv_launch(b, x, w, into, "add_f32")
             return None
         parts = self.linear_partials(b, x, w)

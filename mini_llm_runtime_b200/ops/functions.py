@@ -236,54 +236,61 @@ def finite_check(t: torch.Tensor, flag: torch.Tensor) -> None:
 GEMV_MODES = {"bf16": 0, "f32": 1, "add_f32": 2, "silu_gate": 3}
 
 
+def _gemv_operands(w: torch.Tensor, x: torch.Tensor, out: torch.Tensor, mode: str, x_dtype: torch.dtype) -> None:
+    N, K = w.shape
+    if w.dtype is not torch.bfloat16 or w.stride(1) != 1 or x.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemv_bf16: bfloat16 weights and unit inner strides are wanted")
+    if x.dtype is not x_dtype or x.shape[1] != K:
+        raise KernelError("gemv_bf16: x must be bfloat16 [M, K], or the float32 stream when a norm weight is given")
+    columns = N // 2 if mode == "silu_gate" else N
+    want = torch.bfloat16 if mode in ("bf16", "silu_gate") else torch.float32
+    if out.shape[1] != columns or out.dtype is not want:
+        raise KernelError(f"gemv_bf16: an output {tuple(out.shape)} of {out.dtype} does not fit mode {mode!r}")
+
+
 def gemv_bf16(w: torch.Tensor, x: torch.Tensor, out: torch.Tensor, mode: str = "bf16", norm_weight: Optional[torch.Tensor] = None,
-              eps: float = 0.0, rows: Optional[torch.Tensor] = None) -> None:
+              eps: float = 0.0, rows: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> None:
     """out = f(x w^T) for one to eight rows (a pass over the weights).  x is bfloat16 [M, K];
     or, with `norm_weight`, the float32 residual stream, of which row r (row rows[r] when `rows` is given)
     is RMS-normed first.  `mode`: "bf16" / "f32" store, "add_f32" adds into the float32 out, "silu_gate"
     takes w as a stacked gate/up matrix (`interleave_gate_up`) and stores silu(gate) * up in out [M, N / 2]."""
-    on_gpu(w, x, out, norm_weight, rows)
+    on_gpu(w, x, out, norm_weight, rows, status)
     M = out.shape[0]
     N, K = w.shape
     norm = norm_weight is not None
-    if w.dtype is not torch.bfloat16 or w.stride(1) != 1 or x.stride(1) != 1 or out.stride(1) != 1:
-        raise KernelError("gemv_bf16: bfloat16 weights and unit inner strides are wanted")
-    if x.dtype is not (torch.float32 if norm else torch.bfloat16) or x.shape[1] != K:
-        raise KernelError("gemv_bf16: x must be bfloat16 [M, K], or the float32 stream when a norm weight is given")
-    columns = N // 2 if mode == "silu_gate" else N
-    want = torch.bfloat16 if mode in ("bf16", "silu_gate") else torch.float32
-    if out.shape[1] != columns or out.dtype is not want or (not norm and x.shape[0] != M):
-        raise KernelError(f"gemv_bf16: an output {tuple(out.shape)} of {out.dtype} does not fit mode {mode!r}")
+    _gemv_operands(w, x, out, mode, torch.float32 if norm else torch.bfloat16)
+    if not norm and x.shape[0] != M:
+        raise KernelError(f"gemv_bf16: {x.shape[0]} rows of x for {M} rows of out")
     if rows is not None:
         expect(rows, torch.int32, "row indices")
     call("gemv_bf16", "mlr_gemv_bf16", ptr(w), w.stride(0), N, K, ptr(x), x.stride(0), int(norm), ptr(norm_weight),
-         is_bf16(norm_weight) if norm else 0, float(eps), ptr(rows), M, ptr(out), out.stride(0), GEMV_MODES[mode], stream())
+         is_bf16(norm_weight) if norm else 0, float(eps), ptr(rows), M, ptr(out), out.stride(0), GEMV_MODES[mode], ptr(status), stream())
 
 
-class GemvLink(ctypes.Structure):
-    """One link of `mlr_gemv_chain` as the kernel module declares it (MlrGemvLink)."""
-    _fields_ = [("W", ctypes.c_void_p), ("ldw", ctypes.c_longlong), ("N", ctypes.c_int), ("K", ctypes.c_int), ("x", ctypes.c_void_p),
-                ("ldx", ctypes.c_longlong), ("norm", ctypes.c_int), ("norm_weight_bf16", ctypes.c_int), ("norm_weight", ctypes.c_void_p),
-                ("row_index", ctypes.c_void_p), ("eps", ctypes.c_float), ("mode", ctypes.c_int), ("out", ctypes.c_void_p),
-                ("ldo", ctypes.c_longlong)]
+def gemv_bf16_add_prepare(w: torch.Tensor, x: torch.Tensor, out: torch.Tensor, norm_weight: torch.Tensor, side: torch.Tensor,
+                          squares: torch.Tensor, status: Optional[torch.Tensor] = None) -> None:
+    """out += x w^T as `gemv_bf16` in mode "add_f32", and for the RMS norm with `norm_weight` that reads out next:
+    side [M, N] bfloat16 = the new out times the weight, squares [ceil(N / 16), 8] float32 = the sums of squares
+    of 16 columns of out per row (`gemv_bf16_prepared` takes both)."""
+    on_gpu(w, x, out, norm_weight, side, squares, status)
+    M, N = out.shape
+    _gemv_operands(w, x, out, "add_f32", torch.bfloat16)
+    if (side.dtype is not torch.bfloat16 or tuple(side.shape) != (M, N) or not side.is_contiguous() or squares.dtype is not torch.float32
+            or tuple(squares.shape) != ((N + 15) // 16, 8) or not squares.is_contiguous() or norm_weight.shape[0] != N):
+        raise KernelError("gemv_bf16_add_prepare: side is bfloat16 [M, N], squares float32 [ceil(N / 16), 8], the weight [N]")
+    call("gemv_bf16", "mlr_gemv_bf16_add_prepare", ptr(w), w.stride(0), N, w.shape[1], ptr(x), x.stride(0), M, ptr(out), out.stride(0),
+         ptr(side), ptr(norm_weight), is_bf16(norm_weight), ptr(squares), ptr(status), stream())
 
 
-def gemv_chain(links, M: int, counter: torch.Tensor, status: torch.Tensor) -> None:
-    """Several few-row products in one launch, each as `gemv_bf16` takes it (dicts with w, x, out, mode and, for
-    a norm prologue, norm_weight and eps), each reading what earlier ones wrote.  `counter`: one zeroed int32 on
-    the device that the kernel leaves zero."""
-    array = (GemvLink * len(links))()
-    for link, spec in zip(array, links):
-        w, x, out = spec["w"], spec["x"], spec["out"]
-        on_gpu(w, x, out, spec.get("norm_weight"))
-        nw = spec.get("norm_weight")
-        link.W, link.ldw, link.N, link.K = ptr(w), w.stride(0), w.shape[0], w.shape[1]
-        link.x, link.ldx, link.norm = ptr(x), x.stride(0), int(nw is not None)
-        link.norm_weight, link.norm_weight_bf16 = ptr(nw), (is_bf16(nw) if nw is not None else 0)
-        link.row_index, link.eps, link.mode = None, float(spec.get("eps", 0.0)), GEMV_MODES[spec["mode"]]
-        link.out, link.ldo = ptr(out), out.stride(0)
-    expect(counter, torch.int32, "the meeting counter")
-    call("gemv_bf16", "mlr_gemv_chain", array, len(links), M, ptr(counter), ptr(status), stream())
+def gemv_bf16_prepared(w: torch.Tensor, side: torch.Tensor, squares: torch.Tensor, eps: float, out: torch.Tensor, mode: str = "bf16",
+                       status: Optional[torch.Tensor] = None) -> None:
+    """out = f(n w^T) where n is the RMS norm that `gemv_bf16_add_prepare` left half done in `side` and `squares`."""
+    on_gpu(w, side, squares, out, status)
+    _gemv_operands(w, side, out, mode, torch.bfloat16)
+    if not side.is_contiguous() or tuple(squares.shape) != ((w.shape[1] + 15) // 16, 8) or side.shape[0] != out.shape[0]:
+        raise KernelError("gemv_bf16_prepared: side and squares are not what gemv_bf16_add_prepare leaves for this width")
+    call("gemv_bf16", "mlr_gemv_bf16_prepared", ptr(w), w.stride(0), w.shape[0], w.shape[1], ptr(side), ptr(squares), float(eps),
+         out.shape[0], ptr(out), out.stride(0), GEMV_MODES[mode], ptr(status), stream())
 
 
 def product_modules(dtype) -> list:

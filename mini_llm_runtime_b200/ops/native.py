@@ -71,9 +71,13 @@ _SIGNATURES = {
     },
     "gemv_bf16": {
         "mlr_gemv_bf16": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_int, c_float, c_void_p, c_int,
-                          c_void_p, c_longlong, c_int, c_void_p],
+                          c_void_p, c_longlong, c_int, c_void_p, c_void_p],
         "mlr_gemv_bf16_fits": [c_int, c_int],
-        "mlr_gemv_chain": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
+        "mlr_gemv_bf16_parts": [c_int, c_int],
+        "mlr_gemv_bf16_add_prepare": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_void_p,
+                                      c_void_p, c_int, c_void_p, c_void_p, c_void_p],
+        "mlr_gemv_bf16_prepared": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_void_p, c_longlong, c_int,
+                                   c_void_p, c_void_p],
     },
     "weights": {
         "mlr_normal_fill": [c_void_p, c_int, c_longlong, c_ulonglong, c_double, c_int, c_void_p],

@@ -183,6 +183,11 @@ class Norm(Part):
         b = EagerBuilder(step, want_rows=rows)
         return _tensor_of(self.emit(b, b.wrap(h), b.wrap(delta), rows is not None), b)
 
+    def foldable(self):
+        """What a product needs to know to do this norm's work itself ("rms", weight, eps, width), or
+        None: then the norm is always a launch of its own."""
+        return None
+
 
 class PositionEncoding(Part):
     category = "position"
@@ -214,6 +219,11 @@ class Block(Part):
         `pending`; returns the contribution it leaves pending.  `emit(b, h, pending, run)`
         arranges the parts' `emit`s the same way."""
         raise NotImplementedError
+
+    def first_norm(self) -> Optional[Norm]:
+        """The norm this block applies to the residual stream first, if it starts with one: the block before
+        it may then prepare it (`norm_after_block` of the builder)."""
+        return None
 
     def compiles(self) -> bool:
         return (_definer(type(self), "emit") not in _INTERFACES and self.mixer.compiles() and self.feed_forward.compiles()

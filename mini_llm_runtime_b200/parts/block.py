@@ -21,12 +21,21 @@ class PreNormBlock(Block):
         x = self.norms["pre_feed_forward"].forward(h, mixed, step)
         return self.feed_forward.forward(x, step)
 
+    def first_norm(self):
+        return self.norms["pre_mixer"]
+
     def emit(self, b, h, pending, run):
         b.residual = h
+        after = b.norm_after_block
         x = self.norms["pre_mixer"].emit(b, h, pending)
+        # Whoever adds into the stream is told which norm reads it next (a few-row product can leave it half done).
+        b.norm_ahead = self.norms["pre_feed_forward"].foldable()
         mixed = self.mixer.emit(b, x, run)
         x = self.norms["pre_feed_forward"].emit(b, h, mixed)
-        return self.feed_forward.emit(b, x)
+        b.norm_ahead = after
+        out = self.feed_forward.emit(b, x)
+        b.norm_ahead = None
+        return out
 
 
 register_part("block", "pre_norm", PreNormBlock)

@@ -33,15 +33,22 @@ class RmsNorm(Norm):
     def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
         self.weight = rt.vector(tensors[self.spec.weights["weight"]])
 
+    def foldable(self):
+        return ("rms", self.weight, self.eps, self.width)
+
     def emit(self, b, h, delta, wanted_only: bool = False):
         """out[r] = rmsnorm(h[row] + delta[row]) * weight, row = the r-th wanted row or r; unless only
         the wanted rows are normed, the sum is stored back to h, which moves the residual stream on.
         `delta` may be partial sums [S, M, width], which are added in order first."""
         count = b.want if wanted_only else h.rows
+        prepared, b.prepared = b.prepared, None
         if delta is None and b.rt.norm_can_wait(b, count, self.width):
             # The product that reads this norm's result will norm its own input (a few-row product
             # streams the weights once and has the rows in shared memory anyway): nothing to launch here.
-            return Buf(None, count, self.width, b.rt.dtype, self.width, norm=(h, self.weight, self.eps, wanted_only))
+            # The product that last added into the stream may have left this norm half done.
+            if prepared is not None and (wanted_only or prepared["stream"] != h.ptr or prepared["weight"] is not self.weight):
+                prepared = None
+            return Buf(None, count, self.width, b.rt.dtype, self.width, norm=(h, self.weight, self.eps, wanted_only, prepared))
         out = b.temp(count, self.width, b.rt.dtype)
         slices, stride = (delta.slices or 1, delta.slice_stride) if delta is not None else (1, 0)
         b.launch("elementwise", "mlr_rmsnorm", h.ptr, delta.ptr if delta is not None else None, slices, stride,

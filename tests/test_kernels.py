@@ -200,11 +200,19 @@ def test_gemv_bf16_and_what_it_folds_in(M, N, K):
     w = (torch.randn(N, K, generator=gen(2)) * 0.05).to(torch.bfloat16)
     want = x.double() @ w.double().T
     out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
-    F().gemv_bf16(w.to(DEV), x.to(DEV), out, "bf16")
-    assert torch.allclose(out.cpu().double(), want, atol=2e-2, rtol=2e-2)
     out32 = torch.full((M, N), float("nan"), device=DEV)
-    F().gemv_bf16(w.to(DEV), x.to(DEV), out32, "f32")
-    assert torch.allclose(out32.cpu().double(), want, atol=1e-4, rtol=1e-4)
+    native = __import__("mini_llm_runtime_b200.ops.native", fromlist=["x"])
+    if native.module("gemv_bf16").mlr_gemv_bf16_fits(M, K):
+        F().gemv_bf16(w.to(DEV), x.to(DEV), out, "bf16")
+        assert torch.allclose(out.cpu().double(), want, atol=2e-2, rtol=2e-2)
+        F().gemv_bf16(w.to(DEV), x.to(DEV), out32, "f32")
+        assert torch.allclose(out32.cpu().double(), want, atol=1e-4, rtol=1e-4)
+    else:
+        # Eight rows of 12288 values leave no room for the ring of weights: refused, not wrong (a product that
+        # adds into the stream, below, is cut along K instead).
+        assert M * K * 2 > 150 * 1024
+        with pytest.raises(Exception, match="do not fit shared memory"):
+            F().gemv_bf16(w.to(DEV), x.to(DEV), out, "bf16")
     h = torch.randn(M, N, generator=gen(3))
     stream = h.clone().to(DEV)
     F().gemv_bf16(w.to(DEV), x.to(DEV), stream, "add_f32")
@@ -253,60 +261,72 @@ def test_gemv_bf16_refuses_what_it_cannot_do():
     big = torch.zeros(8, 65536, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(Exception, match="do not fit shared memory"):
         F().gemv_bf16(torch.zeros(8, 65536, dtype=torch.bfloat16, device=DEV), big, torch.empty(8, 8, dtype=torch.bfloat16, device=DEV))
+    # ... but a product that adds into the stream is cut along K until its activations fit
+    stream = torch.zeros(8, 8, device=DEV)
+    F().gemv_bf16(torch.ones(8, 65536, dtype=torch.bfloat16, device=DEV), torch.ones(8, 65536, dtype=torch.bfloat16, device=DEV), stream, "add_f32")
+    assert (stream == 65536).all()
 
 
-def test_gemv_chain_is_the_links_one_after_the_other():
-    """Four products of a layer's shape in one launch (each link reads what earlier links wrote; the blocks meet
-    between links) against the same four as launches of their own: the same bits, twice in a row (the meeting
-    counter is left at zero), for several row counts."""
-    H, I, QKV = 256, 768, 384
-    for M in (1, 3, 8):
-        g = lambda seed, *shape: (torch.randn(*shape, generator=gen(seed)) * 0.05).to(torch.bfloat16).to(DEV)
-        w_o, w_down, w_qkv = g(1, H, H), g(2, H, I), g(3, QKV, H)
-        w_gate_up = F().interleave_gate_up(g(4, I, H), g(5, I, H))
-        attn = g(6, M, H)
-        norm1 = (1 + 0.1 * torch.randn(H, generator=gen(7))).to(torch.bfloat16).to(DEV)
-        norm2 = (1 + 0.1 * torch.randn(H, generator=gen(8))).to(torch.bfloat16).to(DEV)
-        stream0 = torch.randn(M, H, generator=gen(9)).to(DEV)
+@pytest.mark.parametrize("M,H,I,QKV", [(8, 512, 6400, 640), (4, 264, 10240, 300), (1, 4096, 12288, 6144), (8, 384, 768, 128), (3, 256, 768, 384)])
+def test_gemv_bf16_layer_with_parts_and_prepared_norms(M, H, I, QKV):
+    """The four products of a layer as a decode step launches them: o_proj adds into the stream and leaves the next
+    norm half done (the stream times the norm's weight as bfloat16, sums of squares per 16 rows), gate/up takes that,
+    down adds (cut along K into parts when its activations are wide: 8 rows of 6400 or 4 of 10240 values are) and
+    prepares the q/k/v product's norm.  Against float64 and against the same products with the norm as a prologue;
+    the same bits on every run."""
+    g = lambda seed, *shape: (torch.randn(*shape, generator=gen(seed)) * 0.04).to(torch.bfloat16).to(DEV)
+    w_o, w_down, w_qkv = g(1, H, H), g(2, H, I), g(3, QKV, H)
+    w_gate_up = F().interleave_gate_up(g(4, I, H), g(5, I, H))
+    attn = g(6, M, H)
+    norm1 = (1 + 0.1 * torch.randn(H, generator=gen(7))).to(torch.bfloat16).to(DEV)
+    norm2 = (1 + 0.1 * torch.randn(H, generator=gen(8))).to(torch.float32).to(DEV)
+    stream0 = torch.randn(M, H, generator=gen(9)).to(DEV)
+    native = __import__("mini_llm_runtime_b200.ops.native", fromlist=["x"])
+    parts = native.module("gemv_bf16").mlr_gemv_bf16_parts
+    assert (parts(M, I) > 1) == (M * I * 2 > 78 * 1024) and parts(M, H) == 1
+    st = status()
 
-        def separate():
-            h = stream0.clone()
-            act = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
-            qkv = torch.empty(M, QKV, dtype=torch.bfloat16, device=DEV)
-            F().gemv_bf16(w_o, attn, h, "add_f32")
-            F().gemv_bf16(w_gate_up, h, act, "silu_gate", norm_weight=norm1, eps=1e-6)
-            F().gemv_bf16(w_down, act, h, "add_f32")
-            F().gemv_bf16(w_qkv, h, qkv, "bf16", norm_weight=norm2, eps=1e-6)
-            return h, act, qkv
+    def layer(prepare):
+        h = stream0.clone()
+        act = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+        qkv = torch.full((M, QKV), float("nan"), dtype=torch.bfloat16, device=DEV)
+        if prepare:
+            side = torch.full((M, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+            squares = torch.full(((H + 15) // 16, 8), float("nan"), device=DEV)
+            F().gemv_bf16_add_prepare(w_o, attn, h, norm1, side, squares, st)
+            F().gemv_bf16_prepared(w_gate_up, side, squares, 1e-6, act, "silu_gate", st)
+            F().gemv_bf16_add_prepare(w_down, act, h, norm2, side, squares, st)
+            F().gemv_bf16_prepared(w_qkv, side, squares, 1e-6, qkv, "bf16", st)
+        else:
+            F().gemv_bf16(w_o, attn, h, "add_f32", status=st)
+            F().gemv_bf16(w_gate_up, h, act, "silu_gate", norm_weight=norm1, eps=1e-6, status=st)
+            F().gemv_bf16(w_down, act, h, "add_f32", status=st)
+            F().gemv_bf16(w_qkv, h, qkv, "bf16", norm_weight=norm2, eps=1e-6, status=st)
+        assert st.item() == 0
+        return h, act, qkv
 
-        def chained(counter):
-            h = stream0.clone()
-            act = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
-            qkv = torch.full((M, QKV), float("nan"), dtype=torch.bfloat16, device=DEV)
-            F().gemv_chain([dict(w=w_o, x=attn, out=h, mode="add_f32"),
-                            dict(w=w_gate_up, x=h, out=act, mode="silu_gate", norm_weight=norm1, eps=1e-6),
-                            dict(w=w_down, x=act, out=h, mode="add_f32"),
-                            dict(w=w_qkv, x=h, out=qkv, mode="bf16", norm_weight=norm2, eps=1e-6)], M, counter, status())
-            return h, act, qkv
+    first, again, plain = layer(True), layer(True), layer(False)
+    for a, b in zip(first, again):
+        assert torch.equal(a, b)
+    # float64 from the same bfloat16 roundings of the activations that the kernel makes: it rounds the stream
+    # times the norm's weight and multiplies the finished sums by 1/rms.
+    wd = lambda t: t.cpu().double()
 
-        want = separate()
-        counter = torch.zeros(1, dtype=torch.int32, device=DEV)
-        for _ in range(2):
-            got = chained(counter)
-            assert int(counter.item()) == 0
-            for a, b in zip(want, got):
-                assert torch.equal(a, b)
-        # ... and the separate launches are right: the stream after o_proj, the gate, down.
-        attn_, h0 = attn.cpu().double(), stream0.cpu().double()
-        h1 = h0 + attn_ @ w_o.cpu().double().T
-        n1 = P.rms_norm(h1.float(), norm1.cpu().float(), 1e-6).to(torch.bfloat16).double()
-        both = n1 @ w_gate_up.cpu().double().T
-        both = both.view(M, -1, 2, 128)
-        gate, up = both[:, :, 0].reshape(M, -1), both[:, :, 1].reshape(M, -1)
-        act = ((gate / (1 + torch.exp(-gate))) * up).to(torch.bfloat16)
-        assert torch.allclose(want[1].cpu().double(), act.double(), atol=3e-2, rtol=3e-2)
-        h2 = h1 + act.double() @ w_down.cpu().double().T
-        assert torch.allclose(want[0].cpu().double(), h2, atol=3e-2, rtol=3e-2)
+    def normed(h, weight):
+        rounded = (h.float() * weight.cpu().float()).to(torch.bfloat16).double()
+        return rounded / torch.sqrt((h.double() ** 2).mean(-1, keepdim=True) + 1e-6)
+
+    h1 = wd(stream0) + wd(attn) @ wd(w_o).T
+    both = (normed(h1, norm1) @ wd(w_gate_up).T).view(M, -1, 2, 128)
+    gate, up = both[:, :, 0].reshape(M, -1), both[:, :, 1].reshape(M, -1)
+    act = ((gate / (1 + torch.exp(-gate))) * up)
+    for got in (first, plain):
+        assert torch.allclose(wd(got[1]), act, atol=2e-2, rtol=2e-2), (wd(got[1]) - act).abs().max()
+        h2 = h1 + wd(got[1]) @ wd(w_down).T                       # from the activations the kernel rounded
+        assert torch.allclose(wd(got[0]), h2, atol=1e-3, rtol=1e-3), (wd(got[0]) - h2).abs().max()
+        want_qkv = normed(got[0].cpu(), norm2) @ wd(w_qkv).T
+        assert torch.allclose(wd(got[2]), want_qkv, atol=3e-2, rtol=3e-2), (wd(got[2]) - want_qkv).abs().max()
+
 
 
 def test_gemm_bf16_tcgen05_every_tile_width():
