@@ -507,7 +507,7 @@ def main() -> int:
               "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
               "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": args.batch,
               "seq_len": context, "context_len": context, "page_size": page, "prefill_tokens": T,
-              "parallelism": "single_gpu", "products": "own kernel only" if args.own_products else "own kernel and vendor library", "l2": f"inputs>L2 ({weight_bytes / 1e9:.1f} GB of weights per step), no flush",
+              "parallelism": "single_gpu", "products": "own kernel only" if args.own_products else "own kernels for steps of up to 8 rows, own kernel and vendor library above", "l2": f"inputs>L2 ({weight_bytes / 1e9:.1f} GB of weights per step), no flush",
               "weight_gb": round(weight_bytes / 1e9, 2), "kv_kb_per_token": kv_bytes_per_token / 1024}
     print(json.dumps({
         "metric": f"decode tok/s ({name} sizes, batch {args.batch}, context {context}, bf16)", "value": value, "unit": "tokens/s",

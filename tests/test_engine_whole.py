@@ -130,6 +130,7 @@ def test_few_row_products_on_both_routes(tmp_path_factory, gemv_rows):
         logits = model.step([StepEntry(s, [tokens[30 + i + step]], [0]) for i, s in enumerate(slots)]).float().cpu()
         for i in range(8):
             assert_close(logits[i:i + 1], want[30 + i + step:31 + i + step], "bfloat16", f"request {i} of eight, step {step}")
+    model.step([StepEntry(slots[0], [tokens[34]], [0])])           # (a workspace that grew dropped the programs built before)
     model.check_status()
     programs = model._native.programs
     one_row = next(names for (lo, hi, _, _), names in programs.items() if lo <= 1 <= hi)
