@@ -76,6 +76,8 @@ enum ArgKind : int32_t {
 enum PlanField : int64_t {
     kItems = 0, kItemCount = 1, kChunk = 2, kMaxSplits = 3, kScratch = 4, kCounters = 5,
     kTiles = 6, kTileCount = 7, kWideTiles = 8, kWideTileCount = 9,
+    // derived: the split-KV items when the step has no prompt tiles / when it has some; the prompt tiles of both kinds
+    kItemsAlone = 10, kItemsBeside = 11, kPromptTiles = 12,
 };
 enum Need : int32_t { kAlways = 0, kIfWanted = 1, kIfPlanField = 2 };
 
@@ -337,6 +339,9 @@ int64_t resolve(const Arg& a, const StepVars& v) {
                 case kTileCount: return p.n_tiles;
                 case kWideTiles: return p.wide_offset < 0 ? 0 : reinterpret_cast<int64_t>(v.extra_base + p.wide_offset);
                 case kWideTileCount: return p.n_wide;
+                case kItemsAlone: return p.n_tiles + p.n_wide == 0 ? p.n_items : 0;
+                case kItemsBeside: return p.n_tiles + p.n_wide == 0 ? 0 : p.n_items;
+                case kPromptTiles: return p.n_tiles + p.n_wide;
             }
             return 0;
         }

@@ -405,6 +405,111 @@ __device__ __forceinline__ void init_ring(const StageRing& ring, int consumers) 
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
 }
 
+// ---------------------------------------------------------------- the step's own tokens, made in place
+// What the split-KV kernel needs to make the q, k and v rows of the step's own tokens itself, from the raw
+// output of the q/k/v product: per-head RMS norm of q and k (weights may be absent), rotation by the table
+// row of the token's position (the table may be absent), and the write of k and v into the cache.  The
+// arithmetic is that of the row-wise kernel that otherwise runs before attention
+// (elementwise.cu: qk_norm_rope_cache_kernel; src/minillm/runtime.cpp:262-281).
+struct FreshRows {
+    const void* q_weight;
+    const void* k_weight;
+    int weight_bf16;
+    float eps;
+    const float* cos_sin;       // [table_positions][head_dim]: cosines of a position's angles, then sines
+    int table_positions;
+    __nv_bfloat16* cache;       // the cache again, to write into
+};
+
+// A row to make, as one warp sees it: what does not depend on the kernel before this one (norm weight and
+// rotation table entries of the lane's elements j = lane + 32 k and j + head_dim / 2) is fetched first, the raw
+// values after the wait for that kernel, and several rows' loads are issued before any is used.
+struct RowTask {
+    bool valid, is_key;
+    int index, token, position;
+    const __nv_bfloat16* src;
+    const void* weight;
+    const float* cs;
+    float wa[4], wb[4], c[4], sn[4], lo[4], hi[4];
+    uint4 value;                    // a key's task also carries 16 bytes of the token's value row
+};
+__device__ __forceinline__ void task_constants(RowTask& t, int head_dim, int weight_bf16) {
+    const int lane = threadIdx.x & 31, half = head_dim >> 1;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int j = lane + 32 * k;
+        t.wa[k] = t.wb[k] = 1.0f;
+        t.c[k] = 1.0f;
+        t.sn[k] = 0.0f;
+        if (t.valid && j < half) {
+            if (t.weight) {
+                t.wa[k] = weight_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(t.weight)[j]) : static_cast<const float*>(t.weight)[j];
+                t.wb[k] = weight_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(t.weight)[j + half])
+                                      : static_cast<const float*>(t.weight)[j + half];
+            }
+            if (t.cs) {
+                t.c[k] = t.cs[j];
+                t.sn[k] = t.cs[j + half];
+            }
+        }
+    }
+}
+__device__ __forceinline__ void task_raw(RowTask& t, int head_dim, const __nv_bfloat16* value_src) {
+    const int lane = threadIdx.x & 31, half = head_dim >> 1;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int j = lane + 32 * k;
+        t.lo[k] = t.hi[k] = 0.0f;
+        if (t.valid && j < half) {
+            t.lo[k] = __bfloat162float(t.src[j]);
+            t.hi[k] = __bfloat162float(t.src[j + half]);
+        }
+    }
+    t.value = make_uint4(0u, 0u, 0u, 0u);
+    if (t.valid && value_src && lane < (head_dim >> 3)) t.value = *reinterpret_cast<const uint4*>(value_src + lane * 8);
+}
+// Norm (if the task has a weight), rotation (if it has table entries), rounding: to `dst` in shared memory in plain
+// order and, for a key, into its cache row.  The arithmetic is that of qk_norm_rope_cache_kernel.
+__device__ __forceinline__ void task_finish(const RowTask& t, int head_dim, float eps, __nv_bfloat16* dst, __nv_bfloat16* cache_row,
+                                            bool swizzled) {
+    const int lane = threadIdx.x & 31, half = head_dim >> 1;
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        sum = fmaf(t.lo[k], t.lo[k], sum);
+        sum = fmaf(t.hi[k], t.hi[k], sum);
+    }
+    float scale = 1.0f;
+    if (t.weight) {
+        sum = mlr_warp_sum(sum);
+        scale = 1.0f / sqrtf(sum / static_cast<float>(head_dim) + eps);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int j = lane + 32 * k;
+        if (j < half) {
+            float a = t.lo[k], b = t.hi[k];
+            if (t.weight) {
+                a = (a * scale) * t.wa[k];
+                b = (b * scale) * t.wb[k];
+            }
+            if (t.cs) {
+                const float ra = __fsub_rn(__fmul_rn(a, t.c[k]), __fmul_rn(b, t.sn[k]));
+                const float rb = __fadd_rn(__fmul_rn(a, t.sn[k]), __fmul_rn(b, t.c[k]));
+                a = ra;
+                b = rb;
+            }
+            const __nv_bfloat16 va = __float2bfloat16_rn(a), vb = __float2bfloat16_rn(b);
+            dst[j] = va;
+            dst[j + half] = vb;
+            if (cache_row) {
+                cache_row[mlr_cache_col(j, t.position, swizzled)] = va;
+                cache_row[mlr_cache_col(j + half, t.position, swizzled)] = vb;
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------- decode: split-KV
 // grid = (max_splits, kv_heads, items), 160 threads: warps 0-3 compute, warp 4 copies.
 // Row r of the block's 16 rows is token r / group, query head kv_head * group + r % group.
@@ -422,13 +527,18 @@ __device__ __forceinline__ void init_ring(const StageRing& ring, int consumers) 
 // to `out` directly.
 constexpr int kDecodeThreads = 160;
 
-template <int DMAX, bool BLOCKS>
+// FRESH: `q` is the raw output of the q/k/v product (queries, keys, values in a row) and nothing of the
+// step's own tokens is in the cache yet.  The block makes its 16 query rows itself (norm, rotation), and the
+// block whose keys include a token of the step makes that token's key and value, writes them into the cache
+// and puts them into its tile in place of what the copy brought.  The kernel before this one then is the
+// product, not a row-wise kernel, and the copies of the keys of earlier steps need not wait for it.
+template <int DMAX, bool BLOCKS, bool FRESH>
 __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
     const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat16* __restrict__ out, int ldo,
-    const __nv_bfloat16* __restrict__ cache, int num_pages, const int* __restrict__ items,
+    const __nv_bfloat16* cache, int num_pages, const int* __restrict__ items,
     const int* __restrict__ segment_info, const int* __restrict__ block_table, int table_stride,
     int page_size, int q_heads, int kv_heads, int head_dim, int window, float scale, int chunk,
-    int max_splits, float* __restrict__ partial, int* __restrict__ counters, int* status) {
+    int max_splits, float* __restrict__ partial, int* __restrict__ counters, int* status, const FreshRows fresh) {
     mlr_grid_dependents_may_start();
     // The segment table and the block table were uploaded before the step's first kernel;
     // what the preceding kernel writes (queries, the new keys and values) is read after
@@ -473,11 +583,11 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
 
     if (warp == 4) {
         if (!copy_warp<DMAX, BLOCKS>(ring, cache, block_table + static_cast<size_t>(segment) * table_stride, num_pages,
-                                     page_size, kv_heads, head_dim, kv_head, key_begin, key_end, first_valid, tiles, start, &fault))
+                                     page_size, kv_heads, head_dim, kv_head, key_begin, key_end, first_valid, tiles, FRESH ? 0x7fffffff : start, &fault))
             fault = 2;
     } else {
         // ---------------- compute warps
-        mlr_grid_wait();
+        if (!FRESH) mlr_grid_wait();
         const int g = lane >> 2;
         int lo[2], hi[2];
         const __nv_bfloat16* qptr[2];
@@ -490,6 +600,78 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
             lo[r] = valid ? (window > 0 ? max(0, start + token - window + 1) : 0) : 0;
             qptr[r] = valid ? q + static_cast<size_t>(first_row + token) * ldq + static_cast<size_t>(head) * head_dim : nullptr;
         }
+        // FRESH: behind the stages, [16][DMAX] made query rows, then the made keys and values of the step's tokens.
+        __nv_bfloat16* made_q = reinterpret_cast<__nv_bfloat16*>(smem + static_cast<size_t>(kDecodeStages) * 2 * L::kBytes);
+        __nv_bfloat16* made_k = made_q + 16 * DMAX;
+        __nv_bfloat16* made_v = made_k + 16 * DMAX;
+        if constexpr (FRESH) {
+            const bool swizzled = mlr_cache_swizzled(true, head_dim);
+            const size_t head_elems = static_cast<size_t>(page_size) * head_dim;
+            // The rows to make: this block's query rows, then the tokens of the step among this block's keys (a key's
+            // task copies the token's value too).  Warp w takes rows w, w + 4, ...; two at a time.
+            const int query_rows = count * group;
+            const int token_from = max(0, key_begin - start), token_to = min(count, key_end - start);
+            const int total = query_rows + max(0, token_to - token_from);
+            bool waited = false;
+            for (int base = warp; base < total || !waited; base += 8) {
+                RowTask task[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    RowTask& t = task[u];
+                    const int id = base + 4 * u;
+                    t.valid = id < total;
+                    t.is_key = id >= query_rows;
+                    t.token = t.is_key ? token_from + id - query_rows : id / group;
+                    t.index = t.is_key ? t.token : id;
+                    t.position = start + t.token;
+                    const int head = t.is_key ? q_heads + kv_head : kv_head * group + id % group;
+                    t.src = q + static_cast<size_t>(first_row + t.token) * ldq + static_cast<size_t>(head) * head_dim;
+                    t.weight = t.is_key ? fresh.k_weight : fresh.q_weight;
+                    t.cs = nullptr;
+                    if (t.valid && fresh.cos_sin) {
+                        if (t.position < 0 || t.position >= fresh.table_positions) {
+                            if (lane == 0 && status) atomicOr(status, MLR_STATUS_BAD_INDEX);
+                            t.valid = false;
+                        } else {
+                            t.cs = fresh.cos_sin + static_cast<size_t>(t.position) * head_dim;
+                        }
+                    }
+                    task_constants(t, head_dim, fresh.weight_bf16);
+                }
+                if (!waited) {
+                    mlr_grid_wait();        // what came so far had no writer in flight; the product's rows have
+                    waited = true;
+                }
+#pragma unroll
+                for (int u = 0; u < 2; ++u)
+                    task_raw(task[u], head_dim, task[u].is_key ? task[u].src + static_cast<size_t>(kv_heads) * head_dim : nullptr);
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const RowTask& t = task[u];
+                    if (!t.valid) continue;
+                    __nv_bfloat16 *key_row = nullptr, *value_row = nullptr;
+                    if (t.is_key) {
+                        const int page = block_table[static_cast<size_t>(segment) * table_stride + t.position / page_size];
+                        if (page < 0 || page >= num_pages) {
+                            if (lane == 0) fault = 1;
+                            continue;
+                        }
+                        key_row = fresh.cache + static_cast<size_t>(page) * 2 * kv_heads * head_elems + static_cast<size_t>(kv_head) * head_elems +
+                                  static_cast<size_t>(t.position % page_size) * head_dim;
+                        value_row = key_row + static_cast<size_t>(kv_heads) * head_elems;
+                        if (lane < (head_dim >> 3)) {
+                            *reinterpret_cast<uint4*>(made_v + t.index * DMAX + lane * 8) = t.value;
+                            *reinterpret_cast<uint4*>(value_row + mlr_cache_col(lane * 8, t.position, swizzled)) = t.value;
+                        }
+                    }
+                    task_finish(t, head_dim, fresh.eps, (t.is_key ? made_k : made_q) + t.index * DMAX, key_row, swizzled);
+                }
+            }
+            asm volatile("bar.sync 1, 128;\n" ::: "memory");        // the four compute warps: every made row is there
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+                if (qptr[r]) qptr[r] = made_q + (g + 8 * r) * DMAX;
+        }
         uint32_t qf[DMAX / 16][4];
         load_q<DMAX>(qf, qptr[0], qptr[1], dim_steps);
         const float scale_log2 = scale * kLog2e;
@@ -500,6 +682,31 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
             ok = __all_sync(0xffffffffu, mbar_wait(full_bar(stage), (it / kDecodeStages) & 1));     // the whole warp goes on, or none of it
             if (!ok) break;
             const int key_base = key_begin + it * kTileKeys + warp * 16;
+            if constexpr (FRESH) {
+                // The keys and values of the step's own tokens among this warp's 16 keys: from the made rows.
+                const int from = max(start, key_base), to = min(min(start + count, key_base + 16), key_end);
+                const int chunks = head_dim >> 3;
+                for (int position = from; position < to; ++position) {
+                    const int token = position - start, row = position - (key_begin + it * kTileKeys);
+                    for (int c = lane; c < 2 * chunks; c += 32) {
+                        const bool value = c >= chunks;
+                        const int cc = value ? c - chunks : c;
+                        const uint4 v = *reinterpret_cast<const uint4*>((value ? made_v : made_k) + token * DMAX + cc * 8);
+                        *reinterpret_cast<uint4*>(ring.smem + ((value ? v_stage(stage) : k_stage(stage)) - ring.smem_base) + L::offset(row, cc)) = v;
+                    }
+                }
+                if (!BLOCKS && (key_base < first_valid || key_base + 16 > key_end)) {
+                    // Row by row copies fill a key outside the split's range with the nearest key inside it, which here
+                    // may be one the cache does not hold yet: such value rows are zero instead (their scores are masked).
+                    for (int c = lane; c < 16 * chunks; c += 32) {
+                        const int r = c / chunks, position = key_base + r;
+                        if (position < first_valid || position >= key_end)
+                            *reinterpret_cast<uint4*>(ring.smem + (v_stage(stage) - ring.smem_base) + L::offset(warp * 16 + r, c - r * chunks)) =
+                                make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+                __syncwarp();
+            }
             if (key_base < key_end) {
                 float s[2][4] = {};
                 qk_keys<DMAX, 1, L>(s, qf, k_stage(stage), warp * 16, dim_steps);
@@ -847,30 +1054,38 @@ MLR_API long long mlr_attention_decode_scratch_floats(int items, int kv_heads, i
 // max_splits: the most splits any item needs (the grid's x extent).  partial: scratch of
 // mlr_attention_decode_scratch_floats floats, and counters: n_items * kv_heads ints that are
 // zero on entry and are left zero (both may be null when max_splits == 1).
-MLR_API int mlr_attention_decode_bf16(const void* q, int ldq, void* out, int ldo, const void* cache, int num_pages,
-                                      const int* items, int n_items, const int* segment_info,
-                                      const int* block_table, int table_stride, int page_size, int q_heads,
-                                      int kv_heads, int head_dim, int window, float scale, int chunk,
-                                      int max_splits, float* partial, int* counters, int* status, cudaStream_t stream) {
-    if (int e = check_common("attention_decode_bf16", q_heads, kv_heads, head_dim, page_size, num_pages, window, ldq, ldo, scale)) return e;
-    MLR_REQUIRE(q_heads / kv_heads <= 16, "attention_decode_bf16: %d query heads per kv head exceed the 16 rows of a block", q_heads / kv_heads);
-    MLR_REQUIRE(chunk > 0 && chunk % kTileKeys == 0, "attention_decode_bf16: chunk %d is not a positive multiple of %d", chunk, kTileKeys);
-    MLR_REQUIRE(max_splits >= 1 && max_splits <= 512 && (max_splits == 1 || (partial && counters)), "attention_decode_bf16: the split count must be in [1, 512], with scratch and counters when above 1");
-    MLR_REQUIRE(reinterpret_cast<uintptr_t>(partial) % 16 == 0, "attention_decode_bf16: the scratch must be 16-byte aligned");
-    MLR_REQUIRE(n_items >= 0 && n_items <= 65535, "attention_decode_bf16: more than 65535 requests in one launch");
+namespace {
+int launch_decode(const char* what, const void* q, int ldq, void* out, int ldo, const void* cache, int num_pages, const int* items,
+                  int n_items, const int* segment_info, const int* block_table, int table_stride, int page_size, int q_heads,
+                  int kv_heads, int head_dim, int window, float scale, int chunk, int max_splits, float* partial, int* counters,
+                  int* status, const FreshRows* fresh, cudaStream_t stream) {
+    if (int e = check_common(what, q_heads, kv_heads, head_dim, page_size, num_pages, window, ldq, ldo, scale)) return e;
+    MLR_REQUIRE(q_heads / kv_heads <= 16, "%s: %d query heads per kv head exceed the 16 rows of a block", what, q_heads / kv_heads);
+    MLR_REQUIRE(chunk > 0 && chunk % kTileKeys == 0, "%s: chunk %d is not a positive multiple of %d", what, chunk, kTileKeys);
+    MLR_REQUIRE(max_splits >= 1 && max_splits <= 512 && (max_splits == 1 || (partial && counters)),
+                "%s: the split count must be in [1, 512], with scratch and counters when above 1", what);
+    MLR_REQUIRE(reinterpret_cast<uintptr_t>(partial) % 16 == 0, "%s: the scratch must be 16-byte aligned", what);
+    MLR_REQUIRE(n_items >= 0 && n_items <= 65535, "%s: more than 65535 requests in one launch", what);
     if (n_items == 0) return 0;
     const dim3 grid(max_splits, kv_heads, n_items);
-#define MLR_LAUNCH(DMAX, BLOCKS)                                                                                   \
-    do {                                                                                                           \
-        const size_t merge = sizeof(float) * (4 * 16 * DMAX + 4 * 16 * 2 + 32 * max_splits);                       \
-        const size_t tile = BLOCKS ? Tile<DMAX>::kBytes : PaddedTile<DMAX>::kBytes;                                \
-        const size_t stages = static_cast<size_t>(kDecodeStages) * 2 * tile;                                       \
-        const size_t bytes = stages > merge ? stages : merge;                                                      \
-        if (int e = allow_smem(decode_splitkv_kernel<DMAX, BLOCKS>, bytes, "attention_decode_bf16")) return e;    \
-        mlr_launch((decode_splitkv_kernel<DMAX, BLOCKS>), dim3(grid), dim3(kDecodeThreads), bytes, stream,                               \
-            static_cast<const __nv_bfloat16*>(q), ldq, static_cast<__nv_bfloat16*>(out), ldo,                      \
-            static_cast<const __nv_bfloat16*>(cache), num_pages, items, segment_info, block_table, table_stride,   \
-            page_size, q_heads, kv_heads, head_dim, window, scale, chunk, max_splits, partial, counters, status);  \
+    const FreshRows none = {};
+#define MLR_LAUNCH_AS(DMAX, BLOCKS, FRESH)                                                                              \
+    do {                                                                                                                \
+        const size_t merge = sizeof(float) * (4 * 16 * DMAX + 4 * 16 * 2 + 32 * max_splits);                            \
+        const size_t tile = BLOCKS ? Tile<DMAX>::kBytes : PaddedTile<DMAX>::kBytes;                                     \
+        const size_t stages = static_cast<size_t>(kDecodeStages) * 2 * tile + (FRESH ? 3 * 16 * DMAX * 2 : 0);          \
+        const size_t bytes = stages > merge ? stages : merge;                                                           \
+        if (int e = allow_smem(decode_splitkv_kernel<DMAX, BLOCKS, FRESH>, bytes, what)) return e;                      \
+        mlr_launch((decode_splitkv_kernel<DMAX, BLOCKS, FRESH>), dim3(grid), dim3(kDecodeThreads), bytes, stream,       \
+            static_cast<const __nv_bfloat16*>(q), ldq, static_cast<__nv_bfloat16*>(out), ldo,                           \
+            static_cast<const __nv_bfloat16*>(cache), num_pages, items, segment_info, block_table, table_stride,        \
+            page_size, q_heads, kv_heads, head_dim, window, scale, chunk, max_splits, partial, counters, status,        \
+            FRESH ? *fresh : none);                                                                                     \
+    } while (0)
+#define MLR_LAUNCH(DMAX, BLOCKS)                    \
+    do {                                            \
+        if (fresh) MLR_LAUNCH_AS(DMAX, BLOCKS, true); \
+        else MLR_LAUNCH_AS(DMAX, BLOCKS, false);    \
     } while (0)
     if (head_dim == 64) MLR_LAUNCH(64, true);
     else if (head_dim == 128) MLR_LAUNCH(128, true);
@@ -879,7 +1094,40 @@ MLR_API int mlr_attention_decode_bf16(const void* q, int ldq, void* out, int ldo
     else if (head_dim < 128) MLR_LAUNCH(128, false);
     else MLR_LAUNCH(256, false);
 #undef MLR_LAUNCH
-    return mlr_launched("attention_decode_bf16");
+#undef MLR_LAUNCH_AS
+    return mlr_launched(what);
+}
+}  // namespace
+
+MLR_API int mlr_attention_decode_bf16(const void* q, int ldq, void* out, int ldo, const void* cache, int num_pages,
+                                      const int* items, int n_items, const int* segment_info,
+                                      const int* block_table, int table_stride, int page_size, int q_heads,
+                                      int kv_heads, int head_dim, int window, float scale, int chunk,
+                                      int max_splits, float* partial, int* counters, int* status, cudaStream_t stream) {
+    return launch_decode("attention_decode_bf16", q, ldq, out, ldo, cache, num_pages, items, n_items, segment_info, block_table,
+                         table_stride, page_size, q_heads, kv_heads, head_dim, window, scale, chunk, max_splits, partial, counters,
+                         status, nullptr, stream);
+}
+
+// The same over the RAW output of the q/k/v product: `qkv` rows hold q_heads query heads, then kv_heads key
+// heads, then kv_heads value heads, none of them normed or rotated, and the cache does not hold the step's own
+// tokens yet.  The kernel norms q and k per head (`q_weight`, `k_weight`: bfloat16 or float32 as `weight_bf16`
+// says, both null for no norm; `eps`), rotates them by row `position` of `cos_sin` [table_positions][head_dim]
+// (null: no rotation), writes k and v into `cache` and attends.  It replaces the row-wise kernel that otherwise
+// runs before attention when every segment of the step is one of `items`.
+MLR_API int mlr_attention_decode_fresh_bf16(const void* qkv, int ld, void* out, int ldo, void* cache, int num_pages, const int* items,
+                                            int n_items, const int* segment_info, const int* block_table, int table_stride,
+                                            int page_size, int q_heads, int kv_heads, int head_dim, int window, float scale,
+                                            int chunk, int max_splits, float* partial, int* counters, const void* q_weight,
+                                            const void* k_weight, int weight_bf16, float eps, const float* cos_sin,
+                                            int table_positions, int* status, cudaStream_t stream) {
+    MLR_REQUIRE((q_weight == nullptr) == (k_weight == nullptr), "attention_decode_fresh_bf16: q and k norm weights must both be given or both be absent");
+    MLR_REQUIRE(ld >= (q_heads + 2 * kv_heads) * head_dim, "attention_decode_fresh_bf16: row stride %d is smaller than the q/k/v width", ld);
+    MLR_REQUIRE(cos_sin == nullptr || table_positions > 0, "attention_decode_fresh_bf16: a rotation table without rows");
+    const FreshRows fresh = {q_weight, k_weight, weight_bf16, eps, cos_sin, table_positions, static_cast<__nv_bfloat16*>(cache)};
+    return launch_decode("attention_decode_fresh_bf16", qkv, ld, out, ldo, cache, num_pages, items, n_items, segment_info, block_table,
+                         table_stride, page_size, q_heads, kv_heads, head_dim, window, scale, chunk, max_splits, partial, counters,
+                         status, &fresh, stream);
 }
 
 // ---------------------------------------------------------------- the entry point that allocates nothing

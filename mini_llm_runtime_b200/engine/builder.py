@@ -31,7 +31,9 @@ from ..ops import native
 META = {"token_ids": 0, "positions": 1, "segment_of_row": 2, "segment_info": 3, "slots": 4, "want_rows": 5}
 # Fields of an attention launch plan (PlanField in the executor).
 PLAN_FIELDS = {"items": 0, "n_items": 1, "chunk": 2, "max_splits": 3, "scratch": 4, "counters": 5,
-               "tiles": 6, "n_tiles": 7, "wide_tiles": 8, "n_wide": 9}
+               "tiles": 6, "n_tiles": 7, "wide_tiles": 8, "n_wide": 9,
+               # derived: the split-KV items when the step has no prompt tiles / when it has some; all prompt tiles
+               "n_items_alone": 10, "n_items_beside": 11, "n_prompt_tiles": 12}
 
 K_IMM, K_FLOAT, K_ROWS, K_WANT, K_SEGMENTS, K_META, K_TABLE, K_TABLE_STRIDE, K_PLAN, K_STREAM, K_LOGITS = range(11)
 NEED_ALWAYS, NEED_WANTED, NEED_PLAN_FIELD = 0, 1, 2
@@ -183,6 +185,10 @@ class EagerBuilder(_NormHints):
                         "max_splits": values["max_splits"], "scratch": scratch.data_ptr() if scratch is not None else 0,
                         "counters": counters.data_ptr(), "tiles": at(values["tiles_offset"]), "n_tiles": values["n_tiles"],
                         "wide_tiles": at(values["wide_offset"]), "n_wide": values["n_wide"], "_held": (held, scratch, counters)})
+        prompt_tiles = values["n_tiles"] + values["n_wide"]
+        plan.n_prompt_tiles = prompt_tiles
+        plan.n_items_alone = 0 if prompt_tiles else values["n_items"]
+        plan.n_items_beside = values["n_items"] if prompt_tiles else 0
         self.step.scratch[key] = plan
         return plan
 

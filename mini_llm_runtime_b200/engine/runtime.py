@@ -59,7 +59,7 @@ def _give_library_workspace(device: torch.device) -> None:
         _library_workspace[index] = space
 
 
-_ROUTING = {"gemv_rows", "use_tcgen05", "tcgen05_prefill", "pair_rows", "pair_everything", "tcgen05_attention", "decode_rows",
+_ROUTING = {"gemv_rows", "fuse_rotation", "use_tcgen05", "tcgen05_prefill", "pair_rows", "pair_everything", "tcgen05_attention", "decode_rows",
             "own_activation_products", "pair_min_tiles"}
 
 
@@ -108,6 +108,9 @@ class Runtime:
         # way, against 1.013 and 1.087 ms with the split-K tcgen05 products, the library's q/k/v and gate/up and
         # the three row-wise kernels between them (0 switches back to those).
         self.gemv_rows = 8
+        # A step of decoded tokens only: the split-KV attention kernel norms, rotates and writes the cache itself
+        # (no row-wise kernel between the q/k/v product and attention).
+        self.fuse_rotation = True
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.shared_memory_limit = torch.cuda.get_device_properties(self.device).shared_memory_per_block_optin
         if dtype is torch.bfloat16:

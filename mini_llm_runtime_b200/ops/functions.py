@@ -178,6 +178,41 @@ def attention_decode_bf16(q: torch.Tensor, out: torch.Tensor, cache: torch.Tenso
          ptr(counters), ptr(status), stream())
 
 
+def attention_decode_fresh_bf16(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, items: Optional[torch.Tensor],
+                                n_items: int, segment_info: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                                q_heads: int, kv_heads: int, head_dim: int, window: int, scale: float, chunk: int,
+                                max_splits: int, partial: Optional[torch.Tensor], q_weight: Optional[torch.Tensor],
+                                k_weight: Optional[torch.Tensor], eps: float, cos_sin: Optional[torch.Tensor],
+                                status: torch.Tensor, counters: Optional[torch.Tensor] = None) -> None:
+    """`attention_decode_bf16` over the RAW output of the q/k/v product [M, (Hq + 2 Hkv) D]: the kernel norms q and k
+    per head, rotates them by the table row of each token's position, writes the step's k and v into the cache and
+    attends; it stands for `qk_norm_rope_cache` followed by `attention_decode_bf16` when every segment of the step is
+    one of `items`.  qkv is left as it was."""
+    on_gpu(qkv, out, cache, items, segment_info, block_table, partial, status, counters, q_weight, k_weight, cos_sin)
+    if max_splits > 1 and counters is None:
+        counters = torch.zeros(n_items * kv_heads, dtype=torch.int32, device=qkv.device)
+    for t in (qkv, out, cache):
+        if t.dtype is not torch.bfloat16:
+            raise KernelError("attention_decode_fresh_bf16 takes bfloat16 tensors")
+    if qkv.stride(1) != 1 or out.stride(1) != 1 or not cache.is_contiguous():
+        raise KernelError("attention: inner strides must be 1 and the cache contiguous")
+    if cos_sin is not None:
+        expect(cos_sin, torch.float32, "the rotation table")
+        if cos_sin.shape[1] != head_dim or not cos_sin.is_contiguous():
+            raise KernelError("attention_decode_fresh_bf16: the rotation table must be [positions, head_dim]")
+    if q_weight is not None and k_weight is not None and q_weight.dtype is not k_weight.dtype:
+        raise KernelError("attention_decode_fresh_bf16: q and k norm weights must share a dtype")
+    if partial is not None:
+        expect(partial, torch.float32, "the split scratch")
+        if partial.numel() < attention_decode_scratch_floats(n_items, kv_heads, head_dim, max_splits):
+            raise KernelError("attention_decode_fresh_bf16: the split scratch is too small")
+    call("attention_bf16", "mlr_attention_decode_fresh_bf16", ptr(qkv), qkv.stride(0), ptr(out), out.stride(0), ptr(cache),
+         cache.shape[0], ptr(items), n_items, ptr(segment_info), ptr(block_table), block_table.stride(0), page_size,
+         q_heads, kv_heads, head_dim, int(window), float(scale), int(chunk), int(max_splits), ptr(partial), ptr(counters),
+         ptr(q_weight), ptr(k_weight), is_bf16(q_weight) if q_weight is not None else 0, float(eps), ptr(cos_sin),
+         cos_sin.shape[0] if cos_sin is not None else 0, ptr(status), stream())
+
+
 def attention_decode_scratch_floats(n_items: int, kv_heads: int, head_dim: int, max_splits: int) -> int:
     return n_items * kv_heads * max_splits * 16 * (head_dim + 2)
 

@@ -84,6 +84,13 @@ class AttentionMixer(Mixer):
         rotation = self.position.rotation_table() if self.position is not None else None
         if run.write_cache and run.cache.dtype is not qkv.dtype:
             raise native.KernelError(f"cache dtype {run.cache.dtype} differs from activation dtype {qkv.dtype}")
+        out = b.temp(x.rows, self.heads * D, rt.dtype)
+        # When every segment of a step is a decoded token (or a portion of two or three), the split-KV kernel
+        # norms and rotates its own queries and makes the step's keys and values itself: the row-wise kernel
+        # below then runs only in steps that also have prompt tiles.
+        plan, _ = A.plan_for(b, qkv, out, self.heads, self.kv_heads, D, self.window or 0)
+        fused = (plan is not None and partials is None and run.write_cache and rt.fuse_rotation
+                 and (rotation is None or rotation.shape[1] == D) and D <= 256)
         # In place on qkv: per-head RMS norm of q and k, rotation by the table row of each position, and
         # the write of k and v into the run's cache (from the product's partial sums when it left those).
         b.launch("elementwise", "mlr_qk_norm_rope_cache", qkv.ptr, qkv.is_bf16, qkv.ld,
@@ -97,9 +104,10 @@ class AttentionMixer(Mixer):
                  rotation.data_ptr() if rotation is not None else None,
                  rotation.shape[1] if rotation is not None else 0, rotation.shape[0] if rotation is not None else 0,
                  b.meta("positions"), b.meta("segment_of_row"), b.table(run.group), b.table_stride(run.group), b.page_size,
-                 run.cache.data_ptr(), run.cache.shape[0], int(run.write_cache), b.status, b.stream)
-        out = b.temp(x.rows, self.heads * D, rt.dtype)
-        A.paged_attention(b, qkv, out, run.cache, run.group, self.heads, self.kv_heads, D, self.window or 0, self.scale)
+                 run.cache.data_ptr(), run.cache.shape[0], int(run.write_cache), b.status, b.stream,
+                 need=plan.n_prompt_tiles if fused else None)
+        fresh = (self.q_norm, self.k_norm, self.qk_norm_eps, rotation) if fused else None
+        A.paged_attention(b, qkv, out, run.cache, run.group, self.heads, self.kv_heads, D, self.window or 0, self.scale, fresh=fresh)
         return rt.linear_delta(b, out, self.w_o, into=b.residual)
 
 

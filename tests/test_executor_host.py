@@ -204,3 +204,21 @@ def test_the_table_hook_sees_each_step_s_rows():
     owned = host.cache.table_row(0, a)[:3]
     assert seen == [(0, 1, 3, owned)]
     assert section(host, host.recorded()[0][0], 3) == [owned[1], owned[0], owned[2]]
+
+
+def test_plan_fields_that_say_whether_decoded_tokens_have_the_step_to_themselves():
+    """`n_items_alone` / `n_items_beside` / `n_prompt_tiles`: a launch that stands for two others when a step has only
+    decoded tokens depends on the first, the two others on the rest."""
+    host = Host()
+    a, b = host.cache.open(), host.cache.open()
+    fields = [(K_PLAN, host.plan, PLAN_FIELDS[name]) for name in ("n_items", "n_items_alone", "n_items_beside", "n_prompt_tiles")]
+    host.program([host.op(fields),
+                  host.op([(K_IMM, 0, 1)], need=NEED_PLAN_FIELD, need_field=PLAN_FIELDS["n_items_alone"]),
+                  host.op([(K_IMM, 0, 2)], need=NEED_PLAN_FIELD, need_field=PLAN_FIELDS["n_items_beside"]),
+                  host.op([(K_IMM, 0, 3)], need=NEED_PLAN_FIELD, need_field=PLAN_FIELDS["n_prompt_tiles"])])
+    assert host.step([(a, [5, 6, 7, 8, 9, 10], []), (b, [11], [0])])[0] == X.STEP_OK       # a prompt portion beside a token
+    recorded = host.recorded()
+    assert recorded[0][:4] == [1, 0, 1, 1] and [r[0] for r in recorded[1:]] == [2, 3]
+    assert host.step([(a, [1], [0]), (b, [2, 3], [1])])[0] == X.STEP_OK                    # tokens only
+    recorded = host.recorded()
+    assert recorded[0][:4] == [2, 2, 0, 0] and [r[0] for r in recorded[1:]] == [1]

@@ -775,6 +775,58 @@ def test_qk_norm_rope_cache(Hq, Hkv, D, page, dtype, wdtype, segs):
     assert torch.equal(dev2[:, Hq * D:].cpu(), qkv[:, Hq * D:])
 
 
+@pytest.mark.parametrize("Hq,Hkv,D,page,window", [(32, 8, 128, 16, 0), (4, 2, 16, 4, 0), (5, 1, 48, 16, 0), (3, 3, 256, 8, 0), (14, 2, 64, 8, 0),
+                                                  (32, 8, 128, 16, 70), (6, 2, 80, 32, 33), (16, 1, 64, 16, 0)])
+@pytest.mark.parametrize("norms,rotate,wdtype", [(True, True, torch.bfloat16), (True, True, torch.float32), (False, True, torch.bfloat16),
+                                                 (True, False, torch.bfloat16)], ids=["bf16w", "f32w", "no-norm", "no-rotation"])
+def test_decode_attention_that_makes_its_own_rows(Hq, Hkv, D, page, window, norms, rotate, wdtype):
+    """The split-KV kernel over the raw output of the q/k/v product (it norms, rotates, writes the cache and attends)
+    against the row-wise kernel followed by the plain split-KV kernel: the same cache rows and the same attention,
+    for decoded tokens and portions of two and three tokens at the start of a sequence, across page and split
+    edges, with a window, with and without norm weights and rotation; nothing else of the cache is touched."""
+    from mini_llm_runtime_b200.parts.rotary import rotation_table
+    group = Hq // Hkv
+    most = max(1, 16 // group)
+    segs = [(0, 1), (63, min(2, most)), (64, 1), (127, min(3, most)), (200, 1), (15, min(2, most)), (321, 1), (0, min(3, most))]
+    rows = sum(c for _, c in segs)
+    eps, scale, chunk = 1e-5, D ** -0.5, 64
+    qkv = torch.randn(rows, (Hq + 2 * Hkv) * D, generator=gen(0)).to(torch.bfloat16)
+    wq = (1 + 0.1 * torch.randn(D, generator=gen(1))).to(torch.bfloat16).to(wdtype).to(DEV) if norms else None
+    wk = (1 + 0.1 * torch.randn(D, generator=gen(2))).to(torch.bfloat16).to(wdtype).to(DEV) if norms else None
+    table_cs = rotation_table(50000.0, D, 512).to(DEV) if rotate else None
+    positions, seg_of_row, info = segments_meta(segs)
+    # Earlier tokens of every request in the cache, the step's own positions filled with NaN.
+    kvs = []
+    for i, (start, count) in enumerate(segs):
+        k = torch.randn(start + count, Hkv, D, generator=gen(10 + i))
+        v = torch.randn(start + count, Hkv, D, generator=gen(50 + i))
+        k[start:], v[start:] = float("nan"), float("nan")
+        kvs.append((k, v))
+    cache0, table = make_cache(kvs, page, torch.bfloat16, seed=4)
+    longest = max(s + c for s, c in segs)
+    max_splits = -(-longest // chunk)
+    scratch = torch.empty(F().attention_decode_scratch_floats(len(segs), Hkv, D, max_splits), device=DEV)
+    st = status()
+
+    cache_a, qkv_a = cache0.clone(), qkv.to(DEV)
+    out_a = torch.full((rows, Hq * D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    F().qk_norm_rope_cache(qkv_a, Hq, Hkv, D, wq, wk, eps, table_cs, positions, seg_of_row, table, page, cache_a, True, st)
+    F().attention_decode_bf16(qkv_a, out_a, cache_a, None, len(segs), info, table, page, Hq, Hkv, D, window, scale, chunk, max_splits,
+                              scratch, st)
+    cache_b, qkv_b = cache0.clone(), qkv.to(DEV)
+    out_b = torch.full((rows, Hq * D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    F().attention_decode_fresh_bf16(qkv_b, out_b, cache_b, None, len(segs), info, table, page, Hq, Hkv, D, window, scale, chunk,
+                                    max_splits, scratch, wq, wk, eps, table_cs, st)
+    assert st.item() == 0
+    assert torch.equal(qkv_b.cpu(), qkv)                                   # the product's output is left alone
+    a, b = cache_a.float().cpu(), cache_b.float().cpu()
+    assert torch.equal(torch.isnan(a), torch.isnan(b)), "the two routes wrote different cache rows"
+    assert torch.allclose(torch.nan_to_num(a), torch.nan_to_num(b), atol=2e-2, rtol=1e-2)
+    assert torch.equal(a[:, 1], b[:, 1]) or torch.equal(torch.nan_to_num(a[:, 1]), torch.nan_to_num(b[:, 1]))     # values are copied
+    assert not torch.isnan(out_b.float()).any()
+    assert torch.allclose(out_a.float().cpu(), out_b.float().cpu(), atol=3e-2, rtol=3e-2), (out_a.float() - out_b.float()).abs().max()
+
+
 def test_qk_kernel_reports_a_page_outside_the_pool():
     pos, seg, info = segments_meta([(0, 2)])
     qkv = torch.zeros(2, 3 * 16, device=DEV)
