@@ -89,8 +89,8 @@ class AttentionMixer(Mixer):
         # norms and rotates its own queries and makes the step's keys and values itself: the row-wise kernel
         # below then runs only in steps that also have prompt tiles.
         plan, _ = A.plan_for(b, qkv, out, self.heads, self.kv_heads, D, self.window or 0)
-        fused = (plan is not None and partials is None and run.write_cache and rt.fuse_rotation
-                 and (rotation is None or rotation.shape[1] == D) and D <= 256)
+        fused = (plan is not None and partials is None and run.write_cache and (rotation is None or rotation.shape[1] == D)
+                 and D <= 256 and rt.fuse_rotation_rows > 0 and b.le(x.rows, rt.fuse_rotation_rows))
         # In place on qkv: per-head RMS norm of q and k, rotation by the table row of each position, and
         # the write of k and v into the run's cache (from the product's partial sums when it left those).
         b.launch("elementwise", "mlr_qk_norm_rope_cache", qkv.ptr, qkv.is_bf16, qkv.ld,

@@ -111,18 +111,20 @@ def test_every_product_on_the_own_kernel(tmp_path_factory):
         assert_close(logits[i:i + 1], want[20 + i:21 + i], "bfloat16", f"own products, request {i} of a batch of 12")
 
 
-@pytest.mark.parametrize("gemv_rows", [8, 2, 0])
-def test_few_row_products_on_both_routes(tmp_path_factory, gemv_rows):
+@pytest.mark.parametrize("gemv_rows,fuse_rows", [(8, 32), (2, 32), (0, 32), (8, 0)])
+def test_few_row_products_on_both_routes(tmp_path_factory, gemv_rows, fuse_rows):
     """Decode steps of up to `Runtime.gemv_rows` rows run on the kernel that norms its own input, gates, adds into the
     stream and prepares the next norm; with 0 the split-K products, the library and the row-wise kernels between
     them take those steps (and with 2, steps of three to eight rows).  One request token by token, and eight
-    requests together, on each; the programs name the kernels that were meant."""
+    requests together, on each; the programs name the kernels that were meant.  With `fuse_rotation_rows` the split-KV
+    attention kernel makes its own queries, keys and values from the product's raw output in steps of tokens only."""
     from mini_llm_runtime_b200.engine.model import StepEntry
     folder, config, weights = tiny_folder(tmp_path_factory, "tiny_d", seed=41)
     tokens = random_tokens(config, 120, 6)
     want = plain_qwen3.forward(config, weights, tokens)
     model = engine_model(folder, "bfloat16", num_pages=96, max_requests=8)
     model.rt.gemv_rows = gemv_rows
+    model.rt.fuse_rotation_rows = fuse_rows
     assert_close(run_portions(model, tokens, [60, 1]), want, "bfloat16", "token by token")
     slots = [model.open_request() for _ in range(8)]
     model.step([StepEntry(s, tokens[:30 + i], []) for i, s in enumerate(slots)])
@@ -137,6 +139,8 @@ def test_few_row_products_on_both_routes(tmp_path_factory, gemv_rows):
     eight_rows = next(names for (lo, hi, _, _), names in programs.items() if lo <= 8 <= hi)
     assert ("mlr_gemv_bf16_prepared" in one_row) == (gemv_rows > 0) and ("mlr_gemv_bf16_prepared" in eight_rows) == (gemv_rows == 8)
     assert ("mlr_rmsnorm" in eight_rows) == (gemv_rows < 8)
+    # (the split-K products of the other route leave partial sums, which only the row-wise kernel adds up)
+    assert ("mlr_attention_decode_fresh_bf16" in one_row) == (fuse_rows > 0 and gemv_rows > 0)
 
 
 def test_thirty_two_query_heads_per_kv_head_decode_from_graphs(tmp_path_factory):
