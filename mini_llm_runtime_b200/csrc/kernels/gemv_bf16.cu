@@ -2,6 +2,7 @@
 //
 // With so few rows a product is a pass over the weight matrix and nothing else, so the kernel is built
 // around the memory system.  One warp of each block does nothing but fetch: it keeps a ring of two slots
+// (three where one row of activations leaves room: more bytes on their way, 3 us a layer at the 8B sizes)
 // of shared memory filled with the weights of 16 rows of W (a "unit") over a chunk of K, a bulk copy
 // (`cp.async.bulk`, completion counted by an mbarrier) of up to 4 KB per row.  A bulk copy costs the copy
 // engine about 50 ns whatever its size, so the rows are copied in pieces as long as shared memory allows;
@@ -53,7 +54,7 @@ constexpr int kConsumerWarps = 16;          // the warps that multiply; they cut
 constexpr int kConsumers = kConsumerWarps * 32;
 constexpr int kThreads = kConsumers + 32;   // and the warp that fetches weights
 constexpr int kUnitRows = 16;
-constexpr int kSlots = 2;
+constexpr int kMostSlots = 3;
 constexpr int kMostChunk = 2048;            // values of K of a unit's 16 rows in one slot of the ring, at most (4 KB copies)
 constexpr int kStageLoads = 8;              // loads a thread has in flight while a part's activations are staged
 constexpr int kGateBlock = 128;
@@ -93,6 +94,7 @@ struct Job {
     int M;
     int chunk;                  // values of K per ring slot: a multiple of 512
     int x_bytes;                // shared memory for the activations
+    int slots;                  // of the ring: 2, or 3 where the activations leave room
     int* status;
 };
 
@@ -164,14 +166,14 @@ __host__ __device__ inline int units_of(const Link& l) {
 // different banks.
 __host__ __device__ inline int pitch_bytes(int values) { return values * 2 + ((64 - (values * 2) % 128) + 128) % 128; }
 __host__ __device__ inline size_t x_region_bytes(int M, int K) { return (static_cast<size_t>(M) * pitch_bytes(K) + 127) / 128 * 128; }
-__host__ __device__ inline size_t ring_bytes(int chunk) { return static_cast<size_t>(kSlots) * kUnitRows * pitch_bytes(chunk); }
+__host__ __device__ inline size_t ring_bytes(int chunk, int slots) { return static_cast<size_t>(slots) * kUnitRows * pitch_bytes(chunk); }
 
 __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant__ Job job) {
     extern __shared__ __align__(128) unsigned char shared[];
     __shared__ float reduce_scratch[32];
     __shared__ float row_scale[kMaxRows];
     __shared__ __align__(16) float square_scratch[kConsumerWarps * kMaxRows];
-    __shared__ __align__(8) unsigned long long barriers[2 * kSlots];
+    __shared__ __align__(8) unsigned long long barriers[2 * kMostSlots];
     __shared__ int failed_flag;
     // [2][16 warps][16 rows][8 tokens] partial sums of the warps' K ranges | the activations | the ring of weights
     float* partial = reinterpret_cast<float*>(shared);
@@ -180,14 +182,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(xs + job.x_bytes));
     const uint32_t bars = static_cast<uint32_t>(__cvta_generic_to_shared(barriers));
     auto full_bar = [&](int slot) { return bars + 8u * slot; };
-    auto empty_bar = [&](int slot) { return bars + 8u * (kSlots + slot); };
+    auto empty_bar = [&](int slot) { return bars + 8u * (kMostSlots + slot); };
     volatile int* failed = &failed_flag;
     mlr_grid_dependents_may_start();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int M = job.M;
+    const int M = job.M, slots = job.slots;
     if (threadIdx.x == 0) {
         failed_flag = 0;
-        for (int s = 0; s < kSlots; ++s) {
+        for (int s = 0; s < slots; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), kConsumerWarps);
         }
@@ -209,8 +211,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
                 const int n_valid = __popc(__ballot_sync(0xffffffffu, valid));
                 const __nv_bfloat16* src = l.W + static_cast<size_t>(valid ? row : 0) * l.ldw;
                 for (int c = 0; c < chunks; ++c, ++i) {
-                    const int slot = i % kSlots;
-                    if (i >= kSlots) wait_phase(empty_bar(slot), ((i / kSlots) - 1) & 1, failed, job.status);
+                    const int slot = i % slots;
+                    if (i >= slots) wait_phase(empty_bar(slot), ((i / slots) - 1) & 1, failed, job.status);
                     const int k0 = c * job.chunk;
                     const uint32_t bytes = static_cast<uint32_t>(min(job.chunk, l.K - k0)) * 2u;
                     if (lane == 0) mbar_expect_tx(full_bar(slot), bytes * n_valid);
@@ -222,10 +224,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
         if (*failed) {
             // Leave only when the copies that were issued have landed (or after another bounded wait): the block's
             // shared memory must not be given to another block with copies into it in flight.
-            for (int back = 1; back <= kSlots && back <= i; ++back) {
+            for (int back = 1; back <= slots && back <= i; ++back) {
                 const int j = i - back;
                 const long long start = clock64();
-                while (!mbar_try_wait(full_bar(j % kSlots), (j / kSlots) & 1) && clock64() - start < kWaitLimitCycles) {
+                while (!mbar_try_wait(full_bar(j % slots), (j / slots) & 1) && clock64() - start < kWaitLimitCycles) {
                 }
             }
         }
@@ -341,8 +343,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
         for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
             float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             for (int chunk = 0; chunk < chunks; ++chunk, ++i) {
-                const int slot = i % kSlots;
-                wait_phase(full_bar(slot), (i / kSlots) & 1, failed, job.status);
+                const int slot = i % slots;
+                wait_phase(full_bar(slot), (i / slots) & 1, failed, job.status);
                 for (int sub = 0; sub < subs; ++sub) {
                     const int k = chunk * job.chunk + sub * 512 + warp * 32 + t * 8;
                     const bool in = k < K;
@@ -428,8 +430,13 @@ int sm_limit_bytes() {
 int chunk_for(size_t x_bytes) {
     const size_t room = static_cast<size_t>(sm_limit_bytes()) - 2048;        // the kernel's static shared memory and what the driver keeps
     for (int chunk = kMostChunk; chunk >= 512; chunk -= 512)
-        if (kPartialBytes + x_bytes + ring_bytes(chunk) <= room) return chunk;
+        if (kPartialBytes + x_bytes + ring_bytes(chunk, 2) <= room) return chunk;
     return 0;
+}
+// Slots of the ring: a third one where the activations leave room for it (one or two rows of a model's width).
+int slots_for(size_t x_bytes, int chunk) {
+    const size_t room = static_cast<size_t>(sm_limit_bytes()) - 2048;
+    return kPartialBytes + x_bytes + ring_bytes(chunk, kMostSlots) <= room ? kMostSlots : 2;
 }
 
 // How many parts a product over K values is cut into for M rows (1: it stays whole), and the width of a part.  Only a
@@ -484,7 +491,8 @@ int launch(const Link& l, int M, int* status, cudaStream_t stream) {
     job.chunk = chunk_for(x_bytes);
     MLR_REQUIRE(job.chunk > 0, "gemv_bf16: %d rows of %d values do not fit shared memory", M, l.K);
     job.x_bytes = static_cast<int>(x_bytes);
-    const size_t bytes = kPartialBytes + x_bytes + ring_bytes(job.chunk);
+    job.slots = slots_for(x_bytes, job.chunk);
+    const size_t bytes = kPartialBytes + x_bytes + ring_bytes(job.chunk, job.slots);
     static size_t allowed = 0;
     if (bytes > allowed) {
         if (cudaFuncSetAttribute(gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) != cudaSuccess) {
