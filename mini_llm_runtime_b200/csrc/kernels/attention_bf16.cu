@@ -461,12 +461,12 @@ __device__ __forceinline__ void task_raw(RowTask& t, int head_dim, const __nv_bf
         const int j = lane + 32 * k;
         t.lo[k] = t.hi[k] = 0.0f;
         if (t.valid && j < half) {
-            t.lo[k] = __bfloat162float(t.src[j]);
-            t.hi[k] = __bfloat162float(t.src[j + half]);
+            t.lo[k] = __bfloat162float(__ldcg(t.src + j));           // not through the read-only path: the kernel before this
+            t.hi[k] = __bfloat162float(__ldcg(t.src + j + half));    // one wrote these after this kernel had started
         }
     }
     t.value = make_uint4(0u, 0u, 0u, 0u);
-    if (t.valid && value_src && lane < (head_dim >> 3)) t.value = *reinterpret_cast<const uint4*>(value_src + lane * 8);
+    if (t.valid && value_src && lane < (head_dim >> 3)) t.value = __ldcg(reinterpret_cast<const uint4*>(value_src) + lane);
 }
 // Norm (if the task has a weight), rotation (if it has table entries), rounding: to `dst` in shared memory in plain
 // order and, for a key, into its cache row.  The arithmetic is that of qk_norm_rope_cache_kernel.
@@ -534,12 +534,14 @@ constexpr int kDecodeThreads = 160;
 // product, not a row-wise kernel, and the copies of the keys of earlier steps need not wait for it.
 template <int DMAX, bool BLOCKS, bool FRESH>
 __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
-    const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat16* __restrict__ out, int ldo,
+    const __nv_bfloat16* q, int ldq, __nv_bfloat16* __restrict__ out, int ldo,
     const __nv_bfloat16* cache, int num_pages, const int* __restrict__ items,
     const int* __restrict__ segment_info, const int* __restrict__ block_table, int table_stride,
     int page_size, int q_heads, int kv_heads, int head_dim, int window, float scale, int chunk,
     int max_splits, float* __restrict__ partial, int* __restrict__ counters, int* status, const FreshRows fresh) {
     mlr_grid_dependents_may_start();
+    // `q` is NOT declared __restrict__: the kernel before this one writes it while this one may already run, and a
+    // load the compiler knows to be of read-only memory may be moved above the wait for that kernel.
     // The segment table and the block table were uploaded before the step's first kernel;
     // what the preceding kernel writes (queries, the new keys and values) is read after
     // mlr_grid_wait() below.
@@ -894,7 +896,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_splitkv_kernel(
 // runs per SM and the kernel loses about a third of its speed.
 template <int DMAX, bool BLOCKS>
 __global__ void __launch_bounds__(kDecodeThreads) __maxnreg__(DMAX <= 128 ? 168 : 255) prefill_kernel(
-    const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat16* __restrict__ out, int ldo,
+    const __nv_bfloat16* q, int ldq, __nv_bfloat16* __restrict__ out, int ldo,
     const __nv_bfloat16* __restrict__ cache, int num_pages, const int* __restrict__ tiles,
     const int* __restrict__ segment_info, const int* __restrict__ block_table, int table_stride,
     int page_size, int q_heads, int kv_heads, int head_dim, int window, float scale, int* status) {

@@ -35,6 +35,23 @@ def test_first_tokens(case, dtype):
         assert_close(run_whole(model, tokens[:n]), want[:n], dtype, f"first {n} tokens")
 
 
+@pytest.mark.parametrize("filler", [float("nan"), 1e30, -7.0])
+def test_first_tokens_do_not_depend_on_what_memory_held_before(tmp_path_factory, filler):
+    """Every buffer of a fresh model lies in memory that held something else before.  A kernel that reads what the
+    kernel before it writes BEFORE that kernel has finished (a load moved above the wait of a programmatic dependent
+    launch) sees that old content; the first steps of a small model, where launches follow each other fastest, show it."""
+    folder, config, weights = tiny_folder(tmp_path_factory, "tiny_d", seed=3)
+    tokens = random_tokens(config, 8, 103)
+    want = plain_qwen3.forward(config, weights, tokens)
+    for trial in range(4):
+        held = [torch.empty(1 << 20, dtype=torch.float32, device="cuda:0").fill_(filler) for _ in range(64)]
+        del held                                    # the allocator hands these blocks to the model next
+        model = engine_model(folder, "bfloat16", num_pages=32)
+        for n in (1, 2, 3):
+            assert_close(run_whole(model, tokens[:n]), want[:n], "bfloat16", f"trial {trial}, first {n} tokens over memory full of {filler}")
+        del model
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_last_32_one_by_one(case, dtype):
     folder, config, tokens, want = case
