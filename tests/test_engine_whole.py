@@ -156,8 +156,10 @@ def test_few_row_products_on_both_routes(tmp_path_factory, gemv_rows, fuse_rows)
     eight_rows = next(names for (lo, hi, _, _), names in programs.items() if lo <= 8 <= hi)
     assert ("mlr_gemv_bf16_prepared" in one_row) == (gemv_rows > 0) and ("mlr_gemv_bf16_prepared" in eight_rows) == (gemv_rows == 8)
     assert ("mlr_rmsnorm" in eight_rows) == (gemv_rows < 8)
-    # (the split-K products of the other route leave partial sums, which only the row-wise kernel adds up)
-    assert ("mlr_attention_decode_fresh_bf16" in one_row) == (fuse_rows > 0 and gemv_rows > 0)
+    # (where the other route's q/k/v product leaves split-K partial sums, only the row-wise kernel can add them up;
+    # at these sizes it goes to the library, so the attention kernel may make its own rows there too)
+    if gemv_rows > 0:
+        assert ("mlr_attention_decode_fresh_bf16" in one_row) == (fuse_rows > 0)
 
 
 def test_thirty_two_query_heads_per_kv_head_decode_from_graphs(tmp_path_factory):
