@@ -60,7 +60,7 @@ constexpr int kStageLoads = 8;              // loads a thread has in flight whil
 constexpr int kGateBlock = 128;
 constexpr int kMaxParts = 12;
 constexpr int kMaxRows = 8;
-constexpr int kPartialBytes = 2 * kConsumerWarps * kUnitRows * kMaxRows * 4;
+constexpr int kPartialBytes = kConsumerWarps * kUnitRows * kMaxRows * 4;        // one buffer of the warps' partial sums
 constexpr long long kWaitLimitCycles = 4000000000LL;      // about two seconds
 
 enum Mode : int { kStoreBf16 = 0, kStoreF32 = 1, kAddF32 = 2, kSiluGateBf16 = 3 };
@@ -95,6 +95,7 @@ struct Job {
     int chunk;                  // values of K per ring slot: a multiple of 512
     int x_bytes;                // shared memory for the activations
     int slots;                  // of the ring: 2, or 3 where the activations leave room
+    int partial_buffers;        // 2: a unit's partial sums do not wait for the unit before to be finished; 1 where shared memory is short
     int* status;
 };
 
@@ -177,7 +178,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     __shared__ int failed_flag;
     // [2][16 warps][16 rows][8 tokens] partial sums of the warps' K ranges | the activations | the ring of weights
     float* partial = reinterpret_cast<float*>(shared);
-    unsigned char* xs = shared + kPartialBytes;
+    unsigned char* xs = shared + job.partial_buffers * kPartialBytes;
     const int slot_pitch = pitch_bytes(job.chunk), slot_bytes = kUnitRows * slot_pitch;
     const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(xs + job.x_bytes));
     const uint32_t bars = static_cast<uint32_t>(__cvta_generic_to_shared(barriers));
@@ -361,6 +362,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
             }
             {
                 // The 16 warps' sums meet in shared memory; 128 threads add them in warp order and finish the rows.
+                if (job.partial_buffers == 1) asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumers) : "memory");      // the unit before has been finished
                 float* mine = partial + ((parity * kConsumerWarps + warp) * kUnitRows) * kMaxRows;
                 mine[g * kMaxRows + 2 * t] = c[0];
                 mine[g * kMaxRows + 2 * t + 1] = c[1];
@@ -413,7 +415,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
                         if (r == 0) l.squares[static_cast<size_t>(unit) * kMaxRows + m] = square;
                     }
                 }
-                parity ^= 1;
+                if (job.partial_buffers == 2) parity ^= 1;
             }
         }
     }
@@ -427,16 +429,16 @@ int sm_limit_bytes() {
 }
 
 // The longest chunk (a multiple of 512 values, at most kMostChunk) whose ring fits beside `x_bytes` of activations; 0: none does.
-int chunk_for(size_t x_bytes) {
+int chunk_for(size_t x_bytes, int partial_buffers = 2) {
     const size_t room = static_cast<size_t>(sm_limit_bytes()) - 2048;        // the kernel's static shared memory and what the driver keeps
     for (int chunk = kMostChunk; chunk >= 512; chunk -= 512)
-        if (kPartialBytes + x_bytes + ring_bytes(chunk, 2) <= room) return chunk;
+        if (partial_buffers * kPartialBytes + x_bytes + ring_bytes(chunk, 2) <= room) return chunk;
     return 0;
 }
 // Slots of the ring: a third one where the activations leave room for it (one or two rows of a model's width).
 int slots_for(size_t x_bytes, int chunk) {
     const size_t room = static_cast<size_t>(sm_limit_bytes()) - 2048;
-    return kPartialBytes + x_bytes + ring_bytes(chunk, kMostSlots) <= room ? kMostSlots : 2;
+    return 2 * kPartialBytes + x_bytes + ring_bytes(chunk, kMostSlots) <= room ? kMostSlots : 2;
 }
 
 // How many parts a product over K values is cut into for M rows (1: it stays whole), and the width of a part.  Only a
@@ -488,11 +490,18 @@ int launch(const Link& l, int M, int* status, cudaStream_t stream) {
         }
     }
     const size_t x_bytes = x_region_bytes(M, job.parts[0].K);
-    job.chunk = chunk_for(x_bytes);
+    // One buffer of partial sums instead of two where that buys longer copies (eight rows of 5120 values are 1.5 KB
+    // too many for the best ring beside two); not for a product that adds: its finish waits for the stream's cells.
+    job.partial_buffers = 2;
+    job.chunk = chunk_for(x_bytes, 2);
+    if (l.mode != kAddF32 && chunk_for(x_bytes, 1) > job.chunk) {
+        job.partial_buffers = 1;
+        job.chunk = chunk_for(x_bytes, 1);
+    }
     MLR_REQUIRE(job.chunk > 0, "gemv_bf16: %d rows of %d values do not fit shared memory", M, l.K);
     job.x_bytes = static_cast<int>(x_bytes);
-    job.slots = slots_for(x_bytes, job.chunk);
-    const size_t bytes = kPartialBytes + x_bytes + ring_bytes(job.chunk, job.slots);
+    job.slots = job.partial_buffers == 2 ? slots_for(x_bytes, job.chunk) : 2;
+    const size_t bytes = job.partial_buffers * kPartialBytes + x_bytes + ring_bytes(job.chunk, job.slots);
     static size_t allowed = 0;
     if (bytes > allowed) {
         if (cudaFuncSetAttribute(gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) != cudaSuccess) {
@@ -511,7 +520,7 @@ int launch(const Link& l, int M, int* status, cudaStream_t stream) {
 // Whether mlr_gemv_bf16 takes a product of `M` rows over K values that does not add into the stream (its activations
 // must fit shared memory beside the ring; a product that adds is cut into parts that do).
 MLR_API int mlr_gemv_bf16_fits(int M, int K) {
-    return M >= 1 && M <= kMaxRows && K >= 8 && K % 8 == 0 && chunk_for(x_region_bytes(M, K)) > 0;
+    return M >= 1 && M <= kMaxRows && K >= 8 && K % 8 == 0 && chunk_for(x_region_bytes(M, K), 1) > 0;
 }
 
 // Into how many parts along K an adding product of `M` rows is cut.

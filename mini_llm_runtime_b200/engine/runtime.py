@@ -59,8 +59,17 @@ def _give_library_workspace(device: torch.device) -> None:
         _library_workspace[index] = space
 
 
-_ROUTING = {"gemv_rows", "fuse_rotation_rows", "use_tcgen05", "tcgen05_prefill", "pair_rows", "pair_everything", "tcgen05_attention", "decode_rows",
+_ROUTING = {"gemv_rows", "gemv_balance", "fuse_rotation_rows", "use_tcgen05", "tcgen05_prefill", "pair_rows", "pair_everything", "tcgen05_attention", "decode_rows",
             "own_activation_products", "pair_min_tiles"}
+
+
+def units_balance(rows: int, sm_count: int) -> float:
+    """How full the rounds are when `rows` rows of a matrix are dealt 16 at a time to one block per SM (1.0 when all
+    units fit one round: then the SMs that get none are idle, but no block waits for another round)."""
+    units = -(-rows // 16)
+    if units <= sm_count:
+        return 1.0
+    return units / (-(-units // sm_count) * sm_count)
 
 
 class Runtime:
@@ -108,6 +117,7 @@ class Runtime:
         # way, against 1.013 and 1.087 ms with the split-K tcgen05 products, the library's q/k/v and gate/up and
         # the three row-wise kernels between them (0 switches back to those).
         self.gemv_rows = 8
+        self.gemv_balance = 0.8
         # A step of decoded tokens only, of at most this many rows: the split-KV attention kernel norms, rotates and
         # writes the cache itself (no row-wise kernel between the q/k/v product and attention).  Measured in the decode
         # step of the 8B sizes (8 layers, context 2000): 0.867 ms against 0.884 ms at one request, 1.169 against 1.187 ms
@@ -271,6 +281,10 @@ class Runtime:
                 or not self._gemv_fits(w.shape[1], adds and x.norm is None)):
             return False
         if w.stride(1) != 1 or w.stride(0) % 8 or w.data_ptr() % 16 or x.width != w.shape[1]:
+            return False
+        # The kernel deals 16 rows of W at a time to one block per SM: a matrix whose units leave the last round
+        # mostly empty (320 units over 148 SMs: 2.2 rounds cost 3) is better off with K cut across the SMs.
+        if units_balance(w.shape[0], self.sm_count) < self.gemv_balance:
             return False
         if x.norm is None and (x.dtype is not torch.bfloat16 or x.ld % 8 or x.ptr % 16):
             return False

@@ -222,3 +222,13 @@ def test_plan_fields_that_say_whether_decoded_tokens_have_the_step_to_themselves
     assert host.step([(a, [1], [0]), (b, [2, 3], [1])])[0] == X.STEP_OK                    # tokens only
     recorded = host.recorded()
     assert recorded[0][:4] == [2, 2, 0, 0] and [r[0] for r in recorded[1:]] == [1]
+
+
+def test_the_few_row_route_is_left_to_matrices_whose_units_fill_their_rounds():
+    """`units_balance`: 16 rows of a matrix at a time, one block per SM.  256 or 384 units over 148 SMs fill 86 % of
+    their rounds; 320 units (a width of 5120) fill 72 % and are routed to the products that cut K across the SMs."""
+    from mini_llm_runtime_b200.engine.runtime import units_balance
+    assert units_balance(4096, 148) == pytest.approx(256 / 296) and units_balance(6144, 148) == pytest.approx(384 / 444)
+    assert units_balance(5120, 148) == pytest.approx(320 / 444) < 0.8 <= units_balance(4096, 148)
+    assert units_balance(1024, 148) == 1.0 and units_balance(16 * 148, 148) == 1.0 and units_balance(16 * 149, 148) == pytest.approx(149 / 296)
+    assert units_balance(151936, 148) > 0.98

@@ -192,7 +192,7 @@ def test_gemm_bf16_tcgen05(M, N, K, out_dtype):
 
 
 @pytest.mark.parametrize("M", [1, 2, 3, 5, 8])
-@pytest.mark.parametrize("N,K", [(512, 264), (4096, 4096), (6144, 1024), (301, 96), (2, 8), (100, 12288)])
+@pytest.mark.parametrize("N,K", [(512, 264), (4096, 4096), (6144, 1024), (301, 96), (2, 8), (100, 12288), (300, 5120)])
 def test_gemv_bf16_and_what_it_folds_in(M, N, K):
     """The few-row product on the CUDA cores: plain, added into the float32 stream, with the RMS norm of
     the stream (all rows, or indexed rows) as its prologue; odd row counts and widths that are no power of two."""
@@ -233,7 +233,7 @@ def test_gemv_bf16_and_what_it_folds_in(M, N, K):
             assert torch.allclose(got.cpu().double(), want_n, atol=3e-2, rtol=3e-2), (got.cpu().double() - want_n).abs().max()
 
 
-@pytest.mark.parametrize("M,inter,K", [(1, 256, 128), (4, 12288, 4096), (3, 300, 104), (8, 1000, 512)])
+@pytest.mark.parametrize("M,inter,K", [(1, 256, 128), (4, 12288, 4096), (3, 300, 104), (8, 1000, 512), (8, 640, 5120)])
 def test_gemv_bf16_gate(M, inter, K):
     """silu(gate) * up in the epilogue, over the stacked operand the feed-forward keeps (blocks of 128 gate
     rows and their up rows, padded with zero rows)."""
