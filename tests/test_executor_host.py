@@ -229,6 +229,6 @@ def test_the_few_row_route_is_left_to_matrices_whose_units_fill_their_rounds():
     their rounds; 320 units (a width of 5120) fill 72 % and are routed to the products that cut K across the SMs."""
     from mini_llm_runtime_b200.engine.runtime import units_balance
     assert units_balance(4096, 148) == pytest.approx(256 / 296) and units_balance(6144, 148) == pytest.approx(384 / 444)
-    assert units_balance(5120, 148) == pytest.approx(320 / 444) < 0.8 <= units_balance(4096, 148)
+    assert units_balance(5120, 148) == pytest.approx(320 / 444) and units_balance(5120, 148) < 0.8 <= units_balance(4096, 148)
     assert units_balance(1024, 148) == 1.0 and units_balance(16 * 148, 148) == 1.0 and units_balance(16 * 149, 148) == pytest.approx(149 / 296)
     assert units_balance(151936, 148) > 0.98
