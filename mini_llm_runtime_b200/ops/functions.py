@@ -330,7 +330,7 @@ def gemv_bf16_prepared(w: torch.Tensor, side: torch.Tensor, squares: torch.Tenso
 
 def product_modules(dtype) -> list:
     """The kernel modules the matrix products of a precision may call."""
-    return ["gemm_f32"] if dtype is torch.float32 else ["gemm_bf16_tcgen05", "gemm_bf16_tcgen05_pair"]
+    return ["gemm_f32"] if dtype is torch.float32 else ["gemv_bf16", "gemm_bf16_tcgen05", "gemm_bf16_tcgen05_pair"]
 
 
 def gemm_tcgen05_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
