@@ -29,19 +29,23 @@
 //    of 128 gate rows followed by their 128 "up" rows): a unit's 16 rows are then 8 gate rows and their 8
 //    up rows, and it stores silu(gate) * up.
 //
-// Two more things keep eight rows as fast as one:
-//  * A product that ADDS into the stream and whose activations would not leave room for the ring (eight
-//    rows of a feed-forward's inner width are 200 KB) is cut along K into parts: each stages only its
-//    columns of x and adds its partial product into the stream (a cell has the same owner in every part).
+// Three more things keep eight rows as fast as one:
+//  * Where K is at most 4096 and no norm has to be worked out from the stream, the activations never go to shared
+//    memory: a lane needs 16 bytes of its token's row per 512 values of K, eight registers' worth of loads, and
+//    shared memory is all ring (three slots at any row count).  A product that ADDS into the stream is cut along K
+//    into parts of at most 4096 values for that: each part adds its partial product into the stream (a cell has the
+//    same owner in every part).  Other products (a norm prologue, a wider K) stage their activations in shared
+//    memory beside a ring of two slots (three at one row), with shorter copies or one buffer of partial sums
+//    where room is short.
 //  * Every block needs all of a product's activations, so 148 blocks reading eight float32 rows of the
 //    stream for a norm is 19 MB through L2 (8 us).  The product that added into that stream last has the
 //    final values in hand: `mlr_gemv_bf16_add_prepare` stores them a second time as bfloat16, already times
 //    the norm's weight, and the sum of squares of its 16 rows per token; `mlr_gemv_bf16_prepared` then
-//    stages half the bytes in one pass and adds up the partial sums in a fixed order for the row's 1/rms.
+//    reads half the bytes and adds up the partial sums in a fixed order for the row's 1/rms.
 //
 // Measured on a B200 with the 8B layer sizes in a CUDA graph (o_proj, gate/up, down, q/k/v as launches of
-// their own): 7.3 / 31.5 / 18.6 / 9.8 us at one row, 8.0 / 32.3 / 21.5 / 10.2 us at eight, 6.4 TB/s on the
-// largest.  Run by one persistent grid with meetings of all blocks between the products instead of launch
+// their own): 6.9 / 30.4 / 18.1 / 8.8 us at one row, 8.2 / 31.9 / 21.7 / 9.7 us at eight, 6.3 to 6.6 TB/s on
+// the largest.  Run by one persistent grid with meetings of all blocks between the products instead of launch
 // boundaries they took 3.5 us longer per layer, so that form was dropped.
 //
 // The reference sends these products to cuBLAS gemv kernels (src/minillm/cuda/matrix.cpp:30-36) and
@@ -55,10 +59,11 @@ constexpr int kConsumers = kConsumerWarps * 32;
 constexpr int kThreads = kConsumers + 32;   // and the warp that fetches weights
 constexpr int kUnitRows = 16;
 constexpr int kMostSlots = 3;
+constexpr int kRegisterBlocks = 8;          // blocks of 512 values of K whose activations a lane can keep in registers
 constexpr int kMostChunk = 2048;            // values of K of a unit's 16 rows in one slot of the ring, at most (4 KB copies)
 constexpr int kStageLoads = 8;              // loads a thread has in flight while a part's activations are staged
 constexpr int kGateBlock = 128;
-constexpr int kMaxParts = 12;
+constexpr int kMaxParts = 16;
 constexpr int kMaxRows = 8;
 constexpr int kPartialBytes = kConsumerWarps * kUnitRows * kMaxRows * 4;        // one buffer of the warps' partial sums
 constexpr long long kWaitLimitCycles = 4000000000LL;      // about two seconds
@@ -169,6 +174,10 @@ __host__ __device__ inline int pitch_bytes(int values) { return values * 2 + ((6
 __host__ __device__ inline size_t x_region_bytes(int M, int K) { return (static_cast<size_t>(M) * pitch_bytes(K) + 127) / 128 * 128; }
 __host__ __device__ inline size_t ring_bytes(int chunk, int slots) { return static_cast<size_t>(slots) * kUnitRows * pitch_bytes(chunk); }
 
+// XREG: the activations stay in registers (a lane needs 16 bytes of its token's row per 512 values of K, at most
+// kRegisterBlocks of them), shared memory holds no copy of them and the ring has a third slot at any row count.  Only
+// for parts of at most 512 * kRegisterBlocks values whose norm, if any, was prepared.
+template <bool XREG>
 __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant__ Job job) {
     extern __shared__ __align__(128) unsigned char shared[];
     __shared__ float reduce_scratch[32];
@@ -316,7 +325,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
             } else if (threadIdx.x < kMaxRows) {
                 row_scale[threadIdx.x] = 1.0f;
             }
-            if (m < M) {
+            if (!XREG && m < M) {
             const uint4* x = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(l.x) + static_cast<size_t>(m) * l.ldx);
             uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<size_t>(m) * stride);
             const int octs = K >> 3;
@@ -341,8 +350,44 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
         const int units = units_of(l), chunks = (K + job.chunk - 1) / job.chunk, subs = job.chunk / 512;
         const uint32_t x_at = static_cast<uint32_t>(__cvta_generic_to_shared(xs)) + g * stride;
         const uint32_t in_slot = (warp * 32 + t * 8) * 2;
+        uint4 xr[XREG ? kRegisterBlocks : 1];
+        if constexpr (XREG) {
+            // This lane's 16 bytes of its token's row for every 512 values of K, straight from the kernel before.
+            const uint4 zero = make_uint4(0, 0, 0, 0);
+            const __nv_bfloat16* row = static_cast<const __nv_bfloat16*>(l.x) + static_cast<size_t>(g < M ? g : 0) * l.ldx;
+#pragma unroll
+            for (int b = 0; b < kRegisterBlocks; ++b) {
+                const int k = b * 512 + warp * 32 + t * 8;
+                xr[b] = g < M && k < K ? __ldcg(reinterpret_cast<const uint4*>(row + k)) : zero;
+            }
+        }
         for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
             float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if constexpr (XREG) {
+                // chunks of kMostChunk values: at most kRegisterBlocks / 4 of them, so every register's index is a constant
+#pragma unroll
+                for (int chunk = 0; chunk < kRegisterBlocks / 4; ++chunk) {
+                    if (chunk < chunks) {
+                        const int slot = i % slots;
+                        wait_phase(full_bar(slot), (i / slots) & 1, failed, job.status);
+#pragma unroll
+                        for (int sub = 0; sub < 4; ++sub) {
+                            const int k = chunk * kMostChunk + sub * 512 + warp * 32 + t * 8;
+                            const bool in = k < K;
+                            const uint32_t at = ring + slot * slot_bytes + sub * 1024 + in_slot;
+                            const uint4 zero = make_uint4(0, 0, 0, 0);
+                            const uint4 a = in ? load_shared16(at + g * slot_pitch) : zero;
+                            const uint4 b = in ? load_shared16(at + (g + 8) * slot_pitch) : zero;
+                            const uint4 x = xr[chunk * 4 + sub];
+                            mma_16x8x16(c, a.x, b.x, a.y, b.y, x.x, x.y);
+                            mma_16x8x16(c, a.z, b.z, a.w, b.w, x.z, x.w);
+                        }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(empty_bar(slot));
+                        ++i;
+                    }
+                }
+            } else {
             for (int chunk = 0; chunk < chunks; ++chunk, ++i) {
                 const int slot = i % slots;
                 wait_phase(full_bar(slot), (i / slots) & 1, failed, job.status);
@@ -359,6 +404,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
                 }
                 __syncwarp();          // every lane's reads of the slot have ended in its multiply-adds
                 if (lane == 0) mbar_arrive(empty_bar(slot));
+            }
             }
             {
                 // The 16 warps' sums meet in shared memory; 128 threads add them in warp order and finish the rows.
@@ -443,8 +489,18 @@ int slots_for(size_t x_bytes, int chunk) {
 
 // How many parts a product over K values is cut into for M rows (1: it stays whole), and the width of a part.  Only a
 // product that adds into the stream can be cut; it is, when its activations would push the ring below its best size.
+// Whether a product keeps its activations in registers: its norm, if any, was prepared, and its K (or, for a product
+// that adds into the stream, the K of its parts) is at most 512 * kRegisterBlocks.
+bool in_registers(int K, int mode, int norm) { return norm != 1 && (mode == kAddF32 || K <= 512 * kRegisterBlocks); }
+
 int parts_of(int M, int K, int mode, int norm, int& part_width) {
     part_width = K;
+    if (in_registers(K, mode, norm)) {
+        const int parts = (K + 512 * kRegisterBlocks - 1) / (512 * kRegisterBlocks);
+        if (parts > kMaxParts) return 0;        // (the caller falls back to shared memory)
+        part_width = ((K + parts - 1) / parts + 63) / 64 * 64;
+        return (K + part_width - 1) / part_width;
+    }
     if (mode != kAddF32 || norm != 0 || chunk_for(x_region_bytes(M, K)) == kMostChunk) return 1;
     for (int least = kMostChunk; least >= 512; least -= kMostChunk - 512)       // the best ring if some cut allows it, else any ring
         for (int parts = 2; parts <= kMaxParts; ++parts) {
@@ -478,6 +534,7 @@ int launch(const Link& l, int M, int* status, cudaStream_t stream) {
     job.status = status;
     int width = 0;
     job.n_parts = parts_of(M, l.K, l.mode, l.norm, width);
+    if (job.n_parts == 0) job.n_parts = 1, width = l.K;
     for (int part = 0; part < job.n_parts; ++part) {
         Link& p = job.parts[part];
         p = l;
@@ -489,29 +546,41 @@ int launch(const Link& l, int M, int* status, cudaStream_t stream) {
             if (part + 1 < job.n_parts) p.side = nullptr, p.squares = nullptr;       // the last part has the stream's final values
         }
     }
-    const size_t x_bytes = x_region_bytes(M, job.parts[0].K);
-    // One buffer of partial sums instead of two where that buys longer copies (eight rows of 5120 values are 1.5 KB
-    // too many for the best ring beside two); not for a product that adds: its finish waits for the stream's cells.
-    job.partial_buffers = 2;
-    job.chunk = chunk_for(x_bytes, 2);
-    if (l.mode != kAddF32 && chunk_for(x_bytes, 1) > job.chunk) {
-        job.partial_buffers = 1;
-        job.chunk = chunk_for(x_bytes, 1);
+    const bool registers = in_registers(l.K, l.mode, l.norm) && job.parts[0].K <= 512 * kRegisterBlocks;
+    size_t x_bytes = 0;
+    if (registers) {
+        job.partial_buffers = 2;
+        job.chunk = kMostChunk;
+        job.slots = kMostSlots;
+    } else {
+        x_bytes = x_region_bytes(M, job.parts[0].K);
+        // One buffer of partial sums instead of two where that buys longer copies (eight rows of 5120 values are 1.5 KB
+        // too many for the best ring beside two); not for a product that adds: its finish waits for the stream's cells.
+        job.partial_buffers = 2;
+        job.chunk = chunk_for(x_bytes, 2);
+        if (l.mode != kAddF32 && chunk_for(x_bytes, 1) > job.chunk) {
+            job.partial_buffers = 1;
+            job.chunk = chunk_for(x_bytes, 1);
+        }
+        MLR_REQUIRE(job.chunk > 0, "gemv_bf16: %d rows of %d values do not fit shared memory", M, l.K);
+        job.slots = job.partial_buffers == 2 ? slots_for(x_bytes, job.chunk) : 2;
     }
-    MLR_REQUIRE(job.chunk > 0, "gemv_bf16: %d rows of %d values do not fit shared memory", M, l.K);
     job.x_bytes = static_cast<int>(x_bytes);
-    job.slots = job.partial_buffers == 2 ? slots_for(x_bytes, job.chunk) : 2;
     const size_t bytes = job.partial_buffers * kPartialBytes + x_bytes + ring_bytes(job.chunk, job.slots);
-    static size_t allowed = 0;
-    if (bytes > allowed) {
-        if (cudaFuncSetAttribute(gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) != cudaSuccess) {
+    const int units = units_of(l), sms = mlr_sm_count();
+    const dim3 grid(units < sms ? units : sms);
+    static size_t allowed[2] = {0, 0};
+    if (bytes > allowed[registers]) {
+        const cudaError_t e = registers ? cudaFuncSetAttribute(gemv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes))
+                                        : cudaFuncSetAttribute(gemv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+        if (e != cudaSuccess) {
             cudaGetLastError();
             return mlr_fail("gemv_bf16: %zu bytes of shared memory were refused", bytes);
         }
-        allowed = bytes;
+        allowed[registers] = bytes;
     }
-    const int units = units_of(l), sms = mlr_sm_count();
-    mlr_launch((gemv_kernel), dim3(units < sms ? units : sms), dim3(kThreads), bytes, stream, job);
+    if (registers) mlr_launch((gemv_kernel<true>), grid, dim3(kThreads), bytes, stream, job);
+    else mlr_launch((gemv_kernel<false>), grid, dim3(kThreads), bytes, stream, job);
     return mlr_launched("gemv_bf16");
 }
 
@@ -520,7 +589,7 @@ int launch(const Link& l, int M, int* status, cudaStream_t stream) {
 // Whether mlr_gemv_bf16 takes a product of `M` rows over K values that does not add into the stream (its activations
 // must fit shared memory beside the ring; a product that adds is cut into parts that do).
 MLR_API int mlr_gemv_bf16_fits(int M, int K) {
-    return M >= 1 && M <= kMaxRows && K >= 8 && K % 8 == 0 && chunk_for(x_region_bytes(M, K), 1) > 0;
+    return M >= 1 && M <= kMaxRows && K >= 8 && K % 8 == 0 && (K <= 512 * kRegisterBlocks || chunk_for(x_region_bytes(M, K), 1) > 0);
 }
 
 // Into how many parts along K an adding product of `M` rows is cut.

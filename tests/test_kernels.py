@@ -271,7 +271,7 @@ def test_gemv_bf16_refuses_what_it_cannot_do():
 def test_gemv_bf16_layer_with_parts_and_prepared_norms(M, H, I, QKV):
     """The four products of a layer as a decode step launches them: o_proj adds into the stream and leaves the next
     norm half done (the stream times the norm's weight as bfloat16, sums of squares per 16 rows), gate/up takes that,
-    down adds (cut along K into parts when its activations are wide: 8 rows of 6400 or 4 of 10240 values are) and
+    down adds (cut along K into parts of at most 4096 values) and
     prepares the q/k/v product's norm.  Against float64 and against the same products with the norm as a prologue;
     the same bits on every run."""
     g = lambda seed, *shape: (torch.randn(*shape, generator=gen(seed)) * 0.04).to(torch.bfloat16).to(DEV)
@@ -283,7 +283,7 @@ def test_gemv_bf16_layer_with_parts_and_prepared_norms(M, H, I, QKV):
     stream0 = torch.randn(M, H, generator=gen(9)).to(DEV)
     native = __import__("mini_llm_runtime_b200.ops.native", fromlist=["x"])
     parts = native.module("gemv_bf16").mlr_gemv_bf16_parts
-    assert (parts(M, I) > 1) == (M * I * 2 > 78 * 1024) and parts(M, H) == 1
+    assert parts(M, I) == -(-I // 4096) and parts(M, H) == 1          # parts of at most 4096 values: a lane keeps their activations in registers
     st = status()
 
     def layer(prepare):
