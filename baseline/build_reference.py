@@ -2,7 +2,7 @@
 """Builds the reference arm of bench.py: lilong555/mini-llm-runtime's own CUDA runtime,
 compiled UNCHANGED, behind the small driver `baseline/reference_driver.cpp`.
 
-    python baseline/build_reference.py [/path/to/mini-llm-runtime]      (default /root/reference)
+    python baseline/build_reference.py /path/to/mini-llm-runtime        (or MLR_REFERENCE in the environment)
 
 The reference is a CMake C++/CUDA project, not a Python package (`pip install` of its
 checkout fails: neither setup.py nor pyproject.toml), and its build also wants llama.cpp
@@ -30,7 +30,10 @@ SOURCES = ["src/minillm/kernels.cpp", "src/minillm/kernels_avx2.cpp", "src/minil
 
 
 def main() -> int:
-    reference = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    reference = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MLR_REFERENCE", "")
+    if not reference or not os.path.isdir(os.path.join(reference, "src", "minillm")):
+        print("usage: build_reference.py /path/to/a checkout of lilong555/mini-llm-runtime (or set MLR_REFERENCE)", file=sys.stderr)
+        return 2
     tree = os.path.join(OUT, "reference")
     if os.path.isdir(tree):
         shutil.rmtree(tree)
