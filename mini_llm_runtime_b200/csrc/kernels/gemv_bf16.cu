@@ -29,7 +29,7 @@
 //    of 128 gate rows followed by their 128 "up" rows): a unit's 16 rows are then 8 gate rows and their 8
 //    up rows, and it stores silu(gate) * up.
 //
-// Three more things keep eight rows as fast as one:
+// Two more things keep eight rows as fast as one:
 //  * Where K is at most 4096 and no norm has to be worked out from the stream, the activations never go to shared
 //    memory: a lane needs 16 bytes of its token's row per 512 values of K, eight registers' worth of loads, and
 //    shared memory is all ring (three slots at any row count).  A product that ADDS into the stream is cut along K
